@@ -1,0 +1,197 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+The reference has three calls: a whole prompt (or its tail from ``pos_offset``) of one
+sequence, one token of one sequence, one token each of many sequences
+(src/transformer/forward.rs:694-703, :435-444, :1328-1337); prompts of different requests are
+never batched.  Here one ``step`` takes any mix: portions of prompts beside single decoded
+tokens, cut anywhere.  As in the reference, the keys and values of all tokens of the step are
+written first and then every token attends its request's cache up to its own position
+(:875-877, :927-972).  Logits are computed only for the rows that are asked for.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager
+from ..errors import RequestError
+
+
+@dataclass
+class StepEntry:
+    """The next ``tokens`` of the request in ``slot``; ``want`` lists the places among these
+    tokens whose logits are returned, in order."""
+    slot: int
+    tokens: list
+    want: list = field(default_factory=list)
+
+
+def _align4(n):
+    return (n + 3) & ~3
+
+
+class StepContext:
+    """Everything about one step that parts may read.  Device tensors are int32.
+
+    ``token_ids``, ``positions``, ``token_seq`` are per token; ``token_seq`` is the index of the
+    token's request within this step, which is also its row in every block table.
+    ``seq_slot``, ``seq_start`` (tokens cached before the step), ``cu_seqlens`` (token offsets,
+    one more than requests) are per request; ``logit_rows`` are the token rows whose logits are
+    wanted.  The ``h_`` fields are host copies for planning launches.
+    """
+
+    def __init__(self, cache, entries, meta_dev, staging):
+        n = len(entries)
+        lens = [len(e.tokens) for e in entries]
+        T = sum(lens)
+        self.num_tokens, self.num_seqs = T, n
+        self.h_seq_lens = lens
+        self.h_seq_slot = [e.slot for e in entries]
+        self.h_seq_start = [cache.length(e.slot) for e in entries]
+        self.h_cu_seqlens = [0]
+        for l in lens:
+            self.h_cu_seqlens.append(self.h_cu_seqlens[-1] + l)
+        self.max_seq_len = max(lens)
+        self.max_context = max(s + l for s, l in zip(self.h_seq_start, lens))
+        rows = []
+        for i, e in enumerate(entries):
+            for w in e.want:
+                if not 0 <= w < lens[i]:
+                    raise RequestError(f"wanted place {w} lies outside the {lens[i]} tokens given")
+                rows.append(self.h_cu_seqlens[i] + w)
+        self.num_logit_rows = len(rows)
+        self.is_decode = self.max_seq_len == 1
+        self._groups = cache.groups
+        tables = cache.block_tables(self.h_seq_slot)
+        max_pages = [t.shape[1] for t in tables]
+
+        # one packed int32 buffer -> one copy to the device
+        sizes = [T, T, T, n, n, n + 1, len(rows)] + [n * mp for mp in max_pages]
+        offs, total = [], 0
+        for s in sizes:
+            offs.append(total)
+            total += _align4(max(s, 1))
+        pack = staging(total)
+        ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        pack[offs[0]:offs[0] + T] = ids
+        pos = np.concatenate([np.arange(s, s + l, dtype=np.int64) for s, l in zip(self.h_seq_start, lens)])
+        pack[offs[1]:offs[1] + T] = pos
+        pack[offs[2]:offs[2] + T] = np.repeat(np.arange(n, dtype=np.int64), lens)
+        pack[offs[3]:offs[3] + n] = self.h_seq_slot
+        pack[offs[4]:offs[4] + n] = self.h_seq_start
+        pack[offs[5]:offs[5] + n + 1] = self.h_cu_seqlens
+        if rows:
+            pack[offs[6]:offs[6] + len(rows)] = rows
+        for g, t in enumerate(tables):
+            pack[offs[7 + g]:offs[7 + g] + t.size] = t.reshape(-1)
+        dev = meta_dev(pack, total)
+        cut = lambda k, size: dev[offs[k]:offs[k] + size]
+        self.token_ids = cut(0, T)
+        self.positions = cut(1, T)
+        self.token_seq = cut(2, T)
+        self.seq_slot = cut(3, n)
+        self.seq_start = cut(4, n)
+        self.cu_seqlens = cut(5, n + 1)
+        self.logit_rows = cut(6, len(rows))
+        self.block_tables = [cut(7 + g, n * mp).view(n, mp) for g, mp in enumerate(max_pages)]
+
+    def block_table(self, group):
+        """Device block table [requests of this step, max pages] of a cache group."""
+        for g, t in zip(self._groups, self.block_tables):
+            if g is group:
+                return t
+        raise KeyError(group.name)
+
+
+class Engine:
+    """A model, its cache and the step function.  Requests are known here only by slot."""
+
+    def __init__(self, model, num_pages, num_slots=64, page_size=16):
+        self.model = model
+        self.rt = model.rt
+        needs, cache_of = model.cache_needs()
+        self.cache = CacheManager(needs, cache_of, num_slots, num_pages, page_size, model.spec.max_positions,
+                                  self.rt.dtype, self.rt.device)
+        self.vocab_size = model.spec.vocab_size
+        self._meta_dev = None
+        self._staging = []
+        self._staging_events = []
+        self._staging_next = 0
+        self.steps = 0
+        self.tokens_run = 0
+
+    # ---- request slots ----------------------------------------------------------------------------
+
+    def open(self):
+        """Admit a request: returns its slot."""
+        return self.cache.alloc_slot()
+
+    def close(self, slot):
+        """The request is finished: its pages and its slot are given back."""
+        self.cache.free_slot(slot)
+
+    # ---- metadata staging -------------------------------------------------------------------------
+
+    def _stage(self, total):
+        """A pinned int32 host buffer of at least ``total`` elements that no copy in flight reads."""
+        k = self._staging_next
+        if len(self._staging) < 4:
+            self._staging.append(None)
+            self._staging_events.append(None)
+            k = len(self._staging) - 1
+        self._staging_next = (k + 1) % 4
+        if self._staging_events[k] is not None:
+            self._staging_events[k].synchronize()
+        buf = self._staging[k]
+        if buf is None or buf.numel() < total:
+            buf = torch.empty(max(total, 4096), dtype=torch.int32).pin_memory()
+            self._staging[k] = buf
+        self._staging_current = k
+        return buf.numpy()
+
+    def _upload(self, pack, total):
+        if self._meta_dev is None or self._meta_dev.numel() < total:
+            self._meta_dev = torch.empty(max(total * 2, 1 << 16), dtype=torch.int32, device=self.rt.device)
+        k = self._staging_current
+        self._meta_dev[:total].copy_(self._staging[k][:total], non_blocking=True)
+        ev = self._staging_events[k] or torch.cuda.Event()
+        ev.record()
+        self._staging_events[k] = ev
+        return self._meta_dev
+
+    # ---- the step ---------------------------------------------------------------------------------
+
+    def validate(self, entries):
+        if not entries:
+            raise RequestError("a step needs at least one entry")
+        seen = set()
+        for e in entries:
+            if e.slot in seen:
+                raise RequestError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            if len(e.tokens) == 0:
+                raise RequestError("an entry without tokens")
+            lo, hi = min(e.tokens), max(e.tokens)
+            if lo < 0 or hi >= self.vocab_size:
+                raise RequestError(f"token id {lo if lo < 0 else hi} lies outside the vocabulary of "
+                                   f"{self.vocab_size}")
+
+    def step(self, entries):
+        """Run the entries as one batch.  Returns float32 logits [wanted rows, vocab] on the
+        device, in the order of the entries and of each ``want`` (``None`` if nothing is wanted).
+
+        Raises ``PagePoolExhausted`` before anything ran when the cache cannot hold the new
+        tokens; the cache is then unchanged apart from pages that a window had already passed.
+        """
+        self.validate(entries)
+        rows = [(e.slot, len(e.tokens)) for e in entries]
+        self.cache.reserve(rows)
+        with torch.cuda.device(self.rt.device):
+            ctx = StepContext(self.cache, entries, self._upload, self._stage)
+            logits = self.model.forward(ctx, self.cache)
+        self.cache.advance(rows)
+        self.steps += 1
+        self.tokens_run += ctx.num_tokens
+        return logits

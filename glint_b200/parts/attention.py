@@ -1,0 +1,85 @@
+"""Grouped-query attention over the paged cache.
+
+q, k, v products without bias (src/transformer/forward.rs:546-557; the three matrices are
+stacked into one at load, which is exact), position encoding of q and k, cache write
+(:569-572), scores * multiplier then cap * tanh(score / cap) (src/tensor/flash.rs:76-87),
+softmax and weighted values in 32-bit (:65-123), keys of a token at position p from
+max(0, p - window + 1) to p, or from 0 without a window
+(src/transformer/forward.rs:574-582), output product (:675).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..cache import PagedKVNeed
+from .base import Part, TensorNeed
+from .linear import linear
+from .registry import build_part, register_part
+
+
+class Attention(Part):
+    def __init__(self, rt, params, tensors):
+        super().__init__(rt, params, tensors)
+        p = params
+        self.hidden_size = int(p["hidden_size"])
+        self.num_heads = int(p["num_heads"])
+        self.num_kv_heads = int(p["num_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.multiplier = float(p["score_multiplier"])
+        self.softcap = p.get("softcap") or 0.0
+        self.window = p.get("window") or None
+        self.position = build_part("position", p["position"], rt)
+        self.w_qkv = None
+        self.w_o = None
+
+    @property
+    def q_size(self):
+        return self.num_heads * self.head_dim
+
+    @property
+    def kv_size(self):
+        return self.num_kv_heads * self.head_dim
+
+    def cache_need(self):
+        return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window)
+
+    def needs(self):
+        n = self.names
+        return [TensorNeed(n["q"], (self.q_size, self.hidden_size)),
+                TensorNeed(n["k"], (self.kv_size, self.hidden_size)),
+                TensorNeed(n["v"], (self.kv_size, self.hidden_size)),
+                TensorNeed(n["o"], (self.hidden_size, self.q_size))]
+
+    def bind(self, tensors):
+        n = self.names
+        self.w_qkv = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
+        self.w_o = tensors[n["o"]]
+
+    def forward(self, normed, ctx, view, state=None):
+        rt = self.rt
+        T = normed.shape[0]
+        qkv = linear(rt, normed, self.w_qkv)
+        q = torch.empty((T, self.q_size), dtype=rt.dtype, device=normed.device)
+        self.position.encode_and_store(qkv, ctx, q, view, self.num_heads, self.num_kv_heads, self.head_dim)
+        out = torch.empty_like(q)
+        self.attend(q, ctx, view, out)
+        return linear(rt, out, self.w_o)
+
+    def attend(self, q, ctx, view, out):
+        rt = self.rt
+        if rt.tensor_cores:
+            from .. import ops_tensor
+            if ops_tensor.attention_supported(self.num_heads, self.num_kv_heads, self.head_dim, view.page_size):
+                ops_tensor.attention(q, view, ctx, out, self.num_heads, self.num_kv_heads, self.head_dim,
+                                     self.multiplier, self.softcap, self.window, rt.status)
+                return
+        ops.attention_plain(q, view.k, view.v, ctx.positions, ctx.token_seq, ctx.block_table(view.group), out,
+                            self.num_heads, self.num_kv_heads, self.head_dim, view.page_size, view.num_pages,
+                            self.multiplier, self.softcap, self.window, rt.status)
+
+    def parameter_bytes(self):
+        return (self.w_qkv.numel() + self.w_o.numel()) * self.w_o.element_size()
+
+
+register_part("mixer", "attention", Attention)

@@ -1,0 +1,46 @@
+"""What every part is: a class built from its sizes and constants, that names the tensors it
+needs and later receives them.  No part knows which model it is in.
+
+Interfaces (``ctx`` is the step's ``StepContext``; activations are [tokens, size]):
+
+* norm:          ``forward(x_f32, out=None, row_index=None) -> normalized (activation dtype)``;
+                 ``triple()`` -> (weight, eps, offset) for fused add+norm kernels, or ``None``
+* position:      ``encode_and_store(qkv_f32, ctx, q_out, view, nh, nkv, hd)``
+* mixer:         ``cache_need() -> PagedKVNeed | SlotStateNeed | None``;
+                 ``forward(normed, ctx, view, state) -> float32 [tokens, hidden]``
+* feed-forward:  ``forward(normed, ctx) -> float32 [tokens, hidden]``
+* embedding:     ``forward(token_ids, ctx) -> float32 [tokens, hidden]``
+* head:          ``forward(normed_rows, ctx) -> float32 logits [rows, vocab]``
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+
+@dataclass
+class TensorNeed:
+    """One tensor of the weight file: ``kind`` is 'matrix' (kept in the engine's dtype),
+    'vector' (kept in 32-bit: norms) or 'int' (kept as int32)."""
+    name: str
+    shape: tuple
+    kind: str = "matrix"
+    optional: bool = False
+
+
+class Part:
+    """Base of all parts.  ``spec.tensors`` maps the part's roles to file names."""
+
+    def __init__(self, rt, params, tensors):
+        self.rt = rt
+        self.params = dict(params)
+        self.names = dict(tensors)
+
+    def needs(self):
+        return []
+
+    def bind(self, tensors):
+        """Receive the loaded tensors (by file name) once, on the device."""
+
+    def parameter_bytes(self):
+        """Bytes of weights this part reads in one step (for roofline accounting)."""
+        return 0

@@ -1,0 +1,77 @@
+"""Replay on the GPU against the plain implementation: each request whole, most of it in one
+step and the last 32 tokens one by one, portions of changing size, and mixed batches with so
+few pages that they are used again; in 32-bit and in bfloat16."""
+import numpy as np
+import pytest
+
+from tests import tracing
+from tests.helpers import TINY, TOL, make_model_dir, plain_logits, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [5, 23, 40, 61], "B": [1, 9, 31, 77], "C": [3, 50, 120, 97]}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    return {name: make_model_dir(root, name) for name in TINY}
+
+
+@pytest.fixture(scope="module")
+def expected(folders):
+    out = {}
+    for name, folder in folders.items():
+        vocab = TINY[name][0]["vocab_size"]
+        reqs = {f"r{i}": random_tokens(n, vocab, 100 * ord(name) + i) for i, n in enumerate(LENGTHS[name])}
+        out[name] = (reqs, {rid: plain_logits(folder, toks) for rid, toks in reqs.items()})
+    return out
+
+
+def _engine(folder, dtype, max_tokens, kernels="auto"):
+    from glint_b200.engine.loading import build_engine, load_model
+    return build_engine(load_model(folder, dtype, kernels=kernels), max_tokens, num_slots=4)
+
+
+def _check(name, dtype, steps, outputs, expected_logits):
+    vocab = TINY[name][0]["vocab_size"]
+    got = tracing.collect(steps, outputs, vocab)
+    for rid, want in expected_logits.items():
+        assert got[rid].shape == want.shape, (rid, got[rid].shape, want.shape)
+        diff = np.abs(got[rid] - want)
+        worst = np.unravel_index(np.argmax(diff), diff.shape)
+        assert diff.max() <= TOL[dtype], (
+            f"{name}/{dtype}/{rid}: max |diff| {diff.max():.3e} at position {worst[0]}, token {worst[1]}; "
+            f"first position over tolerance: {int(np.argmax(diff.max(axis=1) > TOL[dtype]))}")
+
+
+MODES = {
+    "whole": lambda reqs: tracing.whole(reqs),
+    "tail": lambda reqs: tracing.tail_decode(reqs, 32),
+    "chunked": lambda reqs: tracing.chunked(reqs),
+    "mixed": lambda reqs: tracing.mixed(reqs, seed=3),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", list(MODES))
+@pytest.mark.parametrize("name", list(TINY))
+def test_replay_in_process(folders, expected, name, mode, dtype):
+    reqs, want = expected[name]
+    steps = MODES[mode](reqs)
+    engine = _engine(folders[name], dtype, tracing.max_live_tokens(steps))
+    outputs = tracing.run_in_process(engine, steps)
+    _check(name, dtype, steps, outputs, want)
+    if mode == "mixed":
+        assert any(s["reuses"] > 0 for s in engine.cache.stats().values()), "no page was used again"
+    assert all(s["live"] == 0 for s in engine.cache.stats().values())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_child_process(folders, expected, tmp_path, dtype):
+    """The same through bin/trace_run as a child process (mixed trace of configuration B)."""
+    reqs, want = expected["B"]
+    steps = tracing.mixed(reqs, seed=7)
+    outputs = tracing.run_child(folders["B"], dtype, steps, str(tmp_path / "out"),
+                                tracing.max_live_tokens(steps), TINY["B"][0]["vocab_size"])
+    _check("B", dtype, steps, outputs, want)
