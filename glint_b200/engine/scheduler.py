@@ -1,0 +1,230 @@
+"""Continuous batching above the step function.
+
+The reference's engine loop (src/server/engine.rs:449-671) admits requests first-come while
+fewer than ``max_active`` run (:489-511), prefills each prompt whole and alone (:740-844),
+then decodes one token per live sequence per step in one batch (:650-669); it samples from the
+previous step's logits at the top of the loop (:543-566); a sequence finishes on its token
+budget, on EOS (the EOS token is delivered) or at the context length (:548-578); when pages
+run out in mid-decode that sequence ends with ``length`` and keeps what it produced
+(:637-643, test :1123-1151).
+
+This scheduler keeps those rules and adds what the reference leaves open: prompts are cut
+into portions under a token budget per step and share steps with decoding requests, and
+admission waits (instead of rejecting) while slots or pages are short.  Order within a step:
+decoding requests first, then running prompts in admission order, then new admissions.
+
+When pages run out: a request that cannot get pages for its next tokens waits while others
+free pages; if nobody can run, the request admitted last is preempted — its pages and slot
+are given back and it returns to the head of the queue with its produced tokens appended to
+its prompt, to be recomputed; a request that cannot run even alone on an empty cache ends
+with ``length`` and keeps what it produced.
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Optional
+
+from ..errors import RequestError
+from ..sampling import SamplingParams, Xorshift64
+from .step import StepEntry
+
+FINISH_STOP = "stop"        # sampled the EOS token
+FINISH_LENGTH = "length"    # token budget, context length, or the cache cannot hold it
+FINISH_ABORTED = "aborted"
+
+
+@dataclass
+class Request:
+    rid: object
+    prompt: list
+    max_tokens: int
+    params: SamplingParams = field(default_factory=SamplingParams)
+    eos_token_id: Optional[int] = None
+    output: list = field(default_factory=list)
+    finish_reason: Optional[str] = None
+    slot: Optional[int] = None
+    computed: int = 0            # tokens of prompt + output that are in the cache
+    preemptions: int = 0
+    rng: Optional[Xorshift64] = None
+    order: int = 0
+
+    @property
+    def tokens(self):
+        return self.prompt + self.output
+
+    @property
+    def finished(self):
+        return self.finish_reason is not None
+
+
+class Scheduler:
+    """``engine`` offers ``open()``, ``close(slot)``, ``step(entries) -> logits`` and ``cache``;
+    ``sampler.sample(logits, params, rngs, histories) -> tokens``."""
+
+    def __init__(self, engine, sampler, max_step_tokens=2048, max_active=None, context_length=None):
+        self.engine = engine
+        self.sampler = sampler
+        self.max_step_tokens = int(max_step_tokens)
+        self.max_active = int(max_active or engine.cache.num_slots)
+        self.context_length = int(context_length or engine.cache.max_positions)
+        self.waiting = deque()
+        self.running = []
+        self.finished = []
+        self._order = 0
+        self.counters = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0}
+        self.step_log = deque(maxlen=4096)   # per step: wall seconds, rows, bytes copied each way
+
+    # ---- submission -------------------------------------------------------------------------------
+
+    def add(self, request):
+        """Queue a request.  An empty prompt or one longer than the context is refused at once
+        (the reference drops them with ``Incomplete``, src/server/engine.rs:752-754)."""
+        if len(request.prompt) == 0:
+            raise RequestError("empty prompt")
+        if len(request.prompt) > self.context_length:
+            raise RequestError(f"prompt of {len(request.prompt)} tokens exceeds the context length "
+                               f"{self.context_length}")
+        request.params.validate()
+        if request.max_tokens <= 0:
+            request.finish_reason = FINISH_LENGTH
+            self.finished.append(request)
+            return
+        if request.rng is None:
+            request.rng = Xorshift64(request.params.seed)
+        request.order = self._order
+        self._order += 1
+        self.waiting.append(request)
+
+    @property
+    def idle(self):
+        return not self.waiting and not self.running
+
+    # ---- planning ---------------------------------------------------------------------------------
+
+    def plan(self):
+        """Decide the next step: a list of (request, number of tokens).  Admits waiting requests
+        (taking slots) but takes no pages; ``engine.step`` reserves them all-or-nothing, and the
+        plan only holds rows that the cache can serve together."""
+        cache = self.engine.cache
+        budget = self.max_step_tokens
+        rows = []
+
+        def fits(req, n):
+            return cache.pages_short([(r.slot, k) for r, k in rows] + [(req.slot, n)]) is None
+
+        decoding = [r for r in self.running if r.computed == len(r.tokens) - 1 and r.output]
+        prefilling = [r for r in self.running if r not in decoding]
+        for r in decoding:
+            if budget >= 1 and fits(r, 1):
+                rows.append((r, 1))
+                budget -= 1
+        for r in prefilling:
+            n = min(len(r.tokens) - r.computed, budget)
+            if n > 0 and fits(r, n):   # a portion that does not fit waits for pages
+                rows.append((r, n))
+                budget -= n
+        while (self.waiting and budget > 0 and len(self.running) < self.max_active
+               and cache.free_slots > 0):
+            r = self.waiting[0]
+            n = min(len(r.tokens) - r.computed, budget)
+            r.slot = self.engine.open()
+            if not fits(r, n):
+                self.engine.close(r.slot)
+                r.slot = None
+                break
+            self.waiting.popleft()
+            self.running.append(r)
+            rows.append((r, n))
+            budget -= n
+        return rows
+
+    def _preempt_or_finish(self):
+        """Nobody can run.  Free the request admitted last; if it is alone on an empty cache it
+        can never run: end it with ``length``."""
+        if not self.running:
+            r = self.waiting.popleft()   # cannot even be admitted alone
+            self._finish(r, FINISH_LENGTH)
+            return
+        victim = max(self.running, key=lambda r: r.order)
+        alone = len(self.running) == 1
+        self.running.remove(victim)
+        self.engine.close(victim.slot)
+        victim.slot = None
+        victim.computed = 0
+        if alone:
+            self._finish(victim, FINISH_LENGTH)
+        else:
+            victim.preemptions += 1
+            self.counters["preemptions"] += 1
+            self.waiting.appendleft(victim)
+
+    def _finish(self, r, reason):
+        r.finish_reason = reason
+        if r.slot is not None:
+            self.engine.close(r.slot)
+            r.slot = None
+        if r in self.running:
+            self.running.remove(r)
+        self.finished.append(r)
+
+    # ---- one step ---------------------------------------------------------------------------------
+
+    def step(self):
+        """Plan, run and sample one step.  Returns the requests that finished in it."""
+        done_before = len(self.finished)
+        rows = self.plan()
+        while not rows and not self.idle:
+            self._preempt_or_finish()
+            rows = self.plan()
+        if not rows:
+            return self.finished[done_before:]
+        t_start = time.perf_counter()
+        entries, sampled = [], []
+        n_decode = n_prefill = 0
+        for r, n in rows:
+            toks = r.tokens[r.computed:r.computed + n]
+            last = r.computed + n == len(r.tokens)
+            entries.append(StepEntry(r.slot, toks, [n - 1] if last else []))
+            if last:
+                sampled.append(r)
+            if r.output and n == 1 and last:
+                n_decode += 1
+            else:
+                n_prefill += n
+        logits = self.engine.step(entries)
+        self.counters["steps"] += 1
+        self.counters["decode_tokens"] += n_decode
+        self.counters["prefill_tokens"] += n_prefill
+        for r, n in rows:
+            r.computed += n
+        if sampled:
+            tokens = self.sampler.sample(logits, [r.params for r in sampled], [r.rng for r in sampled],
+                                         [r.tokens for r in sampled])
+            for r, tok in zip(sampled, tokens):
+                r.output.append(int(tok))
+                # the reference's order of checks (src/server/engine.rs:548-578)
+                if r.eos_token_id is not None and tok == r.eos_token_id:
+                    self._finish(r, FINISH_STOP)
+                elif len(r.output) >= r.max_tokens:
+                    self._finish(r, FINISH_LENGTH)
+                elif len(r.tokens) >= self.context_length:
+                    self._finish(r, FINISH_LENGTH)
+        self.step_log.append({"seconds": time.perf_counter() - t_start, "decode_rows": n_decode,
+                              "prefill_tokens": n_prefill,
+                              "h2d_bytes": getattr(self.engine, "last_h2d_bytes", 0),
+                              "d2h_bytes": 4 * len(sampled) * (1 if all(r.params.greedy for r in sampled) else 2)})
+        return self.finished[done_before:]
+
+    def run(self):
+        """Step until every queued request has finished; returns them in finishing order."""
+        start = len(self.finished)
+        while not self.idle:
+            self.step()
+        return self.finished[start:]
+
+    def abort(self, request):
+        if request in self.waiting:
+            self.waiting.remove(request)
+        self._finish(request, FINISH_ABORTED)

@@ -87,6 +87,7 @@ class StepContext:
         for g, t in enumerate(tables):
             pack[offs[7 + g]:offs[7 + g] + t.size] = t.reshape(-1)
         dev = meta_dev(pack, total)
+        self.h2d_bytes = total * 4
         cut = lambda k, size: dev[offs[k]:offs[k] + size]
         self.token_ids = cut(0, T)
         self.positions = cut(1, T)
@@ -121,6 +122,7 @@ class Engine:
         self._staging_next = 0
         self.steps = 0
         self.tokens_run = 0
+        self.last_h2d_bytes = 0
 
     # ---- request slots ----------------------------------------------------------------------------
 
@@ -194,4 +196,5 @@ class Engine:
         self.cache.advance(rows)
         self.steps += 1
         self.tokens_run += ctx.num_tokens
+        self.last_h2d_bytes = ctx.h2d_bytes
         return logits
