@@ -28,8 +28,9 @@ NVCC_FLAGS = ARCH_FLAGS + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPI
 
 LIBRARIES = {
     "core": ["elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu"],
+    "tensor": ["gemm_tcgen05.cu"],
 }
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "tcgen05.cuh"]
 
 _loaded = {}
 _lock = threading.Lock()

@@ -1,0 +1,333 @@
+// out[tokens, features] = X[tokens, K] * W[features, K]^T in bfloat16 on the 5th-generation
+// tensor cores (tcgen05.mma, accumulators in tensor memory, operands staged by TMA).
+//
+// The product is computed transposed: the weight tile is the 128-row M operand and the tokens
+// are the N operand (16..256 wide), so one kernel serves a decode step with a handful of
+// tokens and a prefill with thousands, and the weight matrix is always streamed in full
+// 128-row tiles at HBM speed.  (The reference's batched matvec keeps the same [rows, batch]
+// orientation, src/tensor/quantized.rs:278-337.)  Each accumulator lane is one output
+// feature, each column one token; a lane's K-loop order is fixed by K and the split factor
+// alone, never by which tokens share the launch.
+//
+// Roles in a block of 192 threads: warp 0 issues TMA loads into a ring of shared-memory
+// stages, warp 1 allocates tensor memory and issues the MMAs, warps 2..5 read the accumulator
+// back and write the result.  When a launch has too few tiles to fill the GPU the K range is
+// split over blockIdx.z; partial tiles go to a workspace and the block that arrives last at
+// the tile's counter adds them in split order (no spinning, deterministic) and resets the
+// counter.  Epilogues: soft cap (output head), or with two weight tiles per stage
+// (gate rows and up rows of the same features) act(gate) * up written as bfloat16.
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace glint {
+
+constexpr int GEMM_BM = 128;      // weight rows (output features) per tile
+constexpr int GEMM_BK = 64;       // K elements per stage: 128 bytes, one swizzle atom
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_MAX_STAGES = 8;
+constexpr int A_STAGE_BYTES = GEMM_BM * GEMM_BK * 2;
+
+struct GemmParams {
+  int M, N, K;          // tokens, output features, reduction length
+  int BN;               // tokens per tile
+  int stages;
+  int splits, kb_per_split, total_kb;
+  int dual_offset;      // row offset of the second weight tile (dual kernels)
+  int act;              // activation of the dual epilogue
+  float cap;            // soft cap of the plain epilogue (<= 0: none)
+  int out_bf16;
+  void* out;
+  float* workspace;
+  int* counters;
+  int* status;
+};
+
+struct GemmShared {
+  uint64_t full[GEMM_MAX_STAGES];
+  uint64_t empty[GEMM_MAX_STAGES];
+  uint64_t tmem_full;
+  uint32_t tmem_base;
+  int abort_flag;
+  int is_last;
+  int epilogue_ok;
+};
+
+template <bool DUAL>
+__device__ __forceinline__ void store_result(const GemmParams& p, int f, int t, float a, float b) {
+  if (f >= p.N || t >= p.M) return;
+  float y;
+  if (DUAL) {
+    const float g = p.act == 0 ? gelu_tanh(a) : a * (1.0f / (1.0f + expf(-a)));
+    y = g * b;
+  } else {
+    y = softcap(a, p.cap);
+  }
+  if (p.out_bf16)
+    reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.N + f] = __float2bfloat16_rn(y);
+  else
+    reinterpret_cast<float*>(p.out)[(size_t)t * p.N + f] = y;
+}
+
+template <bool DUAL>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int b_stage_bytes = p.BN * GEMM_BK * 2;
+  const int stage_bytes = A_STAGE_BYTES * (DUAL ? 2 : 1) + b_stage_bytes;
+  GemmShared* sh = reinterpret_cast<GemmShared*>(smem + (size_t)p.stages * stage_bytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * GEMM_BM;
+  const int m0 = blockIdx.y * p.BN;
+  const int split = blockIdx.z;
+  const int kb_begin = split * p.kb_per_split;
+  const int kb_end = min(p.total_kb, kb_begin + p.kb_per_split);
+  const int n_kb = kb_end - kb_begin;
+  const uint32_t tmem_cols_used = p.BN * (DUAL ? 2 : 1);
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < tmem_cols_used) tmem_cols <<= 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      tc::mbar_init(&sh->full[s], 1);
+      tc::mbar_init(&sh->empty[s], 1);
+    }
+    tc::mbar_init(&sh->tmem_full, 1);
+    sh->abort_flag = 0;
+    sh->is_last = 0;
+    tc::fence_barrier_init();
+    tc::tma_prefetch_desc(&map_w);
+    tc::tma_prefetch_desc(&map_x);
+  }
+  if (warp == 1) tc::tmem_alloc(&sh->tmem_base, tmem_cols);
+  tc::fence_before_thread_sync();
+  __syncthreads();
+  tc::fence_after_thread_sync();
+  const uint32_t tmem_base = sh->tmem_base;
+  volatile int* abort_flag = &sh->abort_flag;
+
+  if (warp == 0) {
+    // ---- producer: TMA loads of the weight tile(s) and the token tile --------------------------
+    if (lane == 0) {
+      for (int i = 0; i < n_kb; ++i) {
+        const int s = i % p.stages;
+        const uint32_t round = i / p.stages;
+        if (!tc::mbar_wait(&sh->empty[s], (round & 1) ^ 1, abort_flag)) break;
+        uint8_t* stage = smem + (size_t)s * stage_bytes;
+        tc::mbar_expect_tx(&sh->full[s], stage_bytes);
+        const int k = (kb_begin + i) * GEMM_BK;
+        tc::tma_load_2d(stage, &map_w, &sh->full[s], k, n0);
+        if (DUAL) tc::tma_load_2d(stage + A_STAGE_BYTES, &map_w, &sh->full[s], k, n0 + p.dual_offset);
+        tc::tma_load_2d(stage + A_STAGE_BYTES * (DUAL ? 2 : 1), &map_x, &sh->full[s], k, m0);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----------------------------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = tc::idesc_bf16_f32(GEMM_BM, p.BN);
+      bool ok = true;
+      for (int i = 0; i < n_kb && ok; ++i) {
+        const int s = i % p.stages;
+        const uint32_t round = i / p.stages;
+        ok = tc::mbar_wait(&sh->full[s], round & 1, abort_flag);
+        if (!ok) break;
+        tc::fence_after_thread_sync();
+        const uint32_t a_addr = tc::smem_u32(smem + (size_t)s * stage_bytes);
+        const uint32_t b_addr = a_addr + A_STAGE_BYTES * (DUAL ? 2 : 1);
+#pragma unroll
+        for (int k = 0; k < GEMM_BK / 16; ++k) {
+          const uint64_t db = tc::smem_desc_k_sw128(b_addr + k * 32);
+          const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+          tc::mma_bf16_ss(tmem_base, tc::smem_desc_k_sw128(a_addr + k * 32), db, idesc, acc);
+          if (DUAL)
+            tc::mma_bf16_ss(tmem_base + p.BN, tc::smem_desc_k_sw128(a_addr + A_STAGE_BYTES + k * 32), db, idesc,
+                            acc);
+        }
+        tc::mma_commit(&sh->empty[s]);   // the stage is free once these MMAs have read it
+      }
+      tc::mma_commit(&sh->tmem_full);    // the accumulator is complete
+    }
+  } else {
+    // ---- epilogue: 4 warps, each owns the 32 accumulator lanes of its quarter --------------------
+    const int q = warp & 3;
+    const int f = n0 + q * 32 + lane;              // this thread's output feature
+    tc::mbar_wait(&sh->tmem_full, 0, abort_flag);
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (threadIdx.x == 64) sh->epilogue_ok = !*abort_flag;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const bool ok = sh->epilogue_ok != 0;   // one thread decides, so all 128 take the same branch
+    tc::fence_after_thread_sync();
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+    const int halves = DUAL ? 2 : 1;
+    if (ok && p.splits == 1) {
+      for (int c0 = 0; c0 < p.BN; c0 += 16) {
+        uint32_t a[16], b[16];
+        tc::tmem_ld_16(lane_addr + c0, a);
+        if (DUAL) tc::tmem_ld_16(lane_addr + p.BN + c0, b);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          store_result<DUAL>(p, f, m0 + c0 + j, __uint_as_float(a[j]), DUAL ? __uint_as_float(b[j]) : 0.f);
+      }
+    } else if (ok) {
+      // partial sums of this split: workspace[tile][split][half][column][row]
+      float* mine = p.workspace + ((size_t)(tile_id * p.splits + split) * halves) * p.BN * GEMM_BM;
+      for (int c0 = 0; c0 < p.BN * halves; c0 += 16) {
+        uint32_t a[16];
+        tc::tmem_ld_16(lane_addr + c0, a);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) mine[(size_t)(c0 + j) * GEMM_BM + q * 32 + lane] = __uint_as_float(a[j]);
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        const int prev = atomicAdd(&p.counters[tile_id], 1);
+        sh->is_last = (prev == p.splits - 1);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (sh->is_last) {
+        __threadfence();
+        const float* base = p.workspace + ((size_t)tile_id * p.splits * halves) * p.BN * GEMM_BM;
+        const size_t split_stride = (size_t)halves * p.BN * GEMM_BM;
+        for (int c = 0; c < p.BN; ++c) {
+          float a = 0.f, b = 0.f;
+          for (int s = 0; s < p.splits; ++s) {
+            a += __ldcg(base + s * split_stride + (size_t)c * GEMM_BM + q * 32 + lane);
+            if (DUAL) b += __ldcg(base + s * split_stride + (size_t)(p.BN + c) * GEMM_BM + q * 32 + lane);
+          }
+          store_result<DUAL>(p, f, m0 + c, a, b);
+        }
+        if (threadIdx.x == 64) p.counters[tile_id] = 0;   // ready for the next launch on this stream
+      }
+    }
+  }
+  tc::fence_before_thread_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc::fence_after_thread_sync();
+    tc::tmem_dealloc(tmem_base, tmem_cols);
+  }
+  if (threadIdx.x == 0 && sh->abort_flag) atomicExch(p.status, 4);
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// A [rows, K] bf16 row-major matrix viewed as tiles of box_rows x 64 with the 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return GLINT_ERR_BAD_ARG;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)GEMM_BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? GLINT_OK : GLINT_ERR_BAD_ARG;
+}
+
+}  // namespace glint
+
+using namespace glint;
+
+// Sizes this kernel takes: K a multiple of 8 (rows must start on 16-byte boundaries for TMA) and
+// 16-byte aligned bases.  Everything else (any M, N, K tail) is handled by zero-filled tiles.
+GLINT_API int glint_gemm_tcgen05_supported(long long M, long long N, long long K) {
+  return (M > 0 && N > 0 && K > 0 && K % 8 == 0) ? 1 : 0;
+}
+
+GLINT_API long long glint_gemm_workspace_bytes() { return 16ll << 20; }
+GLINT_API int glint_gemm_counter_count() { return 8192; }
+
+// x: [M, K] bf16; w: [N (or 2N rows when dual), K] bf16; out: [M, N] float32 or bf16.
+// dual != 0: out = act(x w[0:N]^T) * (x w[dual_offset : dual_offset+N]^T), written as bf16.
+// workspace: glint_gemm_workspace_bytes() bytes; counters: glint_gemm_counter_count() zeroed ints.
+GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int out_bf16, int M, int N, int K,
+                                 long long w_rows, float cap, int dual, int dual_offset, int act,
+                                 float* workspace, int* counters, int* status, int force_splits,
+                                 cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return GLINT_OK;
+  if (!glint_gemm_tcgen05_supported(M, N, K)) return GLINT_ERR_UNSUPPORTED_SIZE;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return GLINT_ERR_UNSUPPORTED_SIZE;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  const int m_tiles_256 = (M + 255) / 256;
+  int bn = ((M + m_tiles_256 - 1) / m_tiles_256 + 15) / 16 * 16;
+  if (dual && bn > 256) bn = 256;
+  p.BN = bn;
+  const int m_tiles = (M + bn - 1) / bn;
+  const int n_tiles = (N + GEMM_BM - 1) / GEMM_BM;
+  const int stage_bytes = A_STAGE_BYTES * (dual ? 2 : 1) + bn * GEMM_BK * 2;
+  int stages = (227 * 1024 - 1024 - (int)sizeof(GemmShared) - 256) / stage_bytes;
+  if (stages > GEMM_MAX_STAGES) stages = GEMM_MAX_STAGES;
+  if (stages < 2) return GLINT_ERR_UNSUPPORTED_SIZE;
+  p.stages = stages;
+  p.total_kb = (K + GEMM_BK - 1) / GEMM_BK;
+  const int tiles = m_tiles * n_tiles;
+  int splits = 1;
+  if (force_splits > 0) {
+    splits = force_splits;
+  } else if (tiles < 100) {
+    splits = (148 + tiles - 1) / tiles;
+    const int max_by_k = p.total_kb / 4 > 0 ? p.total_kb / 4 : 1;
+    if (splits > max_by_k) splits = max_by_k;
+    if (splits > 16) splits = 16;
+  }
+  if (splits > p.total_kb) splits = p.total_kb;
+  p.kb_per_split = (p.total_kb + splits - 1) / splits;
+  splits = (p.total_kb + p.kb_per_split - 1) / p.kb_per_split;
+  const long long ws_need = (long long)tiles * splits * (dual ? 2 : 1) * bn * GEMM_BM * 4;
+  if (splits > 1 && (ws_need > glint_gemm_workspace_bytes() || tiles > glint_gemm_counter_count() ||
+                     !workspace || !counters)) {
+    splits = 1;
+    p.kb_per_split = p.total_kb;
+  }
+  p.splits = splits;
+  p.dual_offset = dual_offset;
+  p.act = act;
+  p.cap = cap;
+  p.out_bf16 = out_bf16;
+  p.out = out;
+  p.workspace = workspace;
+  p.counters = counters;
+  p.status = status;
+
+  CUtensorMap map_w, map_x;
+  int rc = make_map(&map_w, w, w_rows, K, GEMM_BM);
+  if (rc != GLINT_OK) return rc;
+  rc = make_map(&map_x, x, M, K, bn);
+  if (rc != GLINT_OK) return rc;
+  const int smem_bytes = stages * stage_bytes + (int)sizeof(GemmShared) + 1024;
+  dim3 grid(n_tiles, m_tiles, splits);
+  cudaError_t e;
+  if (dual) {
+    e = cudaFuncSetAttribute(gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return (int)e;
+    gemm_tcgen05_kernel<true><<<grid, GEMM_THREADS, smem_bytes, stream>>>(map_w, map_x, p);
+  } else {
+    e = cudaFuncSetAttribute(gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return (int)e;
+    gemm_tcgen05_kernel<false><<<grid, GEMM_THREADS, smem_bytes, stream>>>(map_w, map_x, p);
+  }
+  return (int)cudaGetLastError();
+}
