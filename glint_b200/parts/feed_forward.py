@@ -39,9 +39,16 @@ class GatedFeedForward(Part):
     def forward(self, normed, ctx):
         rt = self.rt
         T = normed.shape[0]
-        gu = linear(rt, normed, self.w_gate_up)
         act = torch.empty((T, self.intermediate_size), dtype=rt.dtype, device=normed.device)
-        ops.gated_act(gu, act, self.activation)
+        fused = False
+        if rt.tensor_cores:
+            from .. import ops_tensor
+            if ops_tensor.gemm_supported(T, self.intermediate_size, self.hidden_size):
+                ops_tensor.gemm_gated(normed, self.w_gate_up, act, self.activation, rt.status)
+                fused = True
+        if not fused:
+            gu = linear(rt, normed, self.w_gate_up)
+            ops.gated_act(gu, act, self.activation)
         return linear(rt, act, self.w_down)
 
     def parameter_bytes(self):

@@ -19,7 +19,7 @@ def linear(rt, a, w, cap=0.0, out=None):
     if rt.tensor_cores and w.dtype == torch.bfloat16:
         from .. import ops_tensor
         if ops_tensor.gemm_supported(M, N, w.shape[1]):
-            ops_tensor.gemm(a, w, out, cap)
+            ops_tensor.gemm(a, w, out, cap, rt.status)
             return out
     ops.gemm_plain(a, w, out, cap)
     return out
