@@ -12,6 +12,8 @@ _P, _I, _F, _L = c_void_p, c_int, c_float, c_longlong
 
 _SIGNATURES = {
     "glint_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _L, _F, _I, _I, _I, _P, _P, _P, _I, _P],
+    "glint_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P],
+    "glint_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
 }
 
 _lib = None
@@ -73,4 +75,67 @@ def gemm_gated(a, w_gate_up, out, activation, status=None, force_splits=0):
 
 
 def attention_supported(nh, nkv, hd, page_size):
-    return False
+    """The bfloat16 attention kernels take head sizes in steps of 8 up to 512 (single tokens) and
+    in steps of 16 up to 256 with at most 64 query heads per kv head (prompt portions)."""
+    return nkv > 0 and nh % nkv == 0 and hd % 8 == 0 and 0 < hd <= 512
+
+
+def prefill_supported(nh, nkv, hd):
+    return nkv > 0 and nh % nkv == 0 and nh // nkv <= 64 and hd % 16 == 0 and 16 <= hd <= 256
+
+
+_partials = {}
+
+
+def decode_splits(tokens, nkv, max_context):
+    """Enough blocks to fill the GPU, each with at least 64 keys."""
+    want = -(-444 // max(1, tokens * nkv))
+    return max(1, min(want, max_context // 64, 64))
+
+
+def attention_decode(q, k_pool, v_pool, positions, token_seq, block_table, out, nh, nkv, hd, page_size, num_pages,
+                     multiplier, cap, window, status, splits):
+    """Every token attends alone (split over its keys): right for any batch, meant for single tokens."""
+    T = q.shape[0]
+    ops.require(q, torch.bfloat16, "q"); ops.require(k_pool, torch.bfloat16, "k_pool")
+    ops.require(v_pool, torch.bfloat16, "v_pool"); ops.require(out, torch.bfloat16, "out")
+    partial = None
+    if splits > 1:
+        need = T * nh * splits * (hd + 2)
+        key = str(q.device)
+        partial = _partials.get(key)
+        if partial is None or partial.numel() < need:
+            partial = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device)
+            _partials[key] = partial
+    ops.check(lib().glint_attention_decode(ops.ptr(q), ops.ptr(k_pool), ops.ptr(v_pool), ops.ptr(positions),
+                                           ops.ptr(token_seq), ops.ptr(block_table), block_table.shape[1],
+                                           ops.ptr(out), ops.ptr(partial), T, nh, nkv, hd, page_size, num_pages,
+                                           multiplier, cap or 0.0, window or 0, splits, ops.ptr(status),
+                                           ops.stream()), "attention_decode")
+    if splits > 1:
+        ops.launch_count += 1
+
+
+def attention_prefill(q, k_pool, v_pool, cu_seqlens, seq_start, block_table, out, n_seqs, max_q_len, nh, nkv, hd,
+                      page_size, num_pages, multiplier, cap, window, status):
+    """Flash attention of prompt portions (any mix of lengths, single tokens included)."""
+    ops.require(q, torch.bfloat16, "q"); ops.require(k_pool, torch.bfloat16, "k_pool")
+    ops.require(v_pool, torch.bfloat16, "v_pool"); ops.require(out, torch.bfloat16, "out")
+    ops.check(lib().glint_attention_prefill(ops.ptr(q), ops.ptr(k_pool), ops.ptr(v_pool), ops.ptr(cu_seqlens),
+                                            ops.ptr(seq_start), ops.ptr(block_table), block_table.shape[1],
+                                            ops.ptr(out), n_seqs, max_q_len, nh, nkv, hd, page_size, num_pages,
+                                            multiplier, cap or 0.0, window or 0, ops.ptr(status), ops.stream()),
+              "attention_prefill")
+
+
+def attention(q, view, ctx, out, nh, nkv, hd, multiplier, cap, window, status):
+    """Route a step's attention: single tokens to the split kernel, portions to the tiled one."""
+    table = ctx.block_table(view.group)
+    if ctx.max_seq_len > 1 and prefill_supported(nh, nkv, hd):
+        attention_prefill(q, view.k, view.v, ctx.cu_seqlens, ctx.seq_start, table, out, ctx.num_seqs,
+                          ctx.max_seq_len, nh, nkv, hd, view.page_size, view.num_pages, multiplier, cap, window,
+                          status)
+    else:
+        splits = decode_splits(ctx.num_tokens, nkv, ctx.max_context)
+        attention_decode(q, view.k, view.v, ctx.positions, ctx.token_seq, table, out, nh, nkv, hd, view.page_size,
+                         view.num_pages, multiplier, cap, window, status, splits)

@@ -90,3 +90,135 @@ def test_gemm_gated_against_float32(M, I, K, act):
     torch.cuda.synchronize()
     err = (out.float() - want).abs().max().item()
     assert err <= 1e-2 * max(1.0, want.abs().max().item()), err
+
+
+# ---- attention over a paged cache -----------------------------------------------------------------
+
+def _paged_case(seq_lens_before, seq_lens_new, nkv, hd, page_size, dtype, seed, hot=None):
+    """Random keys/values for every request laid into shuffled pages.  Returns the pools, the block
+    table [requests, max_pages], and the dense per-request K, V [len, nkv, hd]."""
+    g = torch.Generator().manual_seed(seed)
+    totals = [a + b for a, b in zip(seq_lens_before, seq_lens_new)]
+    max_pages = max(-(-t // page_size) for t in totals) + 1
+    n_pages = sum(-(-t // page_size) for t in totals) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    k_pool = torch.full((n_pages, nkv, page_size, hd), float("nan"))
+    v_pool = torch.full((n_pages, nkv, page_size, hd), float("nan"))
+    table = torch.full((len(totals), max_pages), -1, dtype=torch.int32)
+    dense = []
+    for s, total in enumerate(totals):
+        k = torch.randn(total, nkv, hd, generator=g).to(dtype).float()
+        v = torch.randn(total, nkv, hd, generator=g).to(dtype).float()
+        if hot is not None and hot[0] == s:      # one far key that must win the softmax
+            k[hot[1]] *= 6.0
+        dense.append((k, v))
+        for p in range(-(-total // page_size)):
+            page = perm.pop()
+            table[s, p] = page
+            lo, hi = p * page_size, min(total, (p + 1) * page_size)
+            k_pool[page, :, :hi - lo] = k[lo:hi].transpose(0, 1)
+            v_pool[page, :, :hi - lo] = v[lo:hi].transpose(0, 1)
+    return k_pool.to(dtype).to(DEV), v_pool.to(dtype).to(DEV), table.to(DEV), dense
+
+
+def _attention_reference(q, dense, seq_of_token, positions, nh, nkv, multiplier, cap, window):
+    out = torch.zeros_like(q)
+    G = nh // nkv
+    for t in range(q.shape[0]):
+        k, v = dense[seq_of_token[t]]
+        pos = positions[t]
+        lo = max(0, pos - window + 1) if window else 0
+        for h in range(nh):
+            s = (k[lo:pos + 1, h // G] @ q[t, h]) * multiplier
+            if cap:
+                s = cap * torch.tanh(s / cap)
+            out[t, h] = torch.softmax(s, 0) @ v[lo:pos + 1, h // G]
+    return out
+
+
+ATT_CASES = [
+    # nh, nkv, hd, page, before,            new,             window, cap
+    (8, 4, 256, 16, [300, 0, 1023, 77], [1, 1, 1, 1], None, 50.0),
+    (8, 4, 256, 16, [300, 0, 1023, 77], [1, 1, 1, 1], 128, 50.0),
+    (6, 1, 32, 16, [0, 40, 5], [33, 2, 70], 8, 20.0),
+    (6, 2, 48, 16, [10, 0, 200], [50, 129, 1], 40, None),
+    (4, 2, 16, 16, [0, 17], [64, 3], 16, 50.0),
+    (32, 16, 128, 16, [500, 0], [1, 130], 100, 30.0),
+    (3, 3, 80, 32, [90], [45], None, 10.0),
+    (16, 1, 64, 16, [31], [20], None, None),
+]
+
+
+@pytest.mark.parametrize("kernel", ["plain32", "plain16", "decode", "prefill"])
+@pytest.mark.parametrize("case", range(len(ATT_CASES)))
+def test_attention_kernels_against_float32(case, kernel):
+    from glint_b200 import ops, ops_tensor
+    nh, nkv, hd, page, before, new, window, cap = ATT_CASES[case]
+    if kernel == "prefill" and not ops_tensor.prefill_supported(nh, nkv, hd):
+        pytest.skip("size outside the tiled kernel's range (the split kernel takes it)")
+    dtype = torch.float32 if kernel == "plain32" else torch.bfloat16
+    k_pool, v_pool, table, dense = _paged_case(before, new, nkv, hd, page, dtype, seed=case)
+    seq_of_token, positions = [], []
+    for s, (b, n) in enumerate(zip(before, new)):
+        seq_of_token += [s] * n
+        positions += list(range(b, b + n))
+    T = len(positions)
+    torch.manual_seed(case)
+    q = (torch.randn(T, nh, hd) * 1.5).to(dtype)
+    mult = 1.0 / math.sqrt(hd)
+    want = _attention_reference(q.float(), dense, seq_of_token, positions, nh, nkv, mult, cap, window)
+    qd = q.reshape(T, nh * hd).to(DEV)
+    out = torch.full_like(qd, float("nan"))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    if kernel.startswith("plain"):
+        ops.attention_plain(qd, k_pool, v_pool, i32(positions), i32(seq_of_token), table, out, nh, nkv, hd, page,
+                            k_pool.shape[0], mult, cap, window, status)
+    elif kernel == "decode":
+        for splits in (1, 3):
+            ops_tensor.attention_decode(qd, k_pool, v_pool, i32(positions), i32(seq_of_token), table, out, nh, nkv,
+                                        hd, page, k_pool.shape[0], mult, cap, window, status, splits)
+            got = out.float().cpu().reshape(T, nh, hd)
+            assert (got - want).abs().max().item() < 0.03, splits
+    else:
+        cu = [0]
+        for n in new:
+            cu.append(cu[-1] + n)
+        ops_tensor.attention_prefill(qd, k_pool, v_pool, i32(cu), i32(before), table, out, len(new), max(new), nh,
+                                     nkv, hd, page, k_pool.shape[0], mult, cap, window, status)
+    got = out.float().cpu().reshape(T, nh, hd)
+    assert int(status.item()) == 0
+    tol = 2e-5 if kernel == "plain32" else 0.03
+    assert (got - want).abs().max().item() < tol, (got - want).abs().max().item()
+
+
+@pytest.mark.parametrize("kernel", ["plain16", "decode", "prefill"])
+def test_attention_finds_one_far_key_among_hundreds(kernel):
+    """One key far back is scaled so that its score stands out: the output must be its value row."""
+    from glint_b200 import ops, ops_tensor
+    nh, nkv, hd, page = 8, 4, 256, 16
+    before, new = [900], [1]
+    hot_pos = 37
+    k_pool, v_pool, table, dense = _paged_case(before, new, nkv, hd, page, torch.bfloat16, seed=9)
+    k, v = dense[0]
+    q = torch.zeros(1, nh, hd)
+    for h in range(nh):
+        q[0, h] = k[hot_pos, h // 2] * 4.0          # aligned with the far key: its score dominates
+    q = q.to(torch.bfloat16)
+    want = _attention_reference(q.float(), dense, [0], [900], nh, nkv, 1 / 16.0, None, None)
+    assert (want[0, 0] - v[hot_pos, 0]).abs().max() < 1e-2       # the case does what it says
+    qd = q.reshape(1, nh * hd).to(DEV)
+    out = torch.empty_like(qd)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    if kernel == "plain16":
+        ops.attention_plain(qd, k_pool, v_pool, i32([900]), i32([0]), table, out, nh, nkv, hd, page, k_pool.shape[0],
+                            1 / 16.0, None, None, status)
+    elif kernel == "decode":
+        ops_tensor.attention_decode(qd, k_pool, v_pool, i32([900]), i32([0]), table, out, nh, nkv, hd, page,
+                                    k_pool.shape[0], 1 / 16.0, None, None, status, 7)
+    else:
+        ops_tensor.attention_prefill(qd, k_pool, v_pool, i32([0, 1]), i32([900]), table, out, 1, 1, nh, nkv, hd, page,
+                                     k_pool.shape[0], 1 / 16.0, None, None, status)
+    got = out.float().cpu().reshape(1, nh, hd)
+    assert (got - want).abs().max().item() < 0.03
