@@ -36,6 +36,6 @@ def pages_for_tokens(tokens, page_size):
     return max(1, (int(tokens) + page_size - 1) // page_size)
 
 
-def build_engine(model, max_tokens, num_slots=64, page_size=16):
+def build_engine(model, max_tokens, num_slots=64, page_size=16, use_graphs=True):
     """An engine whose every cache group can hold ``max_tokens`` tokens in all."""
-    return Engine(model, pages_for_tokens(max_tokens, page_size), num_slots, page_size)
+    return Engine(model, pages_for_tokens(max_tokens, page_size), num_slots, page_size, use_graphs)

@@ -109,8 +109,11 @@ class StepContext:
 class Engine:
     """A model, its cache and the step function.  Requests are known here only by slot."""
 
-    def __init__(self, model, num_pages, num_slots=64, page_size=16):
+    def __init__(self, model, num_pages, num_slots=64, page_size=16, use_graphs=True):
         self.model = model
+        self.use_graphs = use_graphs
+        self._graphs = {}
+        self._graph_pool = None
         self.rt = model.rt
         needs, cache_of = model.cache_needs()
         self.cache = CacheManager(needs, cache_of, num_slots, num_pages, page_size, model.spec.max_positions,
@@ -155,7 +158,10 @@ class Engine:
 
     def _upload(self, pack, total):
         if self._meta_dev is None or self._meta_dev.numel() < total:
-            self._meta_dev = torch.empty(max(total * 2, 1 << 16), dtype=torch.int32, device=self.rt.device)
+            groups = len(self.cache.groups)
+            roomy = 3 * 16384 + self.cache.num_slots * (8 + groups * max([g.max_pages for g in self.cache.groups] or [0]))
+            self._meta_dev = torch.empty(max(total * 2, roomy), dtype=torch.int32, device=self.rt.device)
+            self._graphs.clear()      # captured launches point into the old buffer
         k = self._staging_current
         self._meta_dev[:total].copy_(self._staging[k][:total], non_blocking=True)
         ev = self._staging_events[k] or torch.cuda.Event()
@@ -183,6 +189,7 @@ class Engine:
     def step(self, entries):
         """Run the entries as one batch.  Returns float32 logits [wanted rows, vocab] on the
         device, in the order of the entries and of each ``want`` (``None`` if nothing is wanted).
+        The tensor is valid until the next step.
 
         Raises ``PagePoolExhausted`` before anything ran when the cache cannot hold the new
         tokens; the cache is then unchanged apart from pages that a window had already passed.
@@ -192,9 +199,53 @@ class Engine:
         self.cache.reserve(rows)
         with torch.cuda.device(self.rt.device):
             ctx = StepContext(self.cache, entries, self._upload, self._stage)
-            logits = self.model.forward(ctx, self.cache)
+            key = self._graph_key(entries, ctx)
+            if key is None:
+                logits = self.model.forward(ctx, self.cache)
+            else:
+                logits = self._run_graphed(key, ctx)
         self.cache.advance(rows)
         self.steps += 1
         self.tokens_run += ctx.num_tokens
         self.last_h2d_bytes = ctx.h2d_bytes
+        return logits
+
+    # ---- CUDA graphs for decode steps -------------------------------------------------------------
+
+    def _graph_key(self, entries, ctx):
+        """Steps of single tokens with logits wanted for each are launch-bound: they replay a
+        captured graph.  The key holds everything a captured launch depends on beyond the
+        step's device metadata: the number of requests, and the context bucket that sizes the
+        split of the attention kernels."""
+        if not self.use_graphs or not ctx.is_decode:
+            return None
+        if any(list(e.want) != [0] for e in entries):
+            return None
+        bucket = 256
+        while bucket < ctx.max_context:
+            bucket *= 2
+        return (ctx.num_seqs, bucket)
+
+    def _run_graphed(self, key, ctx):
+        ctx.max_context = key[1]          # launches are planned for the bucket, not the exact length
+        entry = self._graphs.get(key)
+        if entry is None:                 # first sight: run eagerly (also warms lazy set-up)
+            self._graphs[key] = "seen"
+            return self.model.forward(ctx, self.cache)
+        if entry == "seen":
+            from .. import ops
+            graph = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize()
+            before = ops.launch_count
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                logits = self.model.forward(ctx, self.cache)
+            if self._graph_pool is None:
+                self._graph_pool = graph.pool()
+            entry = (graph, logits, ops.launch_count - before, self._meta_dev.data_ptr())
+            self._graphs[key] = entry
+        graph, logits, launches, meta_ptr = entry
+        assert meta_ptr == self._meta_dev.data_ptr()
+        graph.replay()
+        from .. import ops
+        ops.launch_count += launches
         return logits
