@@ -1,0 +1,172 @@
+"""Times single kernels at given sizes with CUDA events: ``python -m glint_b200.bench_kernels``.
+
+Each case rotates through enough copies of its large operands that consecutive launches never
+find them in the 126 MB L2; times are medians over the launches after warm-up.  Prints one
+line per case with the achieved GB/s (bytes the kernel has to move) and TFLOP/s.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+import torch
+
+DEV = "cuda:0"
+L2_BYTES = 126 << 20
+
+
+def _time(fn, n_variants, iters=20, warmup=5):
+    """Median microseconds per launch.  The launches of one round over all variants are captured
+    in a CUDA graph, so that the time between the events is device time, not host enqueue time."""
+    for i in range(max(warmup, n_variants)):
+        fn(i % n_variants)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(n_variants):
+            fn(i)
+    graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(max(3, iters // n_variants + 1)):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e3 / n_variants)
+    times.sort()
+    return times[len(times) // 2]
+
+
+def _copies(nbytes):
+    return max(2, int(math.ceil(2.5 * L2_BYTES / max(nbytes, 1))))
+
+
+def bench_gemm(M, N, K, gated=False, splits=0, iters=20):
+    from . import ops_tensor
+    rows = 2 * N if gated else N
+    n = min(_copies(rows * K * 2), 64)
+    ws = [torch.randn(rows, K, device=DEV).to(torch.bfloat16) * 0.05 for _ in range(n)]
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16 if gated else torch.float32)
+    if gated:
+        fn = lambda i: ops_tensor.gemm_gated(x, ws[i], out, "gelu_tanh", force_splits=splits)
+    else:
+        fn = lambda i: ops_tensor.gemm(x, ws[i], out, force_splits=splits)
+    us = _time(fn, n, iters)
+    nbytes = rows * K * 2 + M * K * 2 + out.numel() * out.element_size()
+    flops = 2.0 * M * rows * K
+    return {"kernel": "gemm_gated" if gated else "gemm", "M": M, "N": N, "K": K, "splits": splits, "us": round(us, 2),
+            "GB/s": round(nbytes / us / 1e3, 1), "TFLOP/s": round(flops / us / 1e6, 1)}
+
+
+def bench_attention_decode(batch, context, nh=8, nkv=4, hd=256, page=16, window=None, cap=50.0, splits=None, iters=20):
+    from . import ops_tensor
+    pages_per_seq = (context + page - 1) // page
+    n_pages = batch * pages_per_seq
+    bytes_kv = 2 * batch * context * nkv * hd * 2
+    n = min(_copies(bytes_kv), 16)
+    pools = [(torch.randn(n_pages, nkv, page, hd, device=DEV).to(torch.bfloat16),
+              torch.randn(n_pages, nkv, page, hd, device=DEV).to(torch.bfloat16)) for _ in range(n)]
+    table = torch.arange(n_pages, dtype=torch.int32, device=DEV).view(batch, pages_per_seq)
+    q = torch.randn(batch, nh * hd, device=DEV).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    pos = torch.full((batch,), context - 1, dtype=torch.int32, device=DEV)
+    seq = torch.arange(batch, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    sp = splits or ops_tensor.decode_splits(batch, nkv, context)
+    fn = lambda i: ops_tensor.attention_decode(q, pools[i][0], pools[i][1], pos, seq, table, out, nh, nkv, hd, page,
+                                               n_pages, 1 / 16.0, cap, window, status, sp)
+    us = _time(fn, n, iters)
+    keys = min(context, window) if window else context
+    nbytes = 2 * batch * keys * nkv * hd * 2
+    return {"kernel": "attention_decode", "batch": batch, "context": context, "splits": sp, "us": round(us, 2),
+            "GB/s": round(nbytes / us / 1e3, 1)}
+
+
+def bench_attention_prefill(tokens, before=0, nh=8, nkv=4, hd=256, page=16, window=None, cap=50.0, iters=10):
+    from . import ops_tensor
+    total = before + tokens
+    n_pages = (total + page - 1) // page
+    k = torch.randn(n_pages, nkv, page, hd, device=DEV).to(torch.bfloat16)
+    v = torch.randn(n_pages, nkv, page, hd, device=DEV).to(torch.bfloat16)
+    table = torch.arange(n_pages, dtype=torch.int32, device=DEV).view(1, n_pages)
+    q = torch.randn(tokens, nh * hd, device=DEV).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    cu = torch.tensor([0, tokens], dtype=torch.int32, device=DEV)
+    start = torch.tensor([before], dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    fn = lambda i: ops_tensor.attention_prefill(q, k, v, cu, start, table, out, 1, tokens, nh, nkv, hd, page, n_pages,
+                                                1 / 16.0, cap, window, status)
+    us = _time(fn, 1, iters)
+    keys = sum(min(p + 1, window) if window else p + 1 for p in range(before, total))
+    flops = 4.0 * nh * hd * keys
+    return {"kernel": "attention_prefill", "tokens": tokens, "before": before, "window": window, "us": round(us, 2),
+            "TFLOP/s": round(flops / us / 1e6, 1)}
+
+
+def bench_rows(rows, H=2304, iters=20):
+    from . import ops
+    x = torch.randn(rows, H, device=DEV)
+    y = torch.randn(rows, H, device=DEV)
+    w = torch.randn(H, device=DEV)
+    out = torch.empty(rows, H, device=DEV, dtype=torch.bfloat16)
+    res = []
+    us = _time(lambda i: ops.rmsnorm(x, w, out, 1e-6, 1.0), 8, iters)
+    res.append({"kernel": "rmsnorm", "rows": rows, "H": H, "us": round(us, 2), "GB/s": round(rows * H * 6 / us / 1e3, 1)})
+    us = _time(lambda i: ops.add_rmsnorm(x, y, (w, 1e-6, 1.0), out, (w, 1e-6, 1.0)), 8, iters)
+    res.append({"kernel": "add_rmsnorm", "rows": rows, "H": H, "us": round(us, 2),
+                "GB/s": round(rows * H * 14 / us / 1e3, 1)})
+    return res
+
+
+def gemma2_2b_decode_cases(batch):
+    H, I, V, QKV, Q = 2304, 9216, 256000, 4096, 2048
+    return [("qkv", batch, QKV, H, False), ("o", batch, H, Q, False), ("gate_up", batch, I, H, True),
+            ("down", batch, H, I, False), ("lm_head", batch, V, H, False)]
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("what", choices=["gemm", "gated", "decode-shapes", "prefill-shapes", "attention-decode",
+                                     "attention-prefill", "rows"])
+    ap.add_argument("--m", type=int, default=8)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=2304)
+    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=2176)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--window", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=20)
+    a = ap.parse_args()
+    out = []
+    if a.what == "gemm":
+        out.append(bench_gemm(a.m, a.n, a.k, False, a.splits, a.iters))
+    elif a.what == "gated":
+        out.append(bench_gemm(a.m, a.n, a.k, True, a.splits, a.iters))
+    elif a.what == "decode-shapes":
+        for name, M, N, K, gated in gemma2_2b_decode_cases(a.batch):
+            out.append(dict(bench_gemm(M, N, K, gated, 0, a.iters), name=name))
+        out.append(bench_attention_decode(a.batch, a.context, iters=a.iters))
+        out.extend(bench_rows(a.batch))
+    elif a.what == "prefill-shapes":
+        for name, M, N, K, gated in gemma2_2b_decode_cases(a.tokens)[:4]:
+            out.append(dict(bench_gemm(M, N, K, gated, 0, a.iters), name=name))
+        out.append(bench_attention_prefill(a.tokens, iters=a.iters))
+        out.extend(bench_rows(a.tokens))
+    elif a.what == "attention-decode":
+        out.append(bench_attention_decode(a.batch, a.context, window=a.window or None, splits=a.splits or None,
+                                          iters=a.iters))
+    elif a.what == "attention-prefill":
+        out.append(bench_attention_prefill(a.tokens, window=a.window or None, iters=a.iters))
+    elif a.what == "rows":
+        out.extend(bench_rows(a.batch))
+    for row in out:
+        print(json.dumps(row))
+
+
+if __name__ == "__main__":
+    main()

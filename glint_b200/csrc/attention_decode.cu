@@ -181,25 +181,39 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   }
 }
 
-// out[t, head, :] = sum over splits of partial values, rescaled to the common maximum.
-__global__ void attention_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
-                                         int hd, int splits) {
+// out[t, head, :] = sum over splits of partial values, rescaled to the common maximum.  One warp
+// reads every split's (max, sum) at once; the weighted values are added in split order.
+__global__ void __launch_bounds__(128)
+attention_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int hd, int splits) {
+  __shared__ float w[64];
+  __shared__ float inv_l;
   const size_t row = blockIdx.x;     // t * nh + head
   const float* p = partial + row * splits * (hd + 2);
-  float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, p[(size_t)s * (hd + 2) + hd]);
-  float L = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float ms = p[(size_t)s * (hd + 2) + hd];
-    if (ms != -INFINITY) L += p[(size_t)s * (hd + 2) + hd + 1] * __expf(ms - M);
+  if (threadIdx.x < 32) {
+    float ms[2], ls[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int s = threadIdx.x + 32 * u;
+      ms[u] = s < splits ? p[(size_t)s * (hd + 2) + hd] : -INFINITY;
+      ls[u] = s < splits ? p[(size_t)s * (hd + 2) + hd + 1] : 0.f;
+    }
+    const float M = warp_max(fmaxf(ms[0], ms[1]));
+    float L = 0.f;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int s = threadIdx.x + 32 * u;
+      const float ws = ms[u] == -INFINITY ? 0.f : __expf(ms[u] - M);
+      if (s < 64) w[s] = ws;
+      L += ls[u] * ws;
+    }
+    L = warp_sum(L);
+    if (threadIdx.x == 0) inv_l = L > 0.f ? 1.0f / L : 0.f;
   }
+  __syncthreads();
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float o = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float ms = p[(size_t)s * (hd + 2) + hd];
-      if (ms != -INFINITY) o += p[(size_t)s * (hd + 2) + d] * __expf(ms - M);
-    }
-    out[row * hd + d] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
+    for (int s = 0; s < splits; ++s) o += p[(size_t)s * (hd + 2) + d] * w[s];
+    out[row * hd + d] = __float2bfloat16_rn(o * inv_l);
   }
 }
 
@@ -222,7 +236,7 @@ GLINT_API int glint_attention_decode(const void* q, const void* k_pool, const vo
   if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || splits < 1) return GLINT_ERR_BAD_ARG;
   if (hd % 8 || hd <= 0 || hd > 512) return GLINT_ERR_UNSUPPORTED_SIZE;
   if (splits > 1 && !partial) return GLINT_ERR_BAD_ARG;
-  if (nkv > 65535 || splits > 65535) return GLINT_ERR_UNSUPPORTED_SIZE;
+  if (nkv > 65535 || splits > 64) return GLINT_ERR_UNSUPPORTED_SIZE;
   dim3 grid(T, nkv, splits);
   const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)k_pool,
                       *vv = (const __nv_bfloat16*)v_pool;

@@ -161,6 +161,206 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int* _
 }
 
 // ---------------------------------------------------------------------------------------------
+// Fast forms of the row kernels for widths that are a multiple of 4: a row is loaded once into
+// registers as float4 (all loads in flight together), reduced, and written; nothing is re-read.
+// ---------------------------------------------------------------------------------------------
+constexpr int ROW_THREADS = 256;
+
+template <typename S>
+__device__ __forceinline__ void store4(S* dst, float a, float b, float c, float d);
+template <>
+__device__ __forceinline__ void store4<float>(float* dst, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* dst, float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 v;
+  v.x = *reinterpret_cast<const uint32_t*>(&lo);
+  v.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = v;
+}
+
+template <typename S, int ITERS>
+__global__ void __launch_bounds__(ROW_THREADS)
+rmsnorm_fast_kernel(const float* __restrict__ x, const int* __restrict__ row_index, const float* __restrict__ w,
+                    S* __restrict__ out, int H, float eps, float offset) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int H4 = H >> 2;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(row_index ? row_index[r] : r) * H);
+  const float4* w4 = reinterpret_cast<const float4*>(w);
+  float4 xv[ITERS], wv[ITERS];
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = threadIdx.x + it * ROW_THREADS;
+    xv[it] = i < H4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    wv[it] = i < H4 ? w4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it)
+    ss += xv[it].x * xv[it].x + xv[it].y * xv[it].y + xv[it].z * xv[it].z + xv[it].w * xv[it].w;
+  ss = block_sum(ss, scratch);
+  const float rs = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = threadIdx.x + it * ROW_THREADS;
+    if (i < H4)
+      store4<S>(out + (size_t)r * H + 4 * i, xv[it].x * rs * (offset + wv[it].x), xv[it].y * rs * (offset + wv[it].y),
+                xv[it].z * rs * (offset + wv[it].z), xv[it].w * rs * (offset + wv[it].w));
+  }
+}
+
+template <typename S, int ITERS>
+__global__ void __launch_bounds__(ROW_THREADS)
+add_rmsnorm_fast_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ w_a,
+                        float eps_a, float offset_a, S* __restrict__ out, const float* __restrict__ w_b,
+                        float eps_b, float offset_b, int H) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int H4 = H >> 2;
+  float4* xr = reinterpret_cast<float4*>(x + (size_t)r * H);
+  const float4* yr = reinterpret_cast<const float4*>(y + (size_t)r * H);
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 xv[ITERS], yv[ITERS], wa[ITERS], wb[ITERS];
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = threadIdx.x + it * ROW_THREADS;
+    const bool in = i < H4;
+    xv[it] = in ? xr[i] : zero;
+    yv[it] = in ? yr[i] : zero;
+    wa[it] = (in && w_a) ? reinterpret_cast<const float4*>(w_a)[i] : zero;
+    wb[it] = (in && w_b && out) ? reinterpret_cast<const float4*>(w_b)[i] : zero;
+  }
+  float rs_a = 1.f;
+  if (w_a) {
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it)
+      ss += yv[it].x * yv[it].x + yv[it].y * yv[it].y + yv[it].z * yv[it].z + yv[it].w * yv[it].w;
+    ss = block_sum(ss, scratch);
+    rs_a = 1.0f / sqrtf(ss / (float)H + eps_a);
+  }
+  float ss_x = 0.f;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = threadIdx.x + it * ROW_THREADS;
+    if (w_a) {
+      xv[it].x += yv[it].x * rs_a * (offset_a + wa[it].x);
+      xv[it].y += yv[it].y * rs_a * (offset_a + wa[it].y);
+      xv[it].z += yv[it].z * rs_a * (offset_a + wa[it].z);
+      xv[it].w += yv[it].w * rs_a * (offset_a + wa[it].w);
+    } else {
+      xv[it].x += yv[it].x;
+      xv[it].y += yv[it].y;
+      xv[it].z += yv[it].z;
+      xv[it].w += yv[it].w;
+    }
+    if (i < H4) xr[i] = xv[it];
+    ss_x += xv[it].x * xv[it].x + xv[it].y * xv[it].y + xv[it].z * xv[it].z + xv[it].w * xv[it].w;
+  }
+  if (!out) return;
+  ss_x = block_sum(ss_x, scratch);
+  const float rs_b = w_b ? 1.0f / sqrtf(ss_x / (float)H + eps_b) : 1.f;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = threadIdx.x + it * ROW_THREADS;
+    if (i >= H4) continue;
+    if (w_b)
+      store4<S>(out + (size_t)r * H + 4 * i, xv[it].x * rs_b * (offset_b + wb[it].x),
+                xv[it].y * rs_b * (offset_b + wb[it].y), xv[it].z * rs_b * (offset_b + wb[it].z),
+                xv[it].w * rs_b * (offset_b + wb[it].w));
+    else
+      store4<S>(out + (size_t)r * H + 4 * i, xv[it].x, xv[it].y, xv[it].z, xv[it].w);
+  }
+}
+
+// Rotary encoding, fast form: the sines and cosines of the token's position are computed once
+// per block into shared memory, then every head reads them.  Same arithmetic as the plain form.
+template <typename S>
+__global__ void __launch_bounds__(256)
+rope_kv_write_fast_kernel(const float* __restrict__ qkv, const int* __restrict__ positions,
+                          const int* __restrict__ token_slot, const int* __restrict__ block_table, int max_pages,
+                          const float* __restrict__ inv_freq, float factor, S* __restrict__ q_out,
+                          S* __restrict__ k_pool, S* __restrict__ v_pool, int nh, int nkv, int hd, int page_size,
+                          int num_pages, int* __restrict__ status) {
+  extern __shared__ float trig[];   // cos[half], sin[half]
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = hd >> 1;
+  const float ps = (float)pos / factor;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    float s, c;
+    sincosf(ps * inv_freq[j], &s, &c);
+    trig[j] = c;
+    trig[half + j] = s;
+  }
+  long long page_base = -1;
+  if (k_pool) {
+    const int page = block_table[(size_t)token_slot[t] * max_pages + pos / page_size];
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicExch(status, 2);
+    } else {
+      page_base = ((long long)page * nkv) * page_size * hd + (long long)(pos % page_size) * hd;
+    }
+  }
+  __syncthreads();
+  const float* row = qkv + (size_t)t * (nh + 2 * nkv) * hd;
+  const int half2 = half >> 1;   // pairs of adjacent j
+  for (int w = threadIdx.x; w < (nh + nkv) * half2; w += blockDim.x) {
+    const int head = w / half2, j = (w % half2) * 2;
+    const float* src = row + (size_t)head * hd;
+    const float2 lo = *reinterpret_cast<const float2*>(src + j);
+    const float2 hi = *reinterpret_cast<const float2*>(src + j + half);
+    const float c0 = trig[j], c1 = trig[j + 1], s0 = trig[half + j], s1 = trig[half + j + 1];
+    const float a0 = lo.x * c0 - hi.x * s0, a1 = lo.y * c1 - hi.y * s1;
+    const float b0 = lo.x * s0 + hi.x * c0, b1 = lo.y * s1 + hi.y * c1;
+    S* dst = nullptr;
+    if (head < nh) dst = q_out + (size_t)t * nh * hd + (size_t)head * hd;
+    else if (page_base >= 0) dst = k_pool + page_base + (long long)(head - nh) * page_size * hd;
+    if (dst) {
+      dst[j] = from_float<S>(a0);
+      dst[j + 1] = from_float<S>(a1);
+      dst[j + half] = from_float<S>(b0);
+      dst[j + half + 1] = from_float<S>(b1);
+    }
+  }
+  if (page_base >= 0) {
+    const float* vsrc = row + (size_t)(nh + nkv) * hd;
+    for (int w = threadIdx.x; w < (nkv * hd) >> 2; w += blockDim.x) {
+      const int head = (w * 4) / hd, d = (w * 4) % hd;
+      const float4 v = *reinterpret_cast<const float4*>(vsrc + (size_t)w * 4);
+      store4<S>(v_pool + page_base + (long long)head * page_size * hd + d, v.x, v.y, v.z, v.w);
+    }
+  }
+}
+
+// x[t, :] = table[ids[t], :] * scale, 8 elements at a time (bfloat16 table, width a multiple of 8)
+__global__ void embed_scale_fast_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
+                                        float* __restrict__ x, int H, float scale, int vocab,
+                                        int* __restrict__ status) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool bad = id < 0 || id >= vocab;
+  if (bad && threadIdx.x == 0) atomicExch(status, 1);
+  const uint4* row = reinterpret_cast<const uint4*>(table + (size_t)(bad ? 0 : id) * H);
+  for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) {
+    const uint4 raw = row[i];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float4 a, b;
+    const float2 p0 = __bfloat1622float2(h[0]), p1 = __bfloat1622float2(h[1]);
+    const float2 p2 = __bfloat1622float2(h[2]), p3 = __bfloat1622float2(h[3]);
+    const float m = bad ? 0.f : scale;
+    a = make_float4(p0.x * m, p0.y * m, p1.x * m, p1.y * m);
+    b = make_float4(p2.x * m, p2.y * m, p3.x * m, p3.y * m);
+    float4* dst = reinterpret_cast<float4*>(x + (size_t)t * H + 8 * i);
+    dst[0] = a;
+    dst[1] = b;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // out[t, i] = act(gu[t, i]) * gu[t, I + i]
 // ---------------------------------------------------------------------------------------------
 template <typename S>
@@ -196,9 +396,22 @@ using namespace glint;
     return GLINT_ERR_BAD_ARG;                                \
   }
 
+// Number of float4 loads per thread the fast row kernels need, or 0 when the row does not
+// qualify (width not a multiple of 4, too wide, or a pointer not 16-byte aligned).
+static int fast_iters(int H, const void* a, const void* b, const void* c, const void* d) {
+  if (H % 4 || H <= 0) return 0;
+  if ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)c) | ((uintptr_t)d)) & 15) return 0;
+  const int iters = (H / 4 + ROW_THREADS - 1) / ROW_THREADS;
+  return iters <= 8 ? iters : 0;
+}
+
 GLINT_API int glint_embed_scale(const void* table, int dtype, const int* ids, float* x, int T, int H,
                                 float scale, int vocab, int* status, cudaStream_t stream) {
   if (T <= 0) return GLINT_OK;
+  if (dtype == GLINT_DTYPE_BF16 && H % 8 == 0 && ((uintptr_t)table & 15) == 0 && ((uintptr_t)x & 15) == 0) {
+    embed_scale_fast_kernel<<<T, 128, 0, stream>>>((const __nv_bfloat16*)table, ids, x, H, scale, vocab, status);
+    return (int)cudaGetLastError();
+  }
   DISPATCH(dtype, embed_scale_kernel<S><<<T, 256, 0, stream>>>((const S*)table, ids, x, H, scale, vocab, status));
   return (int)cudaGetLastError();
 }
@@ -206,8 +419,17 @@ GLINT_API int glint_embed_scale(const void* table, int dtype, const int* ids, fl
 GLINT_API int glint_rmsnorm(const float* x, const int* row_index, const float* w, void* out, int dtype,
                             int rows, int H, float eps, float offset, cudaStream_t stream) {
   if (rows <= 0) return GLINT_OK;
-  const int threads = H >= 1024 ? 256 : 128;
-  DISPATCH(dtype, rmsnorm_kernel<S><<<rows, threads, 0, stream>>>(x, row_index, w, (S*)out, H, eps, offset));
+  const int iters = fast_iters(H, x, w, out, nullptr);
+#define RMS_FAST(N) DISPATCH(dtype, rmsnorm_fast_kernel<S, N><<<rows, ROW_THREADS, 0, stream>>>(x, row_index, w, (S*)out, H, eps, offset))
+  if (iters == 1) { RMS_FAST(1); }
+  else if (iters == 2) { RMS_FAST(2); }
+  else if (iters <= 4) { RMS_FAST(4); }
+  else if (iters <= 8) { RMS_FAST(8); }
+  else {
+    const int threads = H >= 1024 ? 256 : 128;
+    DISPATCH(dtype, rmsnorm_kernel<S><<<rows, threads, 0, stream>>>(x, row_index, w, (S*)out, H, eps, offset));
+  }
+#undef RMS_FAST
   return (int)cudaGetLastError();
 }
 
@@ -215,9 +437,19 @@ GLINT_API int glint_add_rmsnorm(float* x, const float* y, const float* w_a, floa
                                 void* out, int dtype, const float* w_b, float eps_b, float offset_b,
                                 int rows, int H, cudaStream_t stream) {
   if (rows <= 0) return GLINT_OK;
-  const int threads = H >= 1024 ? 256 : 128;
-  DISPATCH(dtype, add_rmsnorm_kernel<S><<<rows, threads, 0, stream>>>(x, y, w_a, eps_a, offset_a, (S*)out, w_b,
-                                                                    eps_b, offset_b, H));
+  int iters = fast_iters(H, x, y, out, w_a);
+  if (w_b && ((uintptr_t)w_b & 15)) iters = 0;
+#define ADD_FAST(N) DISPATCH(dtype, add_rmsnorm_fast_kernel<S, N><<<rows, ROW_THREADS, 0, stream>>>(x, y, w_a, eps_a, offset_a, (S*)out, w_b, eps_b, offset_b, H))
+  if (iters == 1) { ADD_FAST(1); }
+  else if (iters == 2) { ADD_FAST(2); }
+  else if (iters <= 4 && iters > 0) { ADD_FAST(4); }
+  else if (iters <= 8 && iters > 0) { ADD_FAST(8); }
+  else {
+    const int threads = H >= 1024 ? 256 : 128;
+    DISPATCH(dtype, add_rmsnorm_kernel<S><<<rows, threads, 0, stream>>>(x, y, w_a, eps_a, offset_a, (S*)out, w_b,
+                                                                      eps_b, offset_b, H));
+  }
+#undef ADD_FAST
   return (int)cudaGetLastError();
 }
 
@@ -228,6 +460,13 @@ GLINT_API int glint_rope_kv_write(const float* qkv, const int* positions, const 
                                   int num_pages, int* status, cudaStream_t stream) {
   if (T <= 0) return GLINT_OK;
   if (hd % 2 || rot % 2 || rot > hd || rot < 0 || factor <= 0.f) return GLINT_ERR_BAD_ARG;
+  if (rot == hd && hd % 8 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)q_out & 15) == 0 &&
+      ((uintptr_t)k_pool & 15) == 0 && ((uintptr_t)v_pool & 15) == 0) {
+    DISPATCH(dtype, rope_kv_write_fast_kernel<S><<<T, 256, hd * sizeof(float), stream>>>(
+                        qkv, positions, token_slot, block_table, max_pages, inv_freq, factor, (S*)q_out,
+                        (S*)k_pool, (S*)v_pool, nh, nkv, hd, page_size, num_pages, status));
+    return (int)cudaGetLastError();
+  }
   DISPATCH(dtype, rope_kv_write_kernel<S><<<T, 256, 0, stream>>>(
                       qkv, positions, token_slot, block_table, max_pages, inv_freq, factor, rot, (S*)q_out,
                       (S*)k_pool, (S*)v_pool, nh, nkv, hd, page_size, num_pages, status));

@@ -287,11 +287,12 @@ GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int ou
   int splits = 1;
   if (force_splits > 0) {
     splits = force_splits;
-  } else if (tiles < 100) {
-    splits = (148 + tiles - 1) / tiles;
-    const int max_by_k = p.total_kb / 4 > 0 ? p.total_kb / 4 : 1;
+  } else if (tiles <= 74) {
+    // one wave: as many blocks as fit the 148 SMs at once, each with at least two K blocks
+    splits = 148 / tiles;
+    const int max_by_k = p.total_kb / 2 > 0 ? p.total_kb / 2 : 1;
     if (splits > max_by_k) splits = max_by_k;
-    if (splits > 16) splits = 16;
+    if (splits > 32) splits = 32;
   }
   if (splits > p.total_kb) splits = p.total_kb;
   p.kb_per_split = (p.total_kb + splits - 1) / splits;
