@@ -16,6 +16,8 @@
 // the tile's counter adds them in split order (no spinning, deterministic) and resets the
 // counter.  Epilogues: soft cap (output head), or with two weight tiles per stage
 // (gate rows and up rows of the same features) act(gate) * up written as bfloat16.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -193,13 +195,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         __threadfence();
         const float* base = p.workspace + ((size_t)tile_id * p.splits * halves) * p.BN * GEMM_BM;
         const size_t split_stride = (size_t)halves * p.BN * GEMM_BM;
-        for (int c = 0; c < p.BN; ++c) {
-          float a = 0.f, b = 0.f;
+        // 16 columns at a time, all their loads in flight together; splits are added in order
+        for (int c0 = 0; c0 < p.BN; c0 += 16) {
+          float a[16], b[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) a[j] = b[j] = 0.f;
           for (int s = 0; s < p.splits; ++s) {
-            a += __ldcg(base + s * split_stride + (size_t)c * GEMM_BM + q * 32 + lane);
-            if (DUAL) b += __ldcg(base + s * split_stride + (size_t)(p.BN + c) * GEMM_BM + q * 32 + lane);
+            const float* src = base + s * split_stride + (size_t)c0 * GEMM_BM + q * 32 + lane;
+            float va[16], vb[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              va[j] = __ldcg(src + (size_t)j * GEMM_BM);
+              if (DUAL) vb[j] = __ldcg(src + (size_t)(p.BN + j) * GEMM_BM);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              a[j] += va[j];
+              if (DUAL) b[j] += vb[j];
+            }
           }
-          store_result<DUAL>(p, f, m0 + c, a, b);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) store_result<DUAL>(p, f, m0 + c0 + j, a[j], b[j]);
         }
         if (threadIdx.x == 64) p.counters[tile_id] = 0;   // ready for the next launch on this stream
       }
@@ -280,6 +296,7 @@ GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int ou
   const int stage_bytes = A_STAGE_BYTES * (dual ? 2 : 1) + bn * GEMM_BK * 2;
   int stages = (227 * 1024 - 1024 - (int)sizeof(GemmShared) - 256) / stage_bytes;
   if (stages > GEMM_MAX_STAGES) stages = GEMM_MAX_STAGES;
+  if (const char* ov = getenv("GLINT_GEMM_STAGES")) { const int v = atoi(ov); if (v >= 2 && v < stages) stages = v; }
   if (stages < 2) return GLINT_ERR_UNSUPPORTED_SIZE;
   p.stages = stages;
   p.total_kb = (K + GEMM_BK - 1) / GEMM_BK;

@@ -12,7 +12,7 @@ _P, _I, _F, _L = c_void_p, c_int, c_float, c_longlong
 
 _SIGNATURES = {
     "glint_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _L, _F, _I, _I, _I, _P, _P, _P, _I, _P],
-    "glint_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P],
+    "glint_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P],
     "glint_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
 }
 
@@ -88,9 +88,9 @@ _partials = {}
 
 
 def decode_splits(tokens, nkv, max_context):
-    """Enough blocks to fill the GPU, each with at least 64 keys."""
-    want = -(-444 // max(1, tokens * nkv))
-    return max(1, min(want, max_context // 64, 64))
+    """One wave of blocks (2 fit on each of the 148 SMs), each split with at least 128 keys."""
+    want = 296 // max(1, tokens * nkv)
+    return max(1, min(want, max_context // 128, 32))
 
 
 def attention_decode(q, k_pool, v_pool, positions, token_seq, block_table, out, nh, nkv, hd, page_size, num_pages,
@@ -99,21 +99,21 @@ def attention_decode(q, k_pool, v_pool, positions, token_seq, block_table, out, 
     T = q.shape[0]
     ops.require(q, torch.bfloat16, "q"); ops.require(k_pool, torch.bfloat16, "k_pool")
     ops.require(v_pool, torch.bfloat16, "v_pool"); ops.require(out, torch.bfloat16, "out")
-    partial = None
+    partial = counters = None
     if splits > 1:
         need = T * nh * splits * (hd + 2)
         key = str(q.device)
-        partial = _partials.get(key)
-        if partial is None or partial.numel() < need:
-            partial = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device)
-            _partials[key] = partial
+        entry = _partials.get(key)
+        if entry is None or entry[0].numel() < need or entry[1].numel() < T * nkv:
+            entry = (torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device),
+                     torch.zeros(max(T * nkv, 4096), dtype=torch.int32, device=q.device))
+            _partials[key] = entry
+        partial, counters = entry
     ops.check(lib().glint_attention_decode(ops.ptr(q), ops.ptr(k_pool), ops.ptr(v_pool), ops.ptr(positions),
                                            ops.ptr(token_seq), ops.ptr(block_table), block_table.shape[1],
-                                           ops.ptr(out), ops.ptr(partial), T, nh, nkv, hd, page_size, num_pages,
-                                           multiplier, cap or 0.0, window or 0, splits, ops.ptr(status),
-                                           ops.stream()), "attention_decode")
-    if splits > 1:
-        ops.launch_count += 1
+                                           ops.ptr(out), ops.ptr(partial), ops.ptr(counters), T, nh, nkv, hd,
+                                           page_size, num_pages, multiplier, cap or 0.0, window or 0, splits,
+                                           ops.ptr(status), ops.stream()), "attention_decode")
 
 
 def attention_prefill(q, k_pool, v_pool, cu_seqlens, seq_start, block_table, out, n_seqs, max_q_len, nh, nkv, hd,
