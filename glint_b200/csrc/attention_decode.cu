@@ -1,16 +1,17 @@
 // Attention of single tokens over the paged cache, bfloat16 storage, split over the keys.
 //
 // Memory-bound work: every key and value row of the request is read once per kv head and shared
-// by all query heads of its group.  grid = (tokens, kv heads, splits).  One thread of the block
-// streams the request's pages (a page of one kv head is contiguous) into a ring of shared-memory
-// stages with bulk asynchronous copies that complete on an mbarrier, so the memory system stays
-// busy while the other threads compute.  The block's 128 threads are 16 groups of 8 lanes; a
-// group takes one key row of the page at a time, its 8 lanes covering the head in 16-byte
-// pieces.  Each group keeps a running (max, sum, weighted values) per query head in 32-bit
-// (src/tensor/flash.rs:65-123); groups are merged in shared memory in group order.  With more
-// than one split, partial results go to a workspace and the block that arrives last at the
-// (token, kv head) counter merges the splits in split order and resets the counter: no
-// spinning, no second launch, a fixed order of addition.
+// by all query heads of its group.  grid = (tokens, kv heads, splits).  A producer warp streams
+// the request's pages into a ring of shared-memory stages with TMA tile loads (128-byte swizzle,
+// completion on an mbarrier); four consumer warps take the pages in turn.  A consumer computes,
+// per 16 keys, scores^T = K q^T and out^T += V^T p^T with mma.sync tiles in which the N
+// dimension (8) holds the query heads of the group, so that keys and values are the large
+// operands read straight from shared memory and nothing is padded to a 128-row tile.  Scores,
+// soft cap, running max/sum and the output accumulator are 32-bit (src/tensor/flash.rs:65-123);
+// probabilities are rounded to bfloat16 for the second product.  The four warps are merged in
+// shared memory in warp order.  With more than one split, partial results go to a workspace and
+// the block that arrives last at the (token, kv head) counter merges the splits in split order
+// and resets the counter: no spinning, no second launch, a fixed order of addition.
 // Score = (q.k) * multiplier, then cap * tanh(score / cap) (src/tensor/flash.rs:76-87); keys from
 // max(0, pos - window + 1) to pos (src/transformer/forward.rs:574-582).
 #include "common.cuh"
@@ -18,32 +19,48 @@
 
 namespace glint {
 
-constexpr int DEC_THREADS = 128;   // consumer threads: 16 groups of 8 lanes
-constexpr int DEC_GROUPS = 16;
-constexpr int DEC_WARPS = DEC_THREADS / 32;
-constexpr int DEC_BLOCK = DEC_THREADS + 32;   // plus one producer warp
-constexpr int DEC_MAX_STAGES = 8;
+constexpr int DEC_WARPS = 4;                      // consumer warps
+constexpr int DEC_THREADS = DEC_WARPS * 32;
+constexpr int DEC_BLOCK = DEC_THREADS + 32;       // plus the producer warp
+constexpr int DEC_MAX_STAGES = 12;
 constexpr int DEC_MAX_SPLITS = 64;
-
-__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = __bfloat1622float2(h[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
-}
-
-// Contiguous global -> shared copy that reports its bytes to an mbarrier.
-__device__ __forceinline__ void bulk_copy(void* smem_dst, const void* src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   tc::smem_u32(smem_dst)),
-               "l"(src), "r"(bytes), "r"(tc::smem_u32(bar))
-               : "memory");
-}
+constexpr int DEC_HEADS = 8;                      // query heads per pass (the MMA's N)
+constexpr int SUB_BYTES_PER_ROW = 128;            // one swizzle row: 64 bf16
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+  return r;
+}
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Byte offset of (row, 16-byte chunk) inside a tile of rows x 128 bytes stored with the 128-byte
+// swizzle: chunk c of row r sits at chunk (c ^ (r & 7)).
+__device__ __forceinline__ uint32_t swz(int row, int chunk) {
+  return (uint32_t)(row * SUB_BYTES_PER_ROW + ((chunk ^ (row & 7)) << 4));
+}
 
 struct DecodeShared {
   uint64_t full[DEC_MAX_STAGES];
@@ -54,22 +71,25 @@ struct DecodeShared {
   float inv_l;
 };
 
-// CH: 16-byte pieces per lane (head_dim <= 64 * CH).  GH: query heads handled per pass.
-template <int CH, int GH>
+// HD: register capacity (head_dim <= HD; head_dim and page_size are multiples of 16).
+template <int HD>
 __global__ void __launch_bounds__(DEC_BLOCK, 2)
-attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
-                        const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ positions,
+attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                        const __nv_bfloat16* __restrict__ q, const int* __restrict__ positions,
                         const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_pages,
                         __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int* __restrict__ counters,
                         int nh, int nkv, int hd, int page_size, int num_pages, float multiplier, float cap,
                         int window, int splits, int stages, int* __restrict__ status) {
-  extern __shared__ __align__(128) uint8_t dec_smem[];
+  extern __shared__ uint8_t dec_raw[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dec_raw) + 1023) & ~(uintptr_t)1023);
   const int t = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int G = nh / nkv;
-  const int lane8 = threadIdx.x & 7, group = threadIdx.x >> 3;
-  // groups of one warp may see different key ranges: shuffles name only the group's own lanes
-  const unsigned gmask = 0xFFu << (threadIdx.x & 24);
-  const int pieces = hd >> 3;                    // 16-byte pieces per row
+  const int HP = G < DEC_HEADS ? G : DEC_HEADS;          // heads per pass
+  const int n_pass = (G + DEC_HEADS - 1) / DEC_HEADS;
+  const int hd16 = hd >> 4;
+  const int nsub = (hd + 63) >> 6;                        // 64-wide column tiles of a page
+  const uint32_t sub_bytes = (uint32_t)page_size * SUB_BYTES_PER_ROW;
+  const uint32_t page_bytes = nsub * sub_bytes;
   const int pos = positions[t];
   const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   // the split takes whole pages, counted from the page that holds the first key
@@ -78,33 +98,30 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int my_lo = page_lo + split * pages_per_split;
   const int my_hi = min(page_hi + 1, my_lo + pages_per_split);     // exclusive
   const int n_pages = max(0, my_hi - my_lo);
+  const int n_iter = n_pages * n_pass;                    // every pass streams the split's pages again
   const int* table = block_table + (size_t)token_seq[t] * max_pages;
-  const uint32_t page_bytes = (uint32_t)page_size * hd * 2;
   const int stride_f = hd + 2;
 
-  // shared memory: stages of [K page | V page], then the merge area, then barriers
-  uint8_t* ring = dec_smem;
   float* merge = reinterpret_cast<float*>(ring + (size_t)stages * 2 * page_bytes);
-  DecodeShared* sh = reinterpret_cast<DecodeShared*>(merge + (size_t)DEC_WARPS * GH * stride_f);
+  DecodeShared* sh = reinterpret_cast<DecodeShared*>(merge + (size_t)DEC_WARPS * HP * stride_f);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       tc::mbar_init(&sh->full[s], 1);
-      tc::mbar_init(&sh->empty[s], DEC_WARPS);
+      tc::mbar_init(&sh->empty[s], 1);
     }
     sh->abort_flag = 0;
     sh->is_last = 0;
     tc::fence_barrier_init();
+    tc::tma_prefetch_desc(&map_k);
+    tc::tma_prefetch_desc(&map_v);
   }
   __syncthreads();
   volatile int* abort_flag = &sh->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const int n_pass = (G + GH - 1) / GH;
-  const int n_iter = n_pages * n_pass;       // every pass streams the split's pages again
-
-  if (threadIdx.x >= DEC_THREADS) {
-    // ---- producer warp: looks up 32 pages at a time, one lane starts the copies ----------------------
-    const int lane = threadIdx.x & 31;
+  if (warp == DEC_WARPS) {
+    // ---- producer warp: looks up 32 pages at a time, one lane starts the tile loads ------------------
     for (int base = 0; base < n_iter; base += 32) {
       const int mine = base + lane;
       int page = 0;
@@ -123,10 +140,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
           bool ok = true;
           if (it >= stages) ok = tc::mbar_wait(&sh->empty[s], ((it / stages) - 1) & 1, abort_flag);
           if (ok) {
-            const size_t off = ((size_t)pg * nkv + kvh) * page_size * hd;
+            uint8_t* kdst = ring + (size_t)s * 2 * page_bytes;
+            const int row = (pg * nkv + kvh) * page_size;
             tc::mbar_expect_tx(&sh->full[s], 2 * page_bytes);
-            bulk_copy(ring + (size_t)s * 2 * page_bytes, k_pool + off, page_bytes, &sh->full[s]);
-            bulk_copy(ring + (size_t)s * 2 * page_bytes + page_bytes, v_pool + off, page_bytes, &sh->full[s]);
+            for (int sub = 0; sub < nsub; ++sub) {
+              tc::tma_load_2d(kdst + sub * sub_bytes, &map_k, &sh->full[s], sub * 64, row);
+              tc::tma_load_2d(kdst + page_bytes + sub * sub_bytes, &map_v, &sh->full[s], sub * 64, row);
+            }
           }
         }
       }
@@ -134,146 +154,164 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     return;
   }
 
+  // ---- consumer warps ----------------------------------------------------------------------------------
+  const int g = lane >> 2, tq = lane & 3;
   const float score_scale = cap > 0.f ? multiplier / cap : multiplier;
-  int it = 0;
+  const uint32_t ring_addr = tc::smem_u32(ring);
   for (int pass = 0; pass < n_pass; ++pass) {
-    float qf[GH][CH * 8], acc[GH][CH * 8], m[GH], l[GH];
-#pragma unroll
-    for (int j = 0; j < GH; ++j) {
-      const int hg = pass * GH + j;
+    // q^T as the B operand: this thread holds dims (16 ks + 2 tq, +1) and (+8, +9) of head g
+    uint32_t qb[HD / 16][2];
+    {
+      const int hg = pass * DEC_HEADS + g;
       const __nv_bfloat16* qrow = q + ((size_t)t * nh + kvh * G + (hg < G ? hg : 0)) * hd;
 #pragma unroll
-      for (int c = 0; c < CH; ++c) {
-        const int piece = lane8 + 8 * c;
-        if (piece < pieces && hg < G) {
-          unpack8(*reinterpret_cast<const uint4*>(qrow + piece * 8), &qf[j][c * 8]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) qf[j][c * 8 + i] = 0.f;
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[j][c * 8 + i] = 0.f;
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        const bool in = ks < hd16 && hg < G;
+        qb[ks][0] = in ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + tq * 2) : 0u;
+        qb[ks][1] = in ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + tq * 2) : 0u;
       }
-      m[j] = -INFINITY;
-      l[j] = 0.f;
     }
-    for (int pi = 0; pi < n_pages; ++pi, ++it) {
+    float o[HD / 16][4];
+#pragma unroll
+    for (int i = 0; i < HD / 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    // Iteration `it` (over all passes) belongs to warp it % 4 and stage it % stages; the stage count
+    // is a multiple of 4, so a stage is always read by the same warp and that warp sees every
+    // phase of the stage's barrier (a waiter that skipped a phase would match the wrong parity).
+    const int it_lo = pass * n_pages, it_hi = it_lo + n_pages;
+    for (int it = it_lo + ((warp - it_lo) % DEC_WARPS + DEC_WARPS) % DEC_WARPS; it < it_hi; it += DEC_WARPS) {
+      const int pi = it - it_lo;
       const int s = it % stages;
       const bool ok = tc::mbar_wait(&sh->full[s], (it / stages) & 1, abort_flag);
-      const uint8_t* kpage = ring + (size_t)s * 2 * page_bytes;
-      const uint8_t* vpage = kpage + page_bytes;
-      const int key0 = (my_lo + pi) * page_size;
-      for (int r = group; r < page_size && ok; r += DEC_GROUPS) {
-        const int key = key0 + r;
-        if (key < first || key > pos) continue;        // uniform within the group
-        float dot[GH];
+      const uint32_t kbase = ring_addr + (uint32_t)s * 2 * page_bytes;
+      const uint32_t vbase = kbase + page_bytes;
+      for (int tile = 0; tile * 16 < page_size && ok; ++tile) {
+        const int key0 = (my_lo + pi) * page_size + tile * 16;
+        if (key0 > pos || key0 + 15 < first) continue;            // the whole tile is masked
+        float sc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int j = 0; j < GH; ++j) dot[j] = 0.f;
-#pragma unroll
-        for (int c = 0; c < CH; ++c) {
-          const int piece = lane8 + 8 * c;
-          if (piece < pieces) {
-            float kf[8];
-            unpack8(*reinterpret_cast<const uint4*>(kpage + ((size_t)r * hd + piece * 8) * 2), kf);
-#pragma unroll
-            for (int j = 0; j < GH; ++j)
-#pragma unroll
-              for (int i = 0; i < 8; ++i) dot[j] = fmaf(qf[j][c * 8 + i], kf[i], dot[j]);
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          if (ks < hd16) {
+            uint32_t a[4];
+            const int row = tile * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+            ldsm_x4(a, kbase + (ks >> 2) * sub_bytes + swz(row, (ks & 3) * 2 + (lane >> 4)));
+            mma16816(sc, a, qb[ks][0], qb[ks][1]);
           }
         }
-        float e[GH];
+        // sc[0], sc[1]: key g, heads 2tq, 2tq+1;  sc[2], sc[3]: key g + 8, same heads
+        const bool va = key0 + g >= first && key0 + g <= pos;
+        const bool vb = key0 + g + 8 >= first && key0 + g + 8 <= pos;
+        float corr[2];
 #pragma unroll
-        for (int j = 0; j < GH; ++j) {
-          float d = dot[j];
-          d += __shfl_xor_sync(gmask, d, 1);
-          d += __shfl_xor_sync(gmask, d, 2);
-          d += __shfl_xor_sync(gmask, d, 4);
-          const float sc = cap > 0.f ? cap * tanhf(d * score_scale) : d * score_scale;
-          const float m_new = fmaxf(m[j], sc);
-          const float corr = __expf(m[j] - m_new);
-          e[j] = __expf(sc - m_new);
-          l[j] = l[j] * corr + e[j];
-          m[j] = m_new;
-#pragma unroll
-          for (int i = 0; i < CH * 8; ++i) acc[j][i] *= corr;
+        for (int h = 0; h < 2; ++h) {
+          float xa = sc[h] * score_scale, xb = sc[2 + h] * score_scale;
+          if (cap > 0.f) {
+            xa = cap * tanhf(xa);
+            xb = cap * tanhf(xb);
+          }
+          xa = va ? xa : -INFINITY;
+          xb = vb ? xb : -INFINITY;
+          float mx = fmaxf(xa, xb);
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+          const float m_new = fmaxf(m[h], mx);
+          const float base = m_new == -INFINITY ? 0.f : m_new;
+          corr[h] = __expf(m[h] - base);
+          const float pa = __expf(xa - base), pb = __expf(xb - base);
+          l[h] = l[h] * corr[h] + pa + pb;       // this thread's keys only; lanes are added at the end
+          m[h] = m_new;
+          sc[h] = pa;
+          sc[2 + h] = pb;
         }
+        if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
 #pragma unroll
-        for (int c = 0; c < CH; ++c) {
-          const int piece = lane8 + 8 * c;
-          if (piece < pieces) {
-            float vf[8];
-            unpack8(*reinterpret_cast<const uint4*>(vpage + ((size_t)r * hd + piece * 8) * 2), vf);
+          for (int i = 0; i < HD / 16; ++i) {
+            o[i][0] *= corr[0];
+            o[i][1] *= corr[1];
+            o[i][2] *= corr[0];
+            o[i][3] *= corr[1];
+          }
+        }
+        // value rows of masked keys may hold anything (a page's unwritten tail): zero them, since
+        // 0 * NaN would poison the product.  Only the first and last tile of a range get here.
+        if (key0 < first || key0 + 15 > pos) {
+          for (int r = 0; r < 16; ++r) {
+            const int key = key0 + r;
+            if (key >= first && key <= pos) continue;
+            for (int c = lane; c < nsub * 8; c += 32)
+              *reinterpret_cast<uint4*>(ring + (size_t)s * 2 * page_bytes + page_bytes + (c >> 3) * sub_bytes +
+                                        (tile * 16 + r) * SUB_BYTES_PER_ROW + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+          }
+          __syncwarp();
+        }
+        // p^T as the B operand: keys (2tq, 2tq+1) and (+8) of head g, by an 8x8 transpose in the warp
+        const uint32_t b0 = movmatrix_trans(pack2(sc[0], sc[1]));
+        const uint32_t b1 = movmatrix_trans(pack2(sc[2], sc[3]));
 #pragma unroll
-            for (int j = 0; j < GH; ++j)
-#pragma unroll
-              for (int i = 0; i < 8; ++i) acc[j][c * 8 + i] = fmaf(e[j], vf[i], acc[j][c * 8 + i]);
+        for (int blk = 0; blk < HD / 16; ++blk) {
+          if (blk < hd16) {
+            uint32_t a[4];
+            const int i = lane >> 3;
+            const int key = tile * 16 + (lane & 7) + (i >> 1) * 8;
+            ldsm_x4_trans(a, vbase + (blk >> 2) * sub_bytes + swz(key, (blk & 3) * 2 + (i & 1)));
+            mma16816(o[blk], a, b0, b1);
           }
         }
       }
       __syncwarp();
-      if ((threadIdx.x & 31) == 0) tc::mbar_arrive(&sh->empty[s]);   // this warp is done with stage s
+      if (lane == 0) tc::mbar_arrive(&sh->empty[s]);     // this warp is done with stage s
     }
-    // ---- merge: first the 4 groups of each warp by shuffles, then the 4 warps in shared memory -----
+    // ---- this warp's totals, then the four warps are merged in shared memory, in warp order ----------
 #pragma unroll
-    for (int j = 0; j < GH; ++j) {
-#pragma unroll
-      for (int x = 8; x <= 16; x <<= 1) {
-        const float m_o = __shfl_xor_sync(0xffffffffu, m[j], x);
-        const float l_o = __shfl_xor_sync(0xffffffffu, l[j], x);
-        const float M = fmaxf(m[j], m_o);
-        const float wa = m[j] == -INFINITY ? 0.f : __expf(m[j] - M);
-        const float wb = m_o == -INFINITY ? 0.f : __expf(m_o - M);
-        l[j] = l[j] * wa + l_o * wb;
-        m[j] = M;
-#pragma unroll
-        for (int i = 0; i < CH * 8; ++i) {
-          const float a_o = __shfl_xor_sync(0xffffffffu, acc[j][i], x);
-          acc[j][i] = acc[j][i] * wa + a_o * wb;
-        }
-      }
+    for (int h = 0; h < 2; ++h) {
+      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 4);
+      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 8);
+      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 16);
     }
-    const int warp = threadIdx.x >> 5;
-    if ((threadIdx.x & 31) < 8) {
 #pragma unroll
-      for (int j = 0; j < GH; ++j) {
-        float* dst = merge + ((size_t)warp * GH + j) * stride_f;
+    for (int h = 0; h < 2; ++h) {
+      const int head = 2 * tq + h;
+      if (head < HP && pass * DEC_HEADS + head < G) {
+        float* dst = merge + ((size_t)warp * HP + head) * stride_f;
 #pragma unroll
-        for (int c = 0; c < CH; ++c) {
-          const int piece = lane8 + 8 * c;
-          if (piece < pieces)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) dst[piece * 8 + i] = acc[j][c * 8 + i];
+        for (int blk = 0; blk < HD / 16; ++blk) {
+          if (blk < hd16) {
+            dst[blk * 16 + g] = o[blk][h];
+            dst[blk * 16 + g + 8] = o[blk][2 + h];
+          }
         }
-        if (lane8 == 0) {
-          dst[hd] = m[j];
-          dst[hd + 1] = l[j];
+        if (g == 0) {
+          dst[hd] = m[h];
+          dst[hd + 1] = l[h];
         }
       }
     }
     consumer_sync();
-    for (int j = 0; j < GH; ++j) {
-      const int hg = pass * GH + j;
+    for (int j = 0; j < HP; ++j) {
+      const int hg = pass * DEC_HEADS + j;
       if (hg >= G) break;
       const int head = kvh * G + hg;
       float M = -INFINITY;
 #pragma unroll
-      for (int g = 0; g < DEC_WARPS; ++g) M = fmaxf(M, merge[((size_t)g * GH + j) * stride_f + hd]);
+      for (int wv = 0; wv < DEC_WARPS; ++wv) M = fmaxf(M, merge[((size_t)wv * HP + j) * stride_f + hd]);
       float L = 0.f;
       float w[DEC_WARPS];
 #pragma unroll
-      for (int g = 0; g < DEC_WARPS; ++g) {
-        const float mg = merge[((size_t)g * GH + j) * stride_f + hd];
-        w[g] = mg == -INFINITY ? 0.f : __expf(mg - M);
-        L += merge[((size_t)g * GH + j) * stride_f + hd + 1] * w[g];
+      for (int wv = 0; wv < DEC_WARPS; ++wv) {
+        const float mg = merge[((size_t)wv * HP + j) * stride_f + hd];
+        w[wv] = mg == -INFINITY ? 0.f : __expf(mg - M);
+        L += merge[((size_t)wv * HP + j) * stride_f + hd + 1] * w[wv];
       }
       for (int d = threadIdx.x; d < hd; d += DEC_THREADS) {
-        float o = 0.f;
+        float ov = 0.f;
 #pragma unroll
-        for (int g = 0; g < DEC_WARPS; ++g) o += merge[((size_t)g * GH + j) * stride_f + d] * w[g];
+        for (int wv = 0; wv < DEC_WARPS; ++wv) ov += merge[((size_t)wv * HP + j) * stride_f + d] * w[wv];
         if (splits == 1) {
-          out[((size_t)t * nh + head) * hd + d] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
+          out[((size_t)t * nh + head) * hd + d] = __float2bfloat16_rn(L > 0.f ? ov / L : 0.f);
         } else {
-          partial[(((size_t)t * nh + head) * splits + split) * stride_f + d] = o;
+          partial[(((size_t)t * nh + head) * splits + split) * stride_f + d] = ov;
         }
       }
       if (splits > 1 && threadIdx.x == 0) {
@@ -319,31 +357,34 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
           if (threadIdx.x == 0) sh->inv_l = L > 0.f ? 1.0f / L : 0.f;
         }
         consumer_sync();
-        // warp w adds splits w, w+4, ... (all their loads in flight), then the 4 warps are added in order
-        {
-          const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-          for (int d0 = 0; d0 < hd; d0 += 32 * 4) {
-            const int d = d0 + lane * 4;
-            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (d < hd) {
+        // warp w adds splits w, w+4, ... (all their loads in flight); then the 4 warps are added in order
+        for (int d0 = 0; d0 < hd; d0 += 32 * 4) {
+          const int d = d0 + lane * 4;
+          if (d < hd) {
+            float4 ov = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
-              for (int sidx = warp; sidx < splits; sidx += DEC_WARPS) {
-                const float2 lo = __ldcg(reinterpret_cast<const float2*>(p + (size_t)sidx * stride_f + d));
-                const float2 hi = __ldcg(reinterpret_cast<const float2*>(p + (size_t)sidx * stride_f + d + 2));
-                const float ws = sh->w[sidx];
-                o.x += lo.x * ws; o.y += lo.y * ws; o.z += hi.x * ws; o.w += hi.y * ws;
-              }
-              float* dst = merge + (size_t)warp * stride_f + d;
-              dst[0] = o.x; dst[1] = o.y; dst[2] = o.z; dst[3] = o.w;
+            for (int sidx = warp; sidx < splits; sidx += DEC_WARPS) {
+              const float2 lo = __ldcg(reinterpret_cast<const float2*>(p + (size_t)sidx * stride_f + d));
+              const float2 hi = __ldcg(reinterpret_cast<const float2*>(p + (size_t)sidx * stride_f + d + 2));
+              const float ws = sh->w[sidx];
+              ov.x += lo.x * ws;
+              ov.y += lo.y * ws;
+              ov.z += hi.x * ws;
+              ov.w += hi.y * ws;
             }
+            float* dst = merge + (size_t)warp * stride_f + d;
+            dst[0] = ov.x;
+            dst[1] = ov.y;
+            dst[2] = ov.z;
+            dst[3] = ov.w;
           }
         }
         consumer_sync();
         for (int d = threadIdx.x; d < hd; d += DEC_THREADS) {
-          float o = 0.f;
+          float ov = 0.f;
 #pragma unroll
-          for (int wv = 0; wv < DEC_WARPS; ++wv) o += merge[(size_t)wv * stride_f + d];
-          out[row * hd + d] = __float2bfloat16_rn(o * sh->inv_l);
+          for (int wv = 0; wv < DEC_WARPS; ++wv) ov += merge[(size_t)wv * stride_f + d];
+          out[row * hd + d] = __float2bfloat16_rn(ov * sh->inv_l);
         }
         consumer_sync();
       }
@@ -351,6 +392,39 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     }
   }
   if (threadIdx.x == 0 && sh->abort_flag) atomicExch(status, 4);
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn decode_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// A pool [pages][kv heads][page_size][head_dim] viewed as rows of head_dim, in boxes of
+// page_size rows x 64 columns with the 128-byte swizzle.
+static int pool_map(CUtensorMap* map, const void* pool, long long rows, int hd, int page_size) {
+  EncodeTiledFn fn = decode_encode_fn();
+  if (!fn) return GLINT_ERR_BAD_ARG;
+  cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? GLINT_OK : GLINT_ERR_BAD_ARG;
 }
 
 }  // namespace glint
@@ -361,44 +435,57 @@ GLINT_API long long glint_attention_decode_partial_floats(int T, int nh, int hd,
   return (long long)T * nh * splits * (hd + 2);
 }
 
-// head_dim a multiple of 8 up to 512, splits up to 64.  When splits > 1, `partial` must hold
-// glint_attention_decode_partial_floats(...) floats and `counters` T * nkv zeroed ints (the
-// kernel leaves them zero).
+GLINT_API int glint_attention_decode_supported(int nh, int nkv, int hd, int page_size) {
+  return (nkv > 0 && nh % nkv == 0 && hd % 16 == 0 && hd >= 16 && hd <= 256 && page_size % 16 == 0 &&
+          page_size >= 16 && page_size <= 256) ? 1 : 0;
+}
+
+// head_dim a multiple of 16 up to 256, page_size a multiple of 16 up to 256, splits up to 64.  When
+// splits > 1, `partial` must hold glint_attention_decode_partial_floats(...) floats and `counters`
+// T * nkv zeroed ints (the kernel leaves them zero).
 GLINT_API int glint_attention_decode(const void* q, const void* k_pool, const void* v_pool, const int* positions,
                                      const int* token_seq, const int* block_table, int max_pages, void* out,
                                      float* partial, int* counters, int T, int nh, int nkv, int hd, int page_size,
                                      int num_pages, float multiplier, float cap, int window, int splits,
                                      int* status, cudaStream_t stream) {
   if (T <= 0) return GLINT_OK;
-  if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || splits < 1) return GLINT_ERR_BAD_ARG;
-  if (hd % 8 || hd <= 0 || hd > 512) return GLINT_ERR_UNSUPPORTED_SIZE;
+  if (page_size <= 0 || splits < 1 || nkv <= 0) return GLINT_ERR_BAD_ARG;
+  if (!glint_attention_decode_supported(nh, nkv, hd, page_size)) return GLINT_ERR_UNSUPPORTED_SIZE;
   if (splits > 1 && (!partial || !counters)) return GLINT_ERR_BAD_ARG;
   if (nkv > 65535 || splits > DEC_MAX_SPLITS) return GLINT_ERR_UNSUPPORTED_SIZE;
-  if (((uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)q) & 15) return GLINT_ERR_UNSUPPORTED_SIZE;
-  const long long page_bytes = (long long)page_size * hd * 2;
+  if (((uintptr_t)k_pool | (uintptr_t)v_pool) & 15 || ((uintptr_t)q & 3)) return GLINT_ERR_UNSUPPORTED_SIZE;
+  CUtensorMap map_k, map_v;
+  const long long rows = (long long)num_pages * nkv * page_size;
+  int rc = pool_map(&map_k, k_pool, rows, hd, page_size);
+  if (rc != GLINT_OK) return rc;
+  rc = pool_map(&map_v, v_pool, rows, hd, page_size);
+  if (rc != GLINT_OK) return rc;
+  const int G = nh / nkv;
+  const int HP = G < DEC_HEADS ? G : DEC_HEADS;
+  const long long page_bytes = (long long)((hd + 63) / 64) * page_size * SUB_BYTES_PER_ROW;
+  const long long fixed = (long long)DEC_WARPS * HP * (hd + 2) * 4 + sizeof(DecodeShared) + 1024 + 64;
+  // a multiple of the consumer warps (see the kernel), as many as let two blocks share an SM
+  int stages = (int)((110 * 1024 - fixed) / (2 * page_bytes)) / DEC_WARPS * DEC_WARPS;
+  if (stages > DEC_MAX_STAGES) stages = DEC_MAX_STAGES;
+  if (stages < DEC_WARPS) stages = DEC_WARPS;
+  const long long smem = stages * 2 * page_bytes + fixed;
+  if (smem > 227 * 1024) return GLINT_ERR_UNSUPPORTED_SIZE;
   dim3 grid(T, nkv, splits);
-  const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)k_pool,
-                      *vv = (const __nv_bfloat16*)v_pool;
+  const __nv_bfloat16* qq = (const __nv_bfloat16*)q;
   __nv_bfloat16* oo = (__nv_bfloat16*)out;
-#define LAUNCH(CH, GH)                                                                                         \
-  {                                                                                                            \
-    const long long fixed = (long long)DEC_WARPS * GH * (hd + 2) * 4 + sizeof(DecodeShared) + 128;            \
-    int stages = (int)((110 * 1024 - fixed) / (2 * page_bytes));                                                \
-    if (stages > DEC_MAX_STAGES) stages = DEC_MAX_STAGES;                                                      \
-    if (stages < 2) stages = 2;                                                                                \
-    const long long smem = stages * 2 * page_bytes + fixed;                                                    \
-    if (smem > 227 * 1024) return GLINT_ERR_UNSUPPORTED_SIZE;                                                  \
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<CH, GH>,                                      \
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
-    if (e != cudaSuccess) return (int)e;                                                                       \
-    attention_decode_kernel<CH, GH><<<grid, DEC_BLOCK, smem, stream>>>(                                      \
-        qq, kk, vv, positions, token_seq, block_table, max_pages, oo, partial, counters, nh, nkv, hd, page_size, \
-        num_pages, multiplier, cap, window, splits, stages, status);                                           \
+#define LAUNCH(HD)                                                                                              \
+  {                                                                                                             \
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         (int)smem);                                                            \
+    if (e != cudaSuccess) return (int)e;                                                                        \
+    attention_decode_kernel<HD><<<grid, DEC_BLOCK, smem, stream>>>(map_k, map_v, qq, positions, token_seq,        \
+                                                                  block_table, max_pages, oo, partial, counters, \
+                                                                  nh, nkv, hd, page_size, num_pages, multiplier, \
+                                                                  cap, window, splits, stages, status);         \
   }
-  if (hd <= 64) LAUNCH(1, 4)
-  else if (hd <= 128) LAUNCH(2, 4)
-  else if (hd <= 256) LAUNCH(4, 2)
-  else LAUNCH(8, 1)
+  if (hd <= 64) LAUNCH(64)
+  else if (hd <= 128) LAUNCH(128)
+  else LAUNCH(256)
 #undef LAUNCH
   return (int)cudaGetLastError();
 }

@@ -77,7 +77,12 @@ def gemm_gated(a, w_gate_up, out, activation, status=None, force_splits=0):
 def attention_supported(nh, nkv, hd, page_size):
     """The bfloat16 attention kernels take head sizes in steps of 8 up to 512 (single tokens) and
     in steps of 16 up to 256 with at most 64 query heads per kv head (prompt portions)."""
-    return nkv > 0 and nh % nkv == 0 and hd % 8 == 0 and 0 < hd <= 512
+    return decode_supported(nh, nkv, hd, page_size) or prefill_supported(nh, nkv, hd)
+
+
+def decode_supported(nh, nkv, hd, page_size):
+    return (nkv > 0 and nh % nkv == 0 and hd % 16 == 0 and 16 <= hd <= 256 and page_size % 16 == 0
+            and 16 <= page_size <= 256)
 
 
 def prefill_supported(nh, nkv, hd):
@@ -131,7 +136,7 @@ def attention_prefill(q, k_pool, v_pool, cu_seqlens, seq_start, block_table, out
 def attention(q, view, ctx, out, nh, nkv, hd, multiplier, cap, window, status):
     """Route a step's attention: single tokens to the split kernel, portions to the tiled one."""
     table = ctx.block_table(view.group)
-    if ctx.max_seq_len > 1 and prefill_supported(nh, nkv, hd):
+    if (ctx.max_seq_len > 1 or not decode_supported(nh, nkv, hd, view.page_size)) and prefill_supported(nh, nkv, hd):
         attention_prefill(q, view.k, view.v, ctx.cu_seqlens, ctx.seq_start, table, out, ctx.num_seqs,
                           ctx.max_seq_len, nh, nkv, hd, view.page_size, view.num_pages, multiplier, cap, window,
                           status)
