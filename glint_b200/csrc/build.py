@@ -27,10 +27,10 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 
 LIBRARIES = {
-    "core": ["elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu"],
+    "core": ["elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu", "sample_noalloc.cu"],
     "tensor": ["gemm_tcgen05.cu", "attention_decode.cu", "attention_prefill.cu"],
 }
-HEADERS = ["common.cuh", "tcgen05.cuh"]
+HEADERS = ["common.cuh", "tcgen05.cuh", "noalloc.h"]
 
 _loaded = {}
 _lock = threading.Lock()
