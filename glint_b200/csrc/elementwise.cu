@@ -423,8 +423,8 @@ GLINT_API int glint_rmsnorm(const float* x, const int* row_index, const float* w
 #define RMS_FAST(N) DISPATCH(dtype, rmsnorm_fast_kernel<S, N><<<rows, ROW_THREADS, 0, stream>>>(x, row_index, w, (S*)out, H, eps, offset))
   if (iters == 1) { RMS_FAST(1); }
   else if (iters == 2) { RMS_FAST(2); }
-  else if (iters <= 4) { RMS_FAST(4); }
-  else if (iters <= 8) { RMS_FAST(8); }
+  else if (iters > 0 && iters <= 4) { RMS_FAST(4); }
+  else if (iters > 0 && iters <= 8) { RMS_FAST(8); }
   else {
     const int threads = H >= 1024 ? 256 : 128;
     DISPATCH(dtype, rmsnorm_kernel<S><<<rows, threads, 0, stream>>>(x, row_index, w, (S*)out, H, eps, offset));

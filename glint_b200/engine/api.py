@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import torch
 
-from ..errors import GlintError
+from ..errors import GlintError, RequestError
 from ..sampling import DeviceSampler, SamplingParams
 from .loading import build_engine, load_model, random_model
 from .scheduler import Request, Scheduler
@@ -55,8 +55,13 @@ class LLM:
         ``seed + i``."""
         batch = len(prompt) > 0 and isinstance(prompt[0], (list, tuple))
         prompts = list(prompt) if batch else [prompt]
+        requests = []
         try:
-            requests = []
+            vocab = self.model.spec.vocab_size
+            for p in prompts:
+                bad = [t for t in p if not 0 <= int(t) < vocab]
+                if bad:
+                    raise RequestError(f"token id {bad[0]} lies outside the vocabulary of {vocab}")
             for i, p in enumerate(prompts):
                 params = SamplingParams(temperature=float(temperature), top_k=int(top_k), top_p=float(top_p),
                                         min_p=float(min_p), repeat_penalty=float(repeat_penalty),
@@ -69,6 +74,9 @@ class LLM:
             self.scheduler.run()
             self.model.rt.check_status()
         except GlintError as e:
+            for r in requests:            # leave no half-run request behind
+                if not r.finished:
+                    self.scheduler.abort(r)
             raise ValueError(str(e)) from e
         self.last_requests = requests
         out = [list(r.output) for r in requests]

@@ -1,0 +1,161 @@
+"""Generation through the entry points against the plain implementation: greedy tokens, long
+decoding, the first tokens of a sequence, seeded sampling, a cache too small for everybody, and
+the command line."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from tests import tracing
+from tests.helpers import ROOT, TINY, TOL, make_model_dir, plain_logits, random_tokens
+from tests.plain import model as plain
+from tests.plain import sampler as psampler
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("gen")
+    return {name: make_model_dir(root, name) for name in TINY}
+
+
+def _plain_greedy(folder, prompt, n):
+    c, w = plain.read_config(folder), plain.read_weights(folder)
+    toks, margins = list(prompt), []
+    for _ in range(n):
+        logits = plain.forward(c, w, toks)[-1]
+        top = torch.topk(logits, 2).values
+        margins.append(float(top[0] - top[1]))
+        toks.append(int(torch.argmax(logits)))
+    return toks[len(prompt):], margins
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_float32_equals_plain(folders, name):
+    from glint_b200 import LLM
+    vocab = TINY[name][0]["vocab_size"]
+    lengths = [5, 23, 40] if name == "A" else [1, 9, 31]
+    prompts = [random_tokens(n, vocab, 50 + i) for i, n in enumerate(lengths)]
+    llm = LLM(folders[name], dtype="float32", cache_tokens=512, max_active=4, max_step_tokens=32)
+    got = llm.generate(prompts, max_tokens=16, stop_at_eos=False)
+    for p, g in zip(prompts, got):
+        want, margins = _plain_greedy(folders[name], p, 16)
+        for i, (a, b) in enumerate(zip(g, want)):
+            if a != b:
+                assert margins[i] < 1e-4, (name, len(p), i, g, want)     # a tie within float32 rounding
+                break
+    single = llm.generate(prompts[1], max_tokens=16, stop_at_eos=False)
+    assert single == got[1]                                              # alone == in a batch
+    assert llm.model_info()["architecture"] == "gemma2" and llm.model_info()["vocab_size"] == vocab
+    assert all(s["live"] == 0 for s in llm.cache_stats().values())
+
+
+def test_greedy_generation_bfloat16_follows_plain(folders):
+    from glint_b200 import LLM
+    vocab = TINY["B"][0]["vocab_size"]
+    prompt = random_tokens(31, vocab, 77)
+    llm = LLM(folders["B"], dtype="bfloat16", cache_tokens=256, max_active=2)
+    got = llm.generate(prompt, max_tokens=12, stop_at_eos=False)
+    want, margins = _plain_greedy(folders["B"], prompt, 12)
+    for i, (a, b) in enumerate(zip(got, want)):
+        if a != b:
+            assert margins[i] < TOL["bfloat16"], (i, got, want, margins)
+            break
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(folders, dtype):
+    """From the very first token, one token per step for 300 steps, past several windows and pages."""
+    from glint_b200.engine.loading import build_engine, load_model
+    vocab = TINY["C"][0]["vocab_size"]
+    toks = random_tokens(300, vocab, 5)
+    steps = [{"step": i, "entries": [{"id": "r", "tokens": [t], "want": [0]}], "end": ["r"] if i == 299 else []}
+             for i, t in enumerate(toks)]
+    engine = build_engine(load_model(folders["C"], dtype), 320, num_slots=2)
+    out = tracing.run_in_process(engine, steps)
+    got = tracing.collect(steps, out, vocab)["r"]
+    want = plain_logits(folders["C"], toks)
+    diff = np.abs(got - want).max(axis=1)
+    assert diff[:3].max() <= TOL[dtype], diff[:3]                        # the first tokens of a sequence
+    assert diff.max() <= TOL[dtype], (int(np.argmax(diff > TOL[dtype])), diff.max())
+
+
+def test_temperature_sampling_is_seeded_and_follows_the_plain_sampler(folders):
+    from glint_b200 import LLM
+    vocab = TINY["B"][0]["vocab_size"]
+    prompts = [random_tokens(n, vocab, 90 + i) for i, n in enumerate([1, 9, 31, 77])]
+    llm = LLM(folders["B"], dtype="float32", cache_tokens=1024, max_active=4, max_step_tokens=24)
+    a = llm.generate(prompts, max_tokens=24, temperature=0.8, seed=7, stop_at_eos=False)
+    b = llm.generate(prompts, max_tokens=24, temperature=0.8, seed=7, stop_at_eos=False)
+    c = llm.generate(prompts, max_tokens=24, temperature=0.8, seed=8, stop_at_eos=False)
+    assert a == b and a != c and all(len(x) == 24 for x in a)
+    # the same draws from the plain sampler on the plain logits, request 1 (seed 7 + 1)
+    cfg, w = plain.read_config(folders["B"]), plain.read_weights(folders["B"])
+    rng = psampler.Xorshift64(8)
+    toks = list(prompts[1])
+    agree = 0
+    for i in range(24):
+        logits = plain.forward(cfg, w, toks)[-1].numpy()
+        t = psampler.sample(logits, toks, rng, temperature=0.8)
+        if t != a[1][i]:
+            break
+        agree += 1
+        toks.append(t)
+    assert agree >= 20, (agree, a[1])      # a draw within rounding of a boundary may differ late
+
+
+def test_small_cache_preempts_and_still_gives_the_same_tokens(folders):
+    from glint_b200 import LLM
+    vocab = TINY["A"][0]["vocab_size"]
+    prompts = [random_tokens(n, vocab, 30 + i) for i, n in enumerate([30, 28, 35, 20])]
+    roomy = LLM(folders["A"], dtype="float32", cache_tokens=1024, max_active=4)
+    want = roomy.generate(prompts, max_tokens=20, stop_at_eos=False)
+    tight = LLM(folders["A"], dtype="float32", cache_tokens=96, max_active=4, max_step_tokens=48)
+    got = tight.generate(prompts, max_tokens=20, stop_at_eos=False)
+    assert got == want
+    assert tight.scheduler.counters["preemptions"] >= 1 or any(s["reuses"] > 0 for s in tight.cache_stats().values())
+    assert all(s["live"] == 0 for s in tight.cache_stats().values())
+    with pytest.raises(ValueError, match="empty"):
+        tight.generate([], max_tokens=3) if False else tight.generate([[]], max_tokens=3)
+    with pytest.raises(ValueError, match="vocabulary"):
+        tight.generate([vocab + 5], max_tokens=3)
+
+
+def test_eos_stops_and_is_delivered(folders, tmp_path):
+    from glint_b200 import LLM
+    vocab = TINY["A"][0]["vocab_size"]
+    prompt = random_tokens(12, vocab, 3)
+    llm = LLM(folders["A"], dtype="float32", cache_tokens=256, max_active=2)
+    free = llm.generate(prompt, max_tokens=10, stop_at_eos=False)
+    llm.eos_token_id = free[4]
+    stopped = llm.generate(prompt, max_tokens=10)
+    first = free.index(free[4])
+    assert stopped == free[:first + 1]
+    assert llm.last_requests[0].finish_reason == "stop"
+
+
+def test_command_line(folders, tmp_path):
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    run = lambda *args: subprocess.run([sys.executable, os.path.join(ROOT, "bin", "glint"), *args],
+                                       capture_output=True, text=True, env=env, timeout=600)
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(TINY["A"][0]))
+    out_dir = str(tmp_path / "made")
+    p = run("init", "-c", str(cfg_path), "-o", out_dir, "--seed", "0", "--norm-std", "0.1")
+    assert p.returncode == 0 and os.path.isfile(os.path.join(out_dir, "model.safetensors")), p.stderr
+    p = run("inspect", "-f", out_dir, "--show-tensors")
+    assert p.returncode == 0 and "model.embed_tokens.weight" in p.stdout and "head_count_kv: 2" in p.stdout
+    p = run("generate", "-f", out_dir, "-t", "5,17,3", "-m", "6", "--dtype", "float32")
+    assert p.returncode == 0, p.stderr
+    ids = json.loads(p.stdout.strip().splitlines()[-1].split(":", 1)[1])
+    want, _ = _plain_greedy(out_dir, [5, 17, 3], 6)
+    assert ids == [5, 17, 3] + want
+    p = run("run", "-f", out_dir, "-p", "5 17 3", "-m", "4", "--temperature", "0.7", "--seed", "1", "--dtype", "float32")
+    assert p.returncode == 0 and "Output:" in p.stdout and "tok/s)" in p.stdout, p.stderr
+    p = run("run", "-f", str(tmp_path / "nowhere"), "-p", "1", "-m", "1")
+    assert p.returncode == 1 and "error:" in p.stderr

@@ -222,3 +222,117 @@ def test_attention_finds_one_far_key_among_hundreds(kernel):
                                      k_pool.shape[0], 1 / 16.0, None, None, status)
     got = out.float().cpu().reshape(1, nh, hd)
     assert (got - want).abs().max().item() < 0.03
+
+
+@pytest.mark.parametrize("kernel", ["plain16", "decode", "prefill"])
+@pytest.mark.parametrize("pos", [63, 64, 79, 80, 200])
+def test_attention_window_edge(kernel, pos):
+    """A hot key just outside the window must not be seen; the same key just inside must win.
+    Positions put the window's edge on, before and after a page boundary."""
+    from glint_b200 import ops, ops_tensor
+    nh, nkv, hd, page, window = 4, 2, 64, 16, 33
+    for inside in (False, True):
+        hot = pos - window + 1 if inside else pos - window
+        k_pool, v_pool, table, dense = _paged_case([pos], [1], nkv, hd, page, torch.bfloat16, seed=pos, hot=None)
+        k, v = dense[0]
+        q = torch.zeros(1, nh, hd)
+        for h in range(nh):
+            q[0, h] = k[hot, h // 2] * 3.0
+        q = q.to(torch.bfloat16)
+        want = _attention_reference(q.float(), dense, [0], [pos], nh, nkv, 0.125, None, window)
+        near_hot = (want[0, 0] - v[hot, 0]).abs().max().item()
+        assert (near_hot < 0.05) == inside                   # the case separates the two outcomes
+        qd = q.reshape(1, nh * hd).to(DEV)
+        out = torch.empty_like(qd)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+        if kernel == "plain16":
+            ops.attention_plain(qd, k_pool, v_pool, i32([pos]), i32([0]), table, out, nh, nkv, hd, page,
+                                k_pool.shape[0], 0.125, None, window, status)
+        elif kernel == "decode":
+            ops_tensor.attention_decode(qd, k_pool, v_pool, i32([pos]), i32([0]), table, out, nh, nkv, hd, page,
+                                        k_pool.shape[0], 0.125, None, window, status, 2)
+        else:
+            ops_tensor.attention_prefill(qd, k_pool, v_pool, i32([0, 1]), i32([pos]), table, out, 1, 1, nh, nkv, hd,
+                                         page, k_pool.shape[0], 0.125, None, window, status)
+        got = out.float().cpu().reshape(1, nh, hd)
+        assert (got - want).abs().max().item() < 0.03, (inside, (got - want).abs().max().item())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,H", [(1, 64), (5, 96), (3, 2304), (2, 1002), (4, 10000)])
+def test_norm_kernels_against_float32(rows, H, dtype):
+    from glint_b200 import ops
+    torch.manual_seed(H)
+    x = torch.randn(rows, H, device=DEV) * 3
+    y = torch.randn(rows, H, device=DEV)
+    wa, wb = torch.randn(H, device=DEV) * 0.2, torch.randn(H, device=DEV) * 0.2
+    norm = lambda t, w, eps, off: t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps) * (off + w)
+    out = torch.empty(rows, H, device=DEV, dtype=dtype)
+    ops.rmsnorm(x, wa, out, 1e-6, 1.0)
+    tol = 1e-5 if dtype == torch.float32 else 0.05
+    assert (out.float() - norm(x, wa, 1e-6, 1.0)).abs().max().item() < tol
+    idx = torch.tensor([rows - 1, 0], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(2, H, device=DEV, dtype=dtype)
+    ops.rmsnorm(x, wa, out2, 1e-5, 0.0, idx)
+    assert (out2.float() - norm(x[[rows - 1, 0]], wa, 1e-5, 0.0)).abs().max().item() < tol
+    x2 = x.clone()
+    ops.add_rmsnorm(x2, y, (wa, 1e-6, 1.0), out, (wb, 1e-5, 1.0))
+    want_x = x + norm(y, wa, 1e-6, 1.0)
+    assert (x2 - want_x).abs().max().item() < 1e-5
+    assert (out.float() - norm(want_x, wb, 1e-5, 1.0)).abs().max().item() < tol
+    x3 = x.clone()
+    ops.add_rmsnorm(x3, y, None, None, None)
+    assert torch.equal(x3, x + y)
+
+
+@pytest.mark.parametrize("V", [512, 1000, 256000, 777])
+def test_argmax_takes_the_last_maximum(V):
+    from glint_b200 import ops
+    torch.manual_seed(V)
+    logits = torch.randn(3, V, device=DEV)
+    logits[1, 5] = logits[1, V - 3] = 99.0          # equal maxima: the later index wins
+    logits[2, 0] = 50.0
+    out = torch.empty(3, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, out)
+    assert out.tolist() == [int(torch.argmax(logits[0])), V - 3, 0]
+
+
+def test_sampling_kernel_against_the_plain_sampler():
+    from glint_b200 import ops
+    from tests.plain import sampler as ps
+    V = 1000
+    g = torch.Generator().manual_seed(0)
+    cases = [dict(temperature=0.8), dict(temperature=1.0), dict(temperature=1.3, top_k=20),
+             dict(temperature=0.7, top_p=0.9), dict(temperature=1.0, min_p=0.05),
+             dict(temperature=0.9, top_k=50, top_p=0.8, min_p=0.01)]
+    agree = total = 0
+    for ci, opts in enumerate(cases):
+        for trial in range(12):
+            logits = (torch.randn(V, generator=g) * 2.5).float()
+            rng_a, rng_b = ps.Xorshift64(100 * ci + trial), ps.Xorshift64(100 * ci + trial)
+            want = ps.sample(logits.numpy(), [], rng_a, **opts)
+            u = float(rng_b.next_f32())
+            dev = lambda v, dt: torch.tensor([v], dtype=dt, device=DEV)
+            out = torch.empty(1, dtype=torch.int32, device=DEV)
+            work = torch.empty(1, V, device=DEV)
+            ops.sample(logits.to(DEV).view(1, V), work, dev(opts["temperature"], torch.float32),
+                       dev(opts.get("top_k", 0), torch.int32), dev(opts.get("top_p", 1.0), torch.float32),
+                       dev(opts.get("min_p", 0.0), torch.float32), dev(u, torch.float32), out)
+            agree += int(out.item() == want)
+            total += 1
+    # sums are added in another order on the device: a draw that lands within rounding of a
+    # boundary of the cumulative distribution may fall to the neighbour
+    assert agree >= total - 2, (agree, total)
+
+
+def test_repeat_penalty_kernel():
+    from glint_b200 import ops
+    V = 64
+    logits = torch.tensor([[2.0] * V, [-1.0] * V], device=DEV)
+    work = torch.empty(2, V, device=DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    ops.apply_penalty(logits, work, i32([0, 2, 3]), i32([5, 9, 7]), i32([3, 1, 2]),
+                      torch.tensor([2.0, 1.5], device=DEV))
+    assert work[0, 5].item() == 0.25 and work[0, 9].item() == 1.0 and work[0, 0].item() == 2.0
+    assert work[1, 7].item() == pytest.approx(-2.25) and work[1, 5].item() == -1.0

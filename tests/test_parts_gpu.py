@@ -1,0 +1,210 @@
+"""Each part alone against the plain implementation's function of the same name, and a toy mixer
+with state of its own that is registered, built and stepped without touching the package."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import TINY, make_model_dir, random_tokens
+from tests.plain import model as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+PART_TOL = {"float32": 2e-5, "bfloat16": 0.06}
+
+
+@pytest.fixture(scope="module")
+def folder(tmp_path_factory):
+    return make_model_dir(tmp_path_factory.mktemp("parts"), "C")
+
+
+def _model(folder, dtype):
+    from glint_b200.engine.loading import build_engine, load_model
+    model = load_model(folder, dtype)
+    return model, build_engine(model, 512, num_slots=2, use_graphs=False)
+
+
+def _ctx(engine, slot, tokens):
+    from glint_b200.engine.step import StepContext, StepEntry
+    entries = [StepEntry(slot, tokens, [len(tokens) - 1])]
+    engine.cache.reserve([(slot, len(tokens))])
+    return StepContext(engine.cache, entries, engine._upload, engine._stage)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_parts_one_by_one(folder, dtype):
+    model, engine = _model(folder, dtype)
+    c, w = plain.read_config(folder), plain.read_weights(folder)
+    cfg = TINY["C"][0]
+    tokens = random_tokens(45, cfg["vocab_size"], 11)
+    tol = PART_TOL[dtype]
+    slot = engine.open()
+    ctx = _ctx(engine, slot, tokens)
+    act = model.rt.dtype
+    cpu = lambda t: t.float().cpu()
+
+    # embedding
+    x = model.embedding.forward(ctx.token_ids, ctx)
+    want_x = plain.embed(w["model.embed_tokens.weight"], tokens, c["hidden"])
+    assert (cpu(x) - want_x).abs().max().item() < 1e-5
+
+    block, lw = model.blocks[0], plain.layer_weights(w, 0)
+    # norm
+    n = block.pre_mixer_norm.forward(x)
+    want_n = plain.rms_norm(want_x, lw["in_norm"], c["eps"])
+    assert (cpu(n) - want_n).abs().max().item() < tol
+
+    # mixer (attention with its position encoding and cache write), layers 0 (window) and 1 (global)
+    for layer in (0, 1):
+        blk, lwl = model.blocks[layer], plain.layer_weights(w, layer)
+        nin = plain.rms_norm(want_x, lwl["in_norm"], c["eps"])
+        y = blk.mixer.forward(nin.to(act).to(DEV), ctx, engine.cache.views[layer], None)
+        want_y = plain.attention(nin.to(act).float(), lwl, c, layer)
+        assert (cpu(y) - want_y).abs().max().item() < tol * 2, layer
+
+    # feed-forward
+    f = torch.randn(45, c["hidden"]) * 0.5
+    d = block.feed_forward.forward(f.to(act).to(DEV), ctx)
+    want_d = plain.feed_forward(f.to(act).float(), lw)
+    assert (cpu(d) - want_d).abs().max().item() < tol * 2
+
+    # head with its soft cap
+    rows = torch.randn(3, c["hidden"])
+    logits = model.head.forward(rows.to(act).to(DEV), ctx)
+    head_w = w["lm_head.weight"]
+    want_l = plain.softcap(rows.to(act).float() @ head_w.T, c["final_cap"])
+    assert (cpu(logits) - want_l).abs().max().item() < tol * 3
+
+    # whole block, residual updated in place
+    xb = want_x.clone().to(DEV)
+    model.blocks[2].forward(xb, None, ctx, engine.cache.views[2], None, None, False)
+    want_b = plain.block(want_x, plain.layer_weights(w, 2), c, 2)
+    assert (cpu(xb) - want_b).abs().max().item() < (1e-4 if dtype == "float32" else 0.15)
+    model.rt.check_status()
+
+
+# ---- a toy mixer with state, defined here, never part of the package -------------------------------------
+
+
+def _register_toy():
+    from glint_b200.cache import SlotStateNeed
+    from glint_b200.config import BlockSpec, LayerCall, ModelSpec, PartSpec, register_architecture
+    from glint_b200.parts import Part, TensorNeed, register_part
+
+    class DecayMixer(Part):
+        """s_t = decay * s_{t-1} + x_t ; y_t = s_t W^T.  Its state is one vector per request."""
+
+        def __init__(self, rt, params, tensors):
+            super().__init__(rt, params, tensors)
+            self.size, self.decay = int(params["size"]), float(params["decay"])
+
+        def cache_need(self):
+            return SlotStateNeed((self.size,), torch.float32)
+
+        def needs(self):
+            return [TensorNeed(self.names["w"], (self.size, self.size))]
+
+        def bind(self, tensors):
+            self.w = tensors[self.names["w"]].float()
+
+        def forward(self, normed, ctx, view, state):
+            out = torch.empty(normed.shape, dtype=torch.float32, device=normed.device)
+            x = normed.float()
+            for i, slot in enumerate(ctx.h_seq_slot):          # tokens of one request are sequential
+                s = state[slot]
+                for t in range(ctx.h_cu_seqlens[i], ctx.h_cu_seqlens[i + 1]):
+                    s = self.decay * s + x[t]
+                    out[t] = s @ self.w.T
+                state[slot] = s
+            return out
+
+    class ToyConfig:
+        def __init__(self, obj):
+            self.obj = obj
+
+        @classmethod
+        def from_dict(cls, obj):
+            return cls(obj)
+
+        def to_dict(self):
+            return dict(self.obj)
+
+        def model_spec(self):
+            o = self.obj
+            H, V = o["hidden_size"], o["vocab_size"]
+            norm = lambda name: PartSpec("rmsnorm", {"size": H, "eps": 1e-5, "unit_offset": False}, {"weight": name})
+            ffn = lambda p: PartSpec("gated", {"hidden_size": H, "intermediate_size": o["intermediate_size"],
+                                               "activation": "silu"},
+                                     {"gate": p + "gate", "up": p + "up", "down": p + "down"})
+            toy = PartSpec("decay_toy", {"size": H, "decay": o["decay"]}, {"w": "layers.0.mix.w"})
+            attn = PartSpec("attention", {"hidden_size": H, "num_heads": 2, "num_kv_heads": 1, "head_dim": 16,
+                                          "score_multiplier": 0.25, "softcap": None, "window": None,
+                                          "position": PartSpec("rope", {"head_dim": 16, "theta": 10000.0})},
+                            {"q": "layers.1.q", "k": "layers.1.k", "v": "layers.1.v", "o": "layers.1.o"})
+            blocks = [BlockSpec(toy, ffn("layers.0."), pre_mixer_norm=norm("layers.0.n1"), pre_ffn_norm=norm("layers.0.n2")),
+                      BlockSpec(attn, ffn("layers.1."), pre_mixer_norm=norm("layers.1.n1"), pre_ffn_norm=norm("layers.1.n2"))]
+            # layer 0 runs twice (each run has a state of its own); the last entry reads entry 1's cache
+            order = [LayerCall(0), LayerCall(1), LayerCall(0), LayerCall(1, cache_of=1)]
+            return ModelSpec("ToyForCausalLM", V, H, o["max_position_embeddings"],
+                             PartSpec("embedding", {"vocab_size": V, "hidden_size": H, "scale": 1.0}, {"table": "embed"}),
+                             blocks, order, norm("final_norm"),
+                             PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "softcap": None, "tie": True},
+                                      {"weight": "head", "tied_to": "embed"}))
+
+    register_part("mixer", "decay_toy", DecayMixer)
+    register_architecture("ToyForCausalLM", ToyConfig)
+    return ToyConfig
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    import json
+    from glint_b200.engine.loading import build_engine, load_model
+    from glint_b200.engine.step import StepEntry
+    from glint_b200.weights import model_needs, random_tensors, write_safetensors
+    ToyConfig = _register_toy()
+    obj = {"architectures": ["ToyForCausalLM"], "hidden_size": 32, "vocab_size": 97, "intermediate_size": 48,
+           "decay": 0.9, "max_position_embeddings": 128}
+    folder = str(tmp_path / "toy")
+    os.makedirs(folder)
+    json.dump(obj, open(os.path.join(folder, "config.json"), "w"))
+    tensors = random_tensors(model_needs(ToyConfig(obj)), seed=3, std=0.2, norm_std=1.0, dtype=torch.float32)
+    for k in list(tensors):
+        if k.endswith("n1") or k.endswith("n2") or k == "final_norm":
+            tensors[k] = tensors[k].abs() + 0.5
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
+
+    model = load_model(folder, "float32")
+    assert type(model.blocks[0].mixer).__name__ == "DecayMixer"
+    engine = build_engine(model, 256, num_slots=3, use_graphs=False)
+    needs, cache_of = model.cache_needs()
+    assert [type(n).__name__ for n in needs] == ["SlotStateNeed", "PagedKVNeed", "SlotStateNeed", "PagedKVNeed"]
+    assert cache_of == [None, None, None, 1] and len(engine.cache.groups) == 1
+    assert engine.cache.states[0].shape == (3, 32) and engine.cache.states[2].shape == (3, 32)
+    assert engine.cache.states[0].data_ptr() != engine.cache.states[2].data_ptr()
+
+    toks_a, toks_b = random_tokens(23, 97, 1), random_tokens(17, 97, 2)
+    # whole
+    s = engine.open()
+    whole_a = engine.step([StepEntry(s, toks_a, list(range(23)))]).cpu()
+    engine.close(s)
+    s = engine.open()
+    whole_b = engine.step([StepEntry(s, toks_b, list(range(17)))]).cpu()
+    engine.close(s)
+    # cut into portions and mixed with the other request; the state must carry across steps and a
+    # reused slot must start from zero
+    sa, sb = engine.open(), engine.open()
+    got_a, got_b = [], []
+    got_a.append(engine.step([StepEntry(sa, toks_a[:7], list(range(7)))]).cpu())
+    out = engine.step([StepEntry(sb, toks_b[:5], list(range(5))), StepEntry(sa, toks_a[7:9], [0, 1])]).cpu()
+    got_b.append(out[:5]); got_a.append(out[5:])
+    out = engine.step([StepEntry(sa, toks_a[9:], list(range(14))), StepEntry(sb, toks_b[5:6], [0])]).cpu()
+    got_a.append(out[:14]); got_b.append(out[14:])
+    got_b.append(engine.step([StepEntry(sb, toks_b[6:], list(range(11)))]).cpu())
+    assert (torch.cat(got_a) - whole_a).abs().max().item() < 1e-4
+    assert (torch.cat(got_b) - whole_b).abs().max().item() < 1e-4
+    assert whole_a.abs().max().item() > 1e-3
+    engine.close(sa); engine.close(sb)
+    model.rt.check_status()
