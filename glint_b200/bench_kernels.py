@@ -86,7 +86,8 @@ def bench_attention_decode(batch, context, nh=8, nkv=4, hd=256, page=16, window=
             "GB/s": round(nbytes / us / 1e3, 1)}
 
 
-def bench_attention_prefill(tokens, before=0, nh=8, nkv=4, hd=256, page=16, window=None, cap=50.0, iters=10):
+def bench_attention_prefill(tokens, before=0, nh=8, nkv=4, hd=256, page=16, window=None, cap=50.0, iters=10,
+                            kernel="tcgen05"):
     from . import ops_tensor
     total = before + tokens
     n_pages = (total + page - 1) // page
@@ -98,12 +99,13 @@ def bench_attention_prefill(tokens, before=0, nh=8, nkv=4, hd=256, page=16, wind
     cu = torch.tensor([0, tokens], dtype=torch.int32, device=DEV)
     start = torch.tensor([before], dtype=torch.int32, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    fn = lambda i: ops_tensor.attention_prefill(q, k, v, cu, start, table, out, 1, tokens, nh, nkv, hd, page, n_pages,
-                                                1 / 16.0, cap, window, status)
+    run = ops_tensor.attention_tcgen05 if kernel == "tcgen05" else ops_tensor.attention_prefill
+    fn = lambda i: run(q, k, v, cu, start, table, out, 1, tokens, nh, nkv, hd, page, n_pages, 1 / 16.0, cap, window,
+                       status)
     us = _time(fn, 1, iters)
     keys = sum(min(p + 1, window) if window else p + 1 for p in range(before, total))
     flops = 4.0 * nh * hd * keys
-    return {"kernel": "attention_prefill", "tokens": tokens, "before": before, "window": window, "us": round(us, 2),
+    return {"kernel": "attention_" + kernel, "tokens": tokens, "before": before, "window": window, "us": round(us, 2),
             "TFLOP/s": round(flops / us / 1e6, 1)}
 
 
@@ -156,6 +158,7 @@ def main():
         for name, M, N, K, gated in gemma2_2b_decode_cases(a.tokens)[:4]:
             out.append(dict(bench_gemm(M, N, K, gated, 0, a.iters), name=name))
         out.append(bench_attention_prefill(a.tokens, iters=a.iters))
+        out.append(bench_attention_prefill(a.tokens, iters=a.iters, kernel="mma"))
         out.extend(bench_rows(a.tokens))
     elif a.what == "attention-decode":
         out.append(bench_attention_decode(a.batch, a.context, window=a.window or None, splits=a.splits or None,

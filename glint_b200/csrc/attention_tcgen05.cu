@@ -1,0 +1,360 @@
+// Flash attention for prompt portions over the paged cache on the 5th-generation tensor cores.
+//
+// grid = (query tiles, requests of the step, kv heads); one block per SM.  A block owns 128
+// query rows: rows are (token, query head of the group) pairs, so the heads that share a kv head
+// share every key/value tile.  Keys come in tiles of 64 whose boundaries are multiples of 64 in
+// absolute position.
+//   warp 0     TMA: the query tile once (one 4-D box per 64 columns), then key and value tiles
+//              page by page into a two-deep ring (every lane issues one box)
+//   warp 1     tcgen05.mma: S = Q K^T into tensor memory, then O += P V (V is the MN-major operand)
+//   warps 2-5  softmax: each thread owns one row of S (tcgen05.ld), scales, soft-caps and masks it
+//              by absolute position, keeps the running max and sum in 32-bit, writes P as bfloat16
+//              into shared memory in the swizzled operand layout, and rescales its row of O in
+//              tensor memory only when the running max grew by more than 8 (the result is the same:
+//              the sum carries the same stale max)
+// Formulas: src/tensor/flash.rs:65-123 (online softmax), :76-87 (multiplier, cap * tanh(x / cap)),
+// src/transformer/forward.rs:933-942 (window per absolute position).  The soft cap uses
+// tanh.approx and the exponentials ex2.approx; sums and maxima are float32.
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace glint {
+
+constexpr int FA_M = 128;             // query rows per block
+constexpr int FA_N = 64;              // keys per tile
+constexpr int FA_THREADS = 192;
+constexpr int FA_Q_SUB = FA_M * 128;  // bytes of a 64-column slice of the query tile
+constexpr int FA_KV_SUB = FA_N * 128; // bytes of a 64-column slice of a key or value tile
+constexpr int FA_P_BYTES = FA_M * 128;
+constexpr float FA_RESCALE = 8.0f;
+
+struct FaParams {
+  const int* cu_seqlens;
+  const int* seq_start;
+  const int* block_table;
+  int max_pages;
+  __nv_bfloat16* out;
+  int nh, nkv, hd, page_size, num_pages;
+  float multiplier, cap;
+  int window;
+  int* status;
+};
+
+struct FaShared {
+  uint64_t q_full, s_full, p_ready, o_full;
+  uint64_t kv_full[2], kv_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(FA_THREADS, 1)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, const FaParams p) {
+  extern __shared__ uint8_t fa_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fa_raw) + 1023) & ~(uintptr_t)1023);
+  const int hd = p.hd, hd16 = hd >> 4, nsub = (hd + 63) >> 6;
+  const int G = p.nh / p.nkv;
+  const int tok_per_tile = FA_M / G;
+  uint8_t* sq = smem;
+  uint8_t* sk = sq + (size_t)nsub * FA_Q_SUB;            // [2][nsub][64 keys x 128 B]
+  uint8_t* sv = sk + (size_t)2 * nsub * FA_KV_SUB;
+  uint8_t* sp = sv + (size_t)2 * nsub * FA_KV_SUB;
+  FaShared* sh = reinterpret_cast<FaShared*>(sp + FA_P_BYTES);
+
+  const int seq = blockIdx.y, kvh = blockIdx.z;
+  const int t_begin = p.cu_seqlens[seq];
+  const int q_len = p.cu_seqlens[seq + 1] - t_begin;
+  const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;        // long tiles first
+  const int tok0 = tile * tok_per_tile;
+  if (tok0 >= q_len) return;
+  const int n_tok = min(tok_per_tile, q_len - tok0);
+  const int n_rows = n_tok * G;
+  const int pos0 = p.seq_start[seq] + tok0;
+  const int pos_last = pos0 + n_tok - 1;
+  const int kv_first = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int kv_begin = kv_first & ~(FA_N - 1);
+  const int n_tiles = (pos_last - kv_begin) / FA_N + 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    tc::mbar_init(&sh->q_full, 1);
+    tc::mbar_init(&sh->s_full, 1);
+    tc::mbar_init(&sh->p_ready, 128);
+    tc::mbar_init(&sh->o_full, 1);
+    for (int b = 0; b < 2; ++b) {
+      tc::mbar_init(&sh->kv_full[b], 1);
+      tc::mbar_init(&sh->kv_empty[b], 1);
+    }
+    sh->abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::tma_prefetch_desc(&map_q);
+    tc::tma_prefetch_desc(&map_k);
+    tc::tma_prefetch_desc(&map_v);
+  }
+  if (warp == 1) tc::tmem_alloc(&sh->tmem_base, 512);
+  tc::fence_before_thread_sync();
+  __syncthreads();
+  tc::fence_after_thread_sync();
+  const uint32_t tmem_s = sh->tmem_base;
+  const uint32_t tmem_o = tmem_s + FA_N;
+  volatile int* abort_flag = &sh->abort_flag;
+
+  if (warp == 0) {
+    // ---- producer ---------------------------------------------------------------------------------
+    if (lane == 0) {
+      tc::mbar_expect_tx(&sh->q_full, (uint32_t)nsub * tok_per_tile * G * 128);
+      for (int sub = 0; sub < nsub; ++sub)
+        tc::tma_load_4d(sq + (size_t)sub * FA_Q_SUB, &map_q, &sh->q_full, sub * 64, 0, kvh, t_begin + tok0);
+    }
+    const int ppt = FA_N / p.page_size;                        // pages per tile
+    const int boxes = 2 * ppt * nsub;
+    const int* table = p.block_table + (size_t)seq * p.max_pages;
+    const int page_lo = kv_first / p.page_size, page_hi = pos_last / p.page_size;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int b = j & 1;
+      bool ok = true;
+      if (j >= 2) ok = tc::mbar_wait(&sh->kv_empty[b], ((j >> 1) - 1) & 1, abort_flag);
+      if (!__all_sync(0xffffffffu, ok)) break;
+      if (lane == 0) tc::mbar_expect_tx(&sh->kv_full[b], (uint32_t)2 * nsub * FA_KV_SUB);
+      __syncwarp();
+      const int first_page = (kv_begin + j * FA_N) / p.page_size;
+      for (int bi = lane; bi < boxes; bi += 32) {
+        const int which = bi / (ppt * nsub);                   // 0: keys, 1: values
+        const int rem = bi % (ppt * nsub);
+        const int pi = rem / nsub, sub = rem % nsub;
+        const int page_idx = first_page + pi;
+        int page = 0;                                          // pages outside the range are masked below;
+        if (page_idx >= page_lo && page_idx <= page_hi) {      // they are filled from page 0 (finite values)
+          page = table[page_idx];
+          if (page < 0 || page >= p.num_pages) {
+            atomicExch(p.status, 3);
+            page = 0;
+          }
+        }
+        uint8_t* dst = (which ? sv : sk) + ((size_t)b * nsub + sub) * FA_KV_SUB + (size_t)pi * p.page_size * 128;
+        tc::tma_load_2d(dst, which ? &map_v : &map_k, &sh->kv_full[b], sub * 64, (page * p.nkv + kvh) * p.page_size);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer -------------------------------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc_s = tc::idesc_bf16_f32(FA_M, FA_N);
+      const uint32_t idesc_o = tc::idesc_bf16_f32_b_mn(FA_M, hd);
+      const uint32_t q_addr = tc::smem_u32(sq), k_addr = tc::smem_u32(sk), v_addr = tc::smem_u32(sv);
+      const uint32_t p_addr = tc::smem_u32(sp);
+      bool ok = tc::mbar_wait(&sh->q_full, 0, abort_flag);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int b = j & 1;
+        ok = tc::mbar_wait(&sh->kv_full[b], (j >> 1) & 1, abort_flag);
+        if (!ok) break;
+        tc::fence_after_thread_sync();
+        for (int ks = 0; ks < hd16; ++ks) {
+          const uint32_t a = q_addr + (ks >> 2) * FA_Q_SUB + (ks & 3) * 32;
+          const uint32_t bb = k_addr + (b * nsub + (ks >> 2)) * FA_KV_SUB + (ks & 3) * 32;
+          tc::mma_bf16_ss(tmem_s, tc::smem_desc_k_sw128(a), tc::smem_desc_k_sw128(bb), idesc_s, ks > 0);
+        }
+        tc::mma_commit(&sh->s_full);
+        ok = tc::mbar_wait(&sh->p_ready, j & 1, abort_flag);
+        if (!ok) break;
+        tc::fence_after_thread_sync();
+        for (int kk = 0; kk < FA_N / 16; ++kk) {
+          const uint64_t da = tc::smem_desc_k_sw128(p_addr + kk * 32);
+          const uint64_t db = tc::smem_desc_mn_sw128(v_addr + b * nsub * FA_KV_SUB + kk * 2048, FA_KV_SUB, 1024);
+          tc::mma_bf16_ss(tmem_o, da, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc::mma_commit(&sh->kv_empty[b]);
+      }
+      tc::mma_commit(&sh->o_full);
+    }
+  } else {
+    // ---- softmax, correction and epilogue: thread <-> row of the tile ---------------------------------
+    const int quarter = warp & 3;                              // the warp's 32 lanes of tensor memory
+    const int r = quarter * 32 + lane;
+    const bool rv = r < n_rows;
+    const int qpos = pos0 + (rv ? r / G : 0);
+    const int lo = p.window > 0 ? qpos - p.window + 1 : 0;
+    const uint32_t lane_base = ((uint32_t)(quarter * 32) << 16);
+    const float LOG2E = 1.4426950408889634f;
+    const float in_scale = p.cap > 0.f ? p.multiplier / p.cap : p.multiplier;
+    const float out_scale = p.cap > 0.f ? p.cap * LOG2E : LOG2E;   // scores are kept in log2 units
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      ok = tc::mbar_wait(&sh->s_full, j & 1, abort_flag);
+      if (!ok) break;
+      tc::fence_after_thread_sync();
+      uint32_t raw[FA_N];
+#pragma unroll
+      for (int c0 = 0; c0 < FA_N; c0 += 16) tc::tmem_ld_16(tmem_s + lane_base + c0, raw + c0);
+      tc::tmem_ld_wait();
+      const int key0 = kv_begin + j * FA_N;
+      float x[FA_N];
+      float mt = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < FA_N; ++c) {
+        const int key = key0 + c;
+        const bool valid = rv && key <= qpos && key >= lo;
+        float v = __uint_as_float(raw[c]) * in_scale;
+        if (p.cap > 0.f) v = tc::tanh_approx(v);
+        v = valid ? v * out_scale : -INFINITY;
+        x[c] = v;
+        mt = fmaxf(mt, v);
+      }
+      // rescale only when the running max grew by more than 8 (in natural units)
+      const bool grow = mt > m_used + FA_RESCALE * LOG2E;
+      float corr = 1.f;
+      if (grow) {
+        corr = m_used == -INFINITY ? 0.f : tc::exp2_approx(m_used - mt);
+        l *= corr;
+        m_used = mt;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        for (int c0 = 0; c0 < hd; c0 += 16) {
+          uint32_t o[16];
+          tc::tmem_ld_16(tmem_o + lane_base + c0, o);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+          tc::tmem_st_16(tmem_o + lane_base + c0, o);
+        }
+        tc::tmem_st_wait();
+      }
+      const float base = m_used == -INFINITY ? 0.f : m_used;
+      uint8_t* prow = sp + (size_t)r * 128;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        float pv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          pv[i] = tc::exp2_approx(x[ch * 8 + i] - base);
+          l += pv[i];
+        }
+        uint4 packed;
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(pv[0], pv[1]), h1 = __floats2bfloat162_rn(pv[2], pv[3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(pv[4], pv[5]), h3 = __floats2bfloat162_rn(pv[6], pv[7]);
+        packed.x = *reinterpret_cast<uint32_t*>(&h0);
+        packed.y = *reinterpret_cast<uint32_t*>(&h1);
+        packed.z = *reinterpret_cast<uint32_t*>(&h2);
+        packed.w = *reinterpret_cast<uint32_t*>(&h3);
+        *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = packed;
+      }
+      tc::fence_proxy_async();                 // the MMA reads P through the async proxy
+      tc::fence_before_thread_sync();
+      tc::mbar_arrive(&sh->p_ready);
+    }
+    // ---- epilogue: O / l as bfloat16 ----------------------------------------------------------------
+    if (ok) ok = tc::mbar_wait(&sh->o_full, 0, abort_flag);
+    if (ok) {
+      tc::fence_after_thread_sync();
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      __nv_bfloat16* orow = p.out + ((size_t)(t_begin + tok0 + (rv ? r / G : 0)) * p.nh + kvh * G + (rv ? r % G : 0)) * hd;
+      for (int c0 = 0; c0 < hd; c0 += 16) {
+        uint32_t o[16];
+        tc::tmem_ld_16(tmem_o + lane_base + c0, o);
+        tc::tmem_ld_wait();
+        if (rv) {
+          uint4 lo4, hi4;
+          __nv_bfloat162 h[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            h[i] = __floats2bfloat162_rn(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+          lo4 = make_uint4(*reinterpret_cast<uint32_t*>(&h[0]), *reinterpret_cast<uint32_t*>(&h[1]),
+                           *reinterpret_cast<uint32_t*>(&h[2]), *reinterpret_cast<uint32_t*>(&h[3]));
+          hi4 = make_uint4(*reinterpret_cast<uint32_t*>(&h[4]), *reinterpret_cast<uint32_t*>(&h[5]),
+                           *reinterpret_cast<uint32_t*>(&h[6]), *reinterpret_cast<uint32_t*>(&h[7]));
+          *reinterpret_cast<uint4*>(orow + c0) = lo4;
+          *reinterpret_cast<uint4*>(orow + c0 + 8) = hi4;
+        }
+      }
+    }
+  }
+  tc::fence_before_thread_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc::fence_after_thread_sync();
+    tc::tmem_dealloc(sh->tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && sh->abort_flag) atomicExch(p.status, 4);
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+
+typedef CUresult (*FaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static FaEncodeFn fa_encode_fn() {
+  static FaEncodeFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<FaEncodeFn>(ptr);
+  }
+  return fn;
+}
+
+static int fa_map(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
+                  const cuuint32_t* box) {
+  FaEncodeFn fn = fa_encode_fn();
+  if (!fn) return GLINT_ERR_BAD_ARG;
+  cuuint32_t elem[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? GLINT_OK : GLINT_ERR_BAD_ARG;
+}
+
+}  // namespace glint
+
+using namespace glint;
+
+// head_dim a multiple of 16 up to 256; at most 128 query heads per kv head; pages of 16, 32 or 64.
+GLINT_API int glint_attention_tcgen05_supported(int nh, int nkv, int hd, int page_size) {
+  return (nkv > 0 && nh % nkv == 0 && nh / nkv <= FA_M && hd % 16 == 0 && hd >= 16 && hd <= 256 &&
+          (page_size == 16 || page_size == 32 || page_size == 64)) ? 1 : 0;
+}
+
+// q, out: [T, nh * hd] bf16; pools [pages][nkv][page_size][hd] bf16.
+GLINT_API int glint_attention_tcgen05(const void* q, const void* k_pool, const void* v_pool, const int* cu_seqlens,
+                                      const int* seq_start, const int* block_table, int max_pages, void* out,
+                                      int T, int n_seqs, int max_q_len, int nh, int nkv, int hd, int page_size,
+                                      int num_pages, float multiplier, float cap, int window, int* status,
+                                      cudaStream_t stream) {
+  if (n_seqs <= 0 || max_q_len <= 0 || T <= 0) return GLINT_OK;
+  if (!glint_attention_tcgen05_supported(nh, nkv, hd, page_size)) return GLINT_ERR_UNSUPPORTED_SIZE;
+  if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) return GLINT_ERR_UNSUPPORTED_SIZE;
+  const int G = nh / nkv;
+  const int tok_per_tile = FA_M / G;
+  CUtensorMap map_q, map_k, map_v;
+  {
+    cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)G, (cuuint64_t)nkv, (cuuint64_t)T};
+    cuuint64_t strides[3] = {(cuuint64_t)hd * 2, (cuuint64_t)G * hd * 2, (cuuint64_t)nh * hd * 2};
+    cuuint32_t box[4] = {64, (cuuint32_t)G, 1, (cuuint32_t)tok_per_tile};
+    const int rc = fa_map(&map_q, q, 4, dims, strides, box);
+    if (rc != GLINT_OK) return rc;
+  }
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)num_pages * nkv * page_size};
+    cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+    int rc = fa_map(&map_k, k_pool, 2, dims, strides, box);
+    if (rc != GLINT_OK) return rc;
+    rc = fa_map(&map_v, v_pool, 2, dims, strides, box);
+    if (rc != GLINT_OK) return rc;
+  }
+  FaParams p;
+  p.cu_seqlens = cu_seqlens; p.seq_start = seq_start; p.block_table = block_table; p.max_pages = max_pages;
+  p.out = (__nv_bfloat16*)out; p.nh = nh; p.nkv = nkv; p.hd = hd; p.page_size = page_size; p.num_pages = num_pages;
+  p.multiplier = multiplier; p.cap = cap; p.window = window; p.status = status;
+  const int nsub = (hd + 63) / 64;
+  const int smem = nsub * FA_Q_SUB + 4 * nsub * FA_KV_SUB + FA_P_BYTES + (int)sizeof(FaShared) + 1024 + 64;
+  if (smem > 227 * 1024) return GLINT_ERR_UNSUPPORTED_SIZE;
+  dim3 grid((max_q_len + tok_per_tile - 1) / tok_per_tile, n_seqs, nkv);
+  if (grid.y > 65535 || grid.z > 65535) return GLINT_ERR_UNSUPPORTED_SIZE;
+  cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return (int)e;
+  attention_tcgen05_kernel<<<grid, FA_THREADS, smem, stream>>>(map_q, map_k, map_v, p);
+  return (int)cudaGetLastError();
+}

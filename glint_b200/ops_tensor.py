@@ -14,6 +14,7 @@ _SIGNATURES = {
     "glint_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _L, _F, _I, _I, _I, _P, _P, _P, _I, _P],
     "glint_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P],
     "glint_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
+    "glint_attention_tcgen05": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
 }
 
 _lib = None
@@ -133,10 +134,31 @@ def attention_prefill(q, k_pool, v_pool, cu_seqlens, seq_start, block_table, out
               "attention_prefill")
 
 
+def tcgen05_attention_supported(nh, nkv, hd, page_size):
+    return (nkv > 0 and nh % nkv == 0 and nh // nkv <= 128 and hd % 16 == 0 and 16 <= hd <= 256
+            and page_size in (16, 32, 64))
+
+
+def attention_tcgen05(q, k_pool, v_pool, cu_seqlens, seq_start, block_table, out, n_seqs, max_q_len, nh, nkv, hd,
+                      page_size, num_pages, multiplier, cap, window, status):
+    """Flash attention of prompt portions on tcgen05 tensor cores (any mix of lengths)."""
+    ops.require(q, torch.bfloat16, "q"); ops.require(k_pool, torch.bfloat16, "k_pool")
+    ops.require(v_pool, torch.bfloat16, "v_pool"); ops.require(out, torch.bfloat16, "out")
+    ops.check(lib().glint_attention_tcgen05(ops.ptr(q), ops.ptr(k_pool), ops.ptr(v_pool), ops.ptr(cu_seqlens),
+                                            ops.ptr(seq_start), ops.ptr(block_table), block_table.shape[1],
+                                            ops.ptr(out), q.shape[0], n_seqs, max_q_len, nh, nkv, hd, page_size,
+                                            num_pages, multiplier, cap or 0.0, window or 0, ops.ptr(status),
+                                            ops.stream()), "attention_tcgen05")
+
+
 def attention(q, view, ctx, out, nh, nkv, hd, multiplier, cap, window, status):
     """Route a step's attention: single tokens to the split kernel, portions to the tiled one."""
     table = ctx.block_table(view.group)
-    if (ctx.max_seq_len > 1 or not decode_supported(nh, nkv, hd, view.page_size)) and prefill_supported(nh, nkv, hd):
+    if ctx.max_seq_len > 1 and tcgen05_attention_supported(nh, nkv, hd, view.page_size):
+        attention_tcgen05(q, view.k, view.v, ctx.cu_seqlens, ctx.seq_start, table, out, ctx.num_seqs,
+                          ctx.max_seq_len, nh, nkv, hd, view.page_size, view.num_pages, multiplier, cap, window,
+                          status)
+    elif (ctx.max_seq_len > 1 or not decode_supported(nh, nkv, hd, view.page_size)) and prefill_supported(nh, nkv, hd):
         attention_prefill(q, view.k, view.v, ctx.cu_seqlens, ctx.seq_start, table, out, ctx.num_seqs,
                           ctx.max_seq_len, nh, nkv, hd, view.page_size, view.num_pages, multiplier, cap, window,
                           status)

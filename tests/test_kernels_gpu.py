@@ -94,7 +94,7 @@ def test_gemm_gated_against_float32(M, I, K, act):
 
 # ---- attention over a paged cache -----------------------------------------------------------------
 
-def _paged_case(seq_lens_before, seq_lens_new, nkv, hd, page_size, dtype, seed, hot=None):
+def _paged_case(seq_lens_before, seq_lens_new, nkv, hd, page_size, dtype, seed, hot=None, v_poison=float("nan")):
     """Random keys/values for every request laid into shuffled pages.  Returns the pools, the block
     table [requests, max_pages], and the dense per-request K, V [len, nkv, hd]."""
     g = torch.Generator().manual_seed(seed)
@@ -103,7 +103,7 @@ def _paged_case(seq_lens_before, seq_lens_new, nkv, hd, page_size, dtype, seed, 
     n_pages = sum(-(-t // page_size) for t in totals) + 3
     perm = torch.randperm(n_pages, generator=g).tolist()
     k_pool = torch.full((n_pages, nkv, page_size, hd), float("nan"))
-    v_pool = torch.full((n_pages, nkv, page_size, hd), float("nan"))
+    v_pool = torch.full((n_pages, nkv, page_size, hd), v_poison)
     table = torch.full((len(totals), max_pages), -1, dtype=torch.int32)
     dense = []
     for s, total in enumerate(totals):
@@ -149,15 +149,19 @@ ATT_CASES = [
 ]
 
 
-@pytest.mark.parametrize("kernel", ["plain32", "plain16", "decode", "prefill"])
+@pytest.mark.parametrize("kernel", ["plain32", "plain16", "decode", "prefill", "tcgen05"])
 @pytest.mark.parametrize("case", range(len(ATT_CASES)))
 def test_attention_kernels_against_float32(case, kernel):
     from glint_b200 import ops, ops_tensor
     nh, nkv, hd, page, before, new, window, cap = ATT_CASES[case]
     if kernel == "prefill" and not ops_tensor.prefill_supported(nh, nkv, hd):
         pytest.skip("size outside the tiled kernel's range (the split kernel takes it)")
+    if kernel == "tcgen05" and not ops_tensor.tcgen05_attention_supported(nh, nkv, hd, page):
+        pytest.skip("size outside the tcgen05 kernel's range")
     dtype = torch.float32 if kernel == "plain32" else torch.bfloat16
-    k_pool, v_pool, table, dense = _paged_case(before, new, nkv, hd, page, dtype, seed=case)
+    # the tcgen05 kernel multiplies masked keys' values by exactly zero: its poison must be finite
+    k_pool, v_pool, table, dense = _paged_case(before, new, nkv, hd, page, dtype, seed=case,
+                                               v_poison=3.0e4 if kernel == "tcgen05" else float("nan"))
     seq_of_token, positions = [], []
     for s, (b, n) in enumerate(zip(before, new)):
         seq_of_token += [s] * n
@@ -184,22 +188,24 @@ def test_attention_kernels_against_float32(case, kernel):
         cu = [0]
         for n in new:
             cu.append(cu[-1] + n)
-        ops_tensor.attention_prefill(qd, k_pool, v_pool, i32(cu), i32(before), table, out, len(new), max(new), nh,
-                                     nkv, hd, page, k_pool.shape[0], mult, cap, window, status)
+        fn = ops_tensor.attention_prefill if kernel == "prefill" else ops_tensor.attention_tcgen05
+        fn(qd, k_pool, v_pool, i32(cu), i32(before), table, out, len(new), max(new), nh, nkv, hd, page,
+           k_pool.shape[0], mult, cap, window, status)
     got = out.float().cpu().reshape(T, nh, hd)
     assert int(status.item()) == 0
     tol = 2e-5 if kernel == "plain32" else 0.03
     assert (got - want).abs().max().item() < tol, (got - want).abs().max().item()
 
 
-@pytest.mark.parametrize("kernel", ["plain16", "decode", "prefill"])
+@pytest.mark.parametrize("kernel", ["plain16", "decode", "prefill", "tcgen05"])
 def test_attention_finds_one_far_key_among_hundreds(kernel):
     """One key far back is scaled so that its score stands out: the output must be its value row."""
     from glint_b200 import ops, ops_tensor
     nh, nkv, hd, page = 8, 4, 256, 16
     before, new = [900], [1]
     hot_pos = 37
-    k_pool, v_pool, table, dense = _paged_case(before, new, nkv, hd, page, torch.bfloat16, seed=9)
+    k_pool, v_pool, table, dense = _paged_case(before, new, nkv, hd, page, torch.bfloat16, seed=9,
+                                               v_poison=3.0e4 if kernel == "tcgen05" else float("nan"))
     k, v = dense[0]
     q = torch.zeros(1, nh, hd)
     for h in range(nh):
@@ -218,13 +224,14 @@ def test_attention_finds_one_far_key_among_hundreds(kernel):
         ops_tensor.attention_decode(qd, k_pool, v_pool, i32([900]), i32([0]), table, out, nh, nkv, hd, page,
                                     k_pool.shape[0], 1 / 16.0, None, None, status, 7)
     else:
-        ops_tensor.attention_prefill(qd, k_pool, v_pool, i32([0, 1]), i32([900]), table, out, 1, 1, nh, nkv, hd, page,
-                                     k_pool.shape[0], 1 / 16.0, None, None, status)
+        fn = ops_tensor.attention_prefill if kernel == "prefill" else ops_tensor.attention_tcgen05
+        fn(qd, k_pool, v_pool, i32([0, 1]), i32([900]), table, out, 1, 1, nh, nkv, hd, page, k_pool.shape[0], 1 / 16.0,
+           None, None, status)
     got = out.float().cpu().reshape(1, nh, hd)
     assert (got - want).abs().max().item() < 0.03
 
 
-@pytest.mark.parametrize("kernel", ["plain16", "decode", "prefill"])
+@pytest.mark.parametrize("kernel", ["plain16", "decode", "prefill", "tcgen05"])
 @pytest.mark.parametrize("pos", [63, 64, 79, 80, 200])
 def test_attention_window_edge(kernel, pos):
     """A hot key just outside the window must not be seen; the same key just inside must win.
@@ -233,7 +240,8 @@ def test_attention_window_edge(kernel, pos):
     nh, nkv, hd, page, window = 4, 2, 64, 16, 33
     for inside in (False, True):
         hot = pos - window + 1 if inside else pos - window
-        k_pool, v_pool, table, dense = _paged_case([pos], [1], nkv, hd, page, torch.bfloat16, seed=pos, hot=None)
+        k_pool, v_pool, table, dense = _paged_case([pos], [1], nkv, hd, page, torch.bfloat16, seed=pos, hot=None,
+                                                   v_poison=3.0e4 if kernel == "tcgen05" else float("nan"))
         k, v = dense[0]
         q = torch.zeros(1, nh, hd)
         for h in range(nh):
@@ -253,8 +261,9 @@ def test_attention_window_edge(kernel, pos):
             ops_tensor.attention_decode(qd, k_pool, v_pool, i32([pos]), i32([0]), table, out, nh, nkv, hd, page,
                                         k_pool.shape[0], 0.125, None, window, status, 2)
         else:
-            ops_tensor.attention_prefill(qd, k_pool, v_pool, i32([0, 1]), i32([pos]), table, out, 1, 1, nh, nkv, hd,
-                                         page, k_pool.shape[0], 0.125, None, window, status)
+            fn = ops_tensor.attention_prefill if kernel == "prefill" else ops_tensor.attention_tcgen05
+            fn(qd, k_pool, v_pool, i32([0, 1]), i32([pos]), table, out, 1, 1, nh, nkv, hd, page, k_pool.shape[0],
+               0.125, None, window, status)
         got = out.float().cpu().reshape(1, nh, hd)
         assert (got - want).abs().max().item() < 0.03, (inside, (got - want).abs().max().item())
 
