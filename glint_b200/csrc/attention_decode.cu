@@ -116,7 +116,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     tc::tma_prefetch_desc(&map_k);
     tc::tma_prefetch_desc(&map_v);
   }
+  pdl_launch_dependents();
   __syncthreads();
+  pdl_wait();                                   // the keys of this step and q come from earlier kernels
   volatile int* abort_flag = &sh->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -478,10 +480,10 @@ GLINT_API int glint_attention_decode(const void* q, const void* k_pool, const vo
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                          (int)smem);                                                            \
     if (e != cudaSuccess) return (int)e;                                                                        \
-    attention_decode_kernel<HD><<<grid, DEC_BLOCK, smem, stream>>>(map_k, map_v, qq, positions, token_seq,        \
-                                                                  block_table, max_pages, oo, partial, counters, \
-                                                                  nh, nkv, hd, page_size, num_pages, multiplier, \
-                                                                  cap, window, splits, stages, status);         \
+    e = launch_kernel(attention_decode_kernel<HD>, grid, dim3(DEC_BLOCK), (size_t)smem, stream, map_k, map_v, qq,      \
+                      positions, token_seq, block_table, max_pages, oo, partial, counters, nh, nkv, hd, page_size,      \
+                      num_pages, multiplier, cap, window, splits, stages, status);                                    \
+    if (e != cudaSuccess) return (int)e;                                                                        \
   }
   if (hd <= 64) LAUNCH(64)
   else if (hd <= 128) LAUNCH(128)

@@ -186,6 +186,8 @@ __global__ void __launch_bounds__(ROW_THREADS)
 rmsnorm_fast_kernel(const float* __restrict__ x, const int* __restrict__ row_index, const float* __restrict__ w,
                     S* __restrict__ out, int H, float eps, float offset) {
   __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const int H4 = H >> 2;
   const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(row_index ? row_index[r] : r) * H);
@@ -218,6 +220,8 @@ add_rmsnorm_fast_kernel(float* __restrict__ x, const float* __restrict__ y, cons
                         float eps_a, float offset_a, S* __restrict__ out, const float* __restrict__ w_b,
                         float eps_b, float offset_b, int H) {
   __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const int H4 = H >> 2;
   float4* xr = reinterpret_cast<float4*>(x + (size_t)r * H);
@@ -286,6 +290,8 @@ rope_kv_write_fast_kernel(const float* __restrict__ qkv, const int* __restrict__
                           S* __restrict__ k_pool, S* __restrict__ v_pool, int nh, int nkv, int hd, int page_size,
                           int num_pages, int* __restrict__ status) {
   extern __shared__ float trig[];   // cos[half], sin[half]
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half = hd >> 1;
@@ -340,6 +346,8 @@ rope_kv_write_fast_kernel(const float* __restrict__ qkv, const int* __restrict__
 __global__ void embed_scale_fast_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
                                         float* __restrict__ x, int H, float scale, int vocab,
                                         int* __restrict__ status) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool bad = id < 0 || id >= vocab;
@@ -409,8 +417,7 @@ GLINT_API int glint_embed_scale(const void* table, int dtype, const int* ids, fl
                                 float scale, int vocab, int* status, cudaStream_t stream) {
   if (T <= 0) return GLINT_OK;
   if (dtype == GLINT_DTYPE_BF16 && H % 8 == 0 && ((uintptr_t)table & 15) == 0 && ((uintptr_t)x & 15) == 0) {
-    embed_scale_fast_kernel<<<T, 128, 0, stream>>>((const __nv_bfloat16*)table, ids, x, H, scale, vocab, status);
-    return (int)cudaGetLastError();
+    return (int)launch_kernel(embed_scale_fast_kernel, dim3(T), dim3(128), 0, stream, (const __nv_bfloat16*)table, ids, x, H, scale, vocab, status);
   }
   DISPATCH(dtype, embed_scale_kernel<S><<<T, 256, 0, stream>>>((const S*)table, ids, x, H, scale, vocab, status));
   return (int)cudaGetLastError();
@@ -420,7 +427,8 @@ GLINT_API int glint_rmsnorm(const float* x, const int* row_index, const float* w
                             int rows, int H, float eps, float offset, cudaStream_t stream) {
   if (rows <= 0) return GLINT_OK;
   const int iters = fast_iters(H, x, w, out, nullptr);
-#define RMS_FAST(N) DISPATCH(dtype, rmsnorm_fast_kernel<S, N><<<rows, ROW_THREADS, 0, stream>>>(x, row_index, w, (S*)out, H, eps, offset))
+  int rc = 0;
+#define RMS_FAST(N) DISPATCH(dtype, rc = (int)launch_kernel(rmsnorm_fast_kernel<S, N>, dim3(rows), dim3(ROW_THREADS), 0, stream, x, row_index, w, (S*)out, H, eps, offset))
   if (iters == 1) { RMS_FAST(1); }
   else if (iters == 2) { RMS_FAST(2); }
   else if (iters > 0 && iters <= 4) { RMS_FAST(4); }
@@ -430,7 +438,7 @@ GLINT_API int glint_rmsnorm(const float* x, const int* row_index, const float* w
     DISPATCH(dtype, rmsnorm_kernel<S><<<rows, threads, 0, stream>>>(x, row_index, w, (S*)out, H, eps, offset));
   }
 #undef RMS_FAST
-  return (int)cudaGetLastError();
+  return rc ? rc : (int)cudaGetLastError();
 }
 
 GLINT_API int glint_add_rmsnorm(float* x, const float* y, const float* w_a, float eps_a, float offset_a,
@@ -439,7 +447,8 @@ GLINT_API int glint_add_rmsnorm(float* x, const float* y, const float* w_a, floa
   if (rows <= 0) return GLINT_OK;
   int iters = fast_iters(H, x, y, out, w_a);
   if (w_b && ((uintptr_t)w_b & 15)) iters = 0;
-#define ADD_FAST(N) DISPATCH(dtype, add_rmsnorm_fast_kernel<S, N><<<rows, ROW_THREADS, 0, stream>>>(x, y, w_a, eps_a, offset_a, (S*)out, w_b, eps_b, offset_b, H))
+  int rc = 0;
+#define ADD_FAST(N) DISPATCH(dtype, rc = (int)launch_kernel(add_rmsnorm_fast_kernel<S, N>, dim3(rows), dim3(ROW_THREADS), 0, stream, x, y, w_a, eps_a, offset_a, (S*)out, w_b, eps_b, offset_b, H))
   if (iters == 1) { ADD_FAST(1); }
   else if (iters == 2) { ADD_FAST(2); }
   else if (iters <= 4 && iters > 0) { ADD_FAST(4); }
@@ -450,7 +459,7 @@ GLINT_API int glint_add_rmsnorm(float* x, const float* y, const float* w_a, floa
                                                                       eps_b, offset_b, H));
   }
 #undef ADD_FAST
-  return (int)cudaGetLastError();
+  return rc ? rc : (int)cudaGetLastError();
 }
 
 GLINT_API int glint_rope_kv_write(const float* qkv, const int* positions, const int* token_slot,
@@ -462,10 +471,12 @@ GLINT_API int glint_rope_kv_write(const float* qkv, const int* positions, const 
   if (hd % 2 || rot % 2 || rot > hd || rot < 0 || factor <= 0.f) return GLINT_ERR_BAD_ARG;
   if (rot == hd && hd % 8 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)q_out & 15) == 0 &&
       ((uintptr_t)k_pool & 15) == 0 && ((uintptr_t)v_pool & 15) == 0) {
-    DISPATCH(dtype, rope_kv_write_fast_kernel<S><<<T, 256, hd * sizeof(float), stream>>>(
-                        qkv, positions, token_slot, block_table, max_pages, inv_freq, factor, (S*)q_out,
-                        (S*)k_pool, (S*)v_pool, nh, nkv, hd, page_size, num_pages, status));
-    return (int)cudaGetLastError();
+    int rc = 0;
+    DISPATCH(dtype, rc = (int)launch_kernel(rope_kv_write_fast_kernel<S>, dim3(T), dim3(256), hd * sizeof(float), stream,
+                                            qkv, positions, token_slot, block_table, max_pages, inv_freq, factor,
+                                            (S*)q_out, (S*)k_pool, (S*)v_pool, nh, nkv, hd, page_size, num_pages,
+                                            status));
+    return rc ? rc : (int)cudaGetLastError();
   }
   DISPATCH(dtype, rope_kv_write_kernel<S><<<T, 256, 0, stream>>>(
                       qkv, positions, token_slot, block_table, max_pages, inv_freq, factor, rot, (S*)q_out,

@@ -80,6 +80,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const int stage_bytes = A_STAGE_BYTES * (DUAL ? 2 : 1) + b_stage_bytes;
   GemmShared* sh = reinterpret_cast<GemmShared*>(smem + (size_t)p.stages * stage_bytes);
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * GEMM_BM;
   const int m0 = blockIdx.y * p.BN;
@@ -113,46 +114,80 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   if (warp == 0) {
     // ---- producer: TMA loads of the weight tile(s) and the token tile --------------------------
     if (lane == 0) {
-      for (int i = 0; i < n_kb; ++i) {
-        const int s = i % p.stages;
-        const uint32_t round = i / p.stages;
-        if (!tc::mbar_wait(&sh->empty[s], (round & 1) ^ 1, abort_flag)) break;
-        uint8_t* stage = smem + (size_t)s * stage_bytes;
-        tc::mbar_expect_tx(&sh->full[s], stage_bytes);
+      // The weights are written by no kernel: the first ring of weight tiles is requested before
+      // waiting for the kernel that produces the tokens, and so streams in under its tail.
+      const int pre = min(n_kb, p.stages);
+      for (int i = 0; i < pre; ++i) {
+        uint8_t* stage = smem + (size_t)i * stage_bytes;
+        tc::mbar_expect_tx(&sh->full[i], stage_bytes);
         const int k = (kb_begin + i) * GEMM_BK;
+        tc::tma_load_2d(stage, &map_w, &sh->full[i], k, n0);
+        if (DUAL) tc::tma_load_2d(stage + A_STAGE_BYTES, &map_w, &sh->full[i], k, n0 + p.dual_offset);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tc::tma_load_2d(smem + (size_t)i * stage_bytes + A_STAGE_BYTES * (DUAL ? 2 : 1), &map_x, &sh->full[i],
+                        (kb_begin + i) * GEMM_BK, m0);
+      int s = 0;                 // pre == stages whenever this loop runs
+      uint32_t parity = 0;       // the first refill of a stage waits for its first release
+      int k = (kb_begin + pre) * GEMM_BK;
+      uint8_t* stage = smem;
+      for (int i = pre; i < n_kb; ++i, k += GEMM_BK) {
+        if (!tc::mbar_wait(&sh->empty[s], parity, abort_flag)) break;
+        tc::mbar_expect_tx(&sh->full[s], stage_bytes);
         tc::tma_load_2d(stage, &map_w, &sh->full[s], k, n0);
         if (DUAL) tc::tma_load_2d(stage + A_STAGE_BYTES, &map_w, &sh->full[s], k, n0 + p.dual_offset);
         tc::tma_load_2d(stage + A_STAGE_BYTES * (DUAL ? 2 : 1), &map_x, &sh->full[s], k, m0);
+        if (++s == p.stages) {
+          s = 0;
+          parity ^= 1;
+          stage = smem;
+        } else {
+          stage += stage_bytes;
+        }
       }
+    } else {
+      pdl_wait();
     }
   } else if (warp == 1) {
     // ---- MMA issuer ----------------------------------------------------------------------------
+    pdl_wait();
     if (lane == 0) {
+      // One thread issues everything, so its instruction count per K block is what bounds a
+      // launch with few tokens: stage index and phase are counters (no division), and the
+      // descriptors are built once and advanced by addition (the address field counts 16 bytes).
       const uint32_t idesc = tc::idesc_bf16_f32(GEMM_BM, p.BN);
-      bool ok = true;
-      for (int i = 0; i < n_kb && ok; ++i) {
-        const int s = i % p.stages;
-        const uint32_t round = i / p.stages;
-        ok = tc::mbar_wait(&sh->full[s], round & 1, abort_flag);
-        if (!ok) break;
+      const uint64_t a0 = tc::smem_desc_k_sw128(tc::smem_u32(smem));
+      const uint64_t b0 = tc::smem_desc_k_sw128(tc::smem_u32(smem) + A_STAGE_BYTES * (DUAL ? 2 : 1));
+      const uint64_t stage_step = (uint64_t)(stage_bytes >> 4);
+      int s = 0;
+      uint32_t phase = 0;
+      uint64_t da = a0, db = b0;
+      for (int i = 0; i < n_kb; ++i) {
+        if (!tc::mbar_wait(&sh->full[s], phase, abort_flag)) break;
         tc::fence_after_thread_sync();
-        const uint32_t a_addr = tc::smem_u32(smem + (size_t)s * stage_bytes);
-        const uint32_t b_addr = a_addr + A_STAGE_BYTES * (DUAL ? 2 : 1);
 #pragma unroll
         for (int k = 0; k < GEMM_BK / 16; ++k) {
-          const uint64_t db = tc::smem_desc_k_sw128(b_addr + k * 32);
           const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-          tc::mma_bf16_ss(tmem_base, tc::smem_desc_k_sw128(a_addr + k * 32), db, idesc, acc);
-          if (DUAL)
-            tc::mma_bf16_ss(tmem_base + p.BN, tc::smem_desc_k_sw128(a_addr + A_STAGE_BYTES + k * 32), db, idesc,
-                            acc);
+          tc::mma_bf16_ss(tmem_base, da + 2 * k, db + 2 * k, idesc, acc);
+          if (DUAL) tc::mma_bf16_ss(tmem_base + p.BN, da + (A_STAGE_BYTES >> 4) + 2 * k, db + 2 * k, idesc, acc);
         }
         tc::mma_commit(&sh->empty[s]);   // the stage is free once these MMAs have read it
+        if (++s == p.stages) {
+          s = 0;
+          phase ^= 1;
+          da = a0;
+          db = b0;
+        } else {
+          da += stage_step;
+          db += stage_step;
+        }
       }
       tc::mma_commit(&sh->tmem_full);    // the accumulator is complete
     }
   } else {
     // ---- epilogue: 4 warps, each owns the 32 accumulator lanes of its quarter --------------------
+    pdl_wait();
     const int q = warp & 3;
     const int f = n0 + q * 32 + lane;              // this thread's output feature
     tc::mbar_wait(&sh->tmem_full, 0, abort_flag);
@@ -341,11 +376,13 @@ GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int ou
   if (dual) {
     e = cudaFuncSetAttribute(gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) return (int)e;
-    gemm_tcgen05_kernel<true><<<grid, GEMM_THREADS, smem_bytes, stream>>>(map_w, map_x, p);
+    e = launch_kernel(gemm_tcgen05_kernel<true>, grid, dim3(GEMM_THREADS), smem_bytes, stream, map_w, map_x, p);
+    if (e != cudaSuccess) return (int)e;
   } else {
     e = cudaFuncSetAttribute(gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) return (int)e;
-    gemm_tcgen05_kernel<false><<<grid, GEMM_THREADS, smem_bytes, stream>>>(map_w, map_x, p);
+    e = launch_kernel(gemm_tcgen05_kernel<false>, grid, dim3(GEMM_THREADS), smem_bytes, stream, map_w, map_x, p);
+    if (e != cudaSuccess) return (int)e;
   }
   return (int)cudaGetLastError();
 }

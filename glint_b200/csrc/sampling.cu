@@ -56,6 +56,8 @@ __device__ __forceinline__ ArgBest block_argmax(ArgBest best, ArgBest* scratch) 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, long long row_stride, int V, int* __restrict__ out) {
   __shared__ ArgBest scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const float* row = logits + (size_t)blockIdx.x * row_stride;
   ArgBest best{-INFINITY, -1};
   if ((V & 3) == 0 && ((uintptr_t)row & 15) == 0) {
@@ -282,8 +284,9 @@ GLINT_API int glint_argmax(const float* logits, long long row_stride, int rows, 
                            cudaStream_t stream) {
   if (rows <= 0) return GLINT_OK;
   if (V <= 0) return GLINT_ERR_BAD_ARG;
-  argmax_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, V, out);
-  return (int)cudaGetLastError();
+  const cudaError_t e = launch_kernel(argmax_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, row_stride,
+                                      V, out);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 GLINT_API int glint_apply_penalty(const float* logits, long long row_stride, int rows, int V, float* work,
