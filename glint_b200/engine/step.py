@@ -186,10 +186,12 @@ class Engine:
                 raise RequestError(f"token id {lo if lo < 0 else hi} lies outside the vocabulary of "
                                    f"{self.vocab_size}")
 
-    def step(self, entries):
+    def step(self, entries, device_tokens=None):
         """Run the entries as one batch.  Returns float32 logits [wanted rows, vocab] on the
         device, in the order of the entries and of each ``want`` (``None`` if nothing is wanted).
-        The tensor is valid until the next step.
+        The tensor is valid until the next step.  ``device_tokens`` (int32 on the device, one
+        per token of the step) replaces the entries' token ids, for callers whose tokens never
+        leave the device (the entries then carry placeholders of the right count).
 
         Raises ``PagePoolExhausted`` before anything ran when the cache cannot hold the new
         tokens; the cache is then unchanged apart from pages that a window had already passed.
@@ -199,6 +201,8 @@ class Engine:
         self.cache.reserve(rows)
         with torch.cuda.device(self.rt.device):
             ctx = StepContext(self.cache, entries, self._upload, self._stage)
+            if device_tokens is not None:
+                ctx.token_ids.copy_(device_tokens, non_blocking=True)
             key = self._graph_key(entries, ctx)
             if key is None:
                 logits = self.model.forward(ctx, self.cache)
