@@ -54,6 +54,31 @@ struct GemmShared {
   int epilogue_ok;
 };
 
+// tanh GELU with the hardware tanh (relative error about 2^-11, below the bfloat16 rounding of the
+// result): 0.5 x (1 + tanh(0.7978846 (x + 0.044715 x^3)))   (src/tensor/ops.rs:169-178)
+__device__ __forceinline__ float gelu_tanh_fast(float v) {
+  return 0.5f * v * (1.0f + tc::tanh_approx(0.7978846f * (v + 0.044715f * v * v * v)));
+}
+
+
+// Writes 16 token columns of one feature per lane as bfloat16 pairs: neighbouring lanes (features
+// f, f+1) swap halves so that an even lane stores (f, f+1) of token j and the odd lane (f-1, f) of
+// token j+1, four bytes each (two-byte stores are several times slower).  N must be even.
+__device__ __forceinline__ void store_bf16_pairs(__nv_bfloat16* out, size_t N, int f, bool f_pair_ok, int c0,
+                                                 int n, const float* v, int lane) {
+  const bool odd = lane & 1;
+#pragma unroll
+  for (int j = 0; j < 16; j += 2) {
+    const float send = odd ? v[j] : v[j + 1];
+    const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+    const int tok = j + (odd ? 1 : 0);
+    if (f_pair_ok && tok < n) {
+      const __nv_bfloat162 pair = odd ? __floats2bfloat162_rn(recv, v[j + 1]) : __floats2bfloat162_rn(v[j], recv);
+      *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(c0 + tok) * N + (f & ~1)) = pair;
+    }
+  }
+}
+
 template <bool DUAL>
 __device__ __forceinline__ void store_result(const GemmParams& p, int f, int t, float a, float b) {
   if (f >= p.N || t >= p.M) return;
@@ -200,14 +225,83 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
     const int halves = DUAL ? 2 : 1;
     if (ok && p.splits == 1) {
-      for (int c0 = 0; c0 < p.BN; c0 += 16) {
-        uint32_t a[16], b[16];
-        tc::tmem_ld_16(lane_addr + c0, a);
-        if (DUAL) tc::tmem_ld_16(lane_addr + p.BN + c0, b);
-        tc::tmem_ld_wait();
+      // One row pointer per thread, advanced by a whole output row per token; the epilogue kind is
+      // chosen once, outside the loops, so that each loop body is a load, a little math and a store.
+      const bool f_ok = f < p.N;
+      const int t_end = min(p.BN, p.M - m0);                  // columns of this tile that are tokens
+      // bfloat16 outputs go out as pairs of features (N even; the last feature of an odd N has no
+      // partner and takes the scalar store)
+      const bool pairs = (p.N & 1) == 0;
+      const bool f_pair_ok = (f | 1) < p.N;
+      if (DUAL) {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m0 * p.N;
+        for (int c0 = 0; c0 < t_end; c0 += 16) {
+          uint32_t a[16], b[16];
+          tc::tmem_ld_16(lane_addr + c0, a);
+          tc::tmem_ld_16(lane_addr + p.BN + c0, b);
+          tc::tmem_ld_wait();
+          const int n = min(16, t_end - c0);
+          float v[16];
+          if (p.act == 0) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-          store_result<DUAL>(p, f, m0 + c0 + j, __uint_as_float(a[j]), DUAL ? __uint_as_float(b[j]) : 0.f);
+            for (int j = 0; j < 16; ++j) v[j] = gelu_tanh_fast(__uint_as_float(a[j])) * __uint_as_float(b[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float g = __uint_as_float(a[j]);
+              v[j] = g * (1.0f / (1.0f + __expf(-g))) * __uint_as_float(b[j]);
+            }
+          }
+          if (pairs) {
+            store_bf16_pairs(o, p.N, f, f_pair_ok, c0, n, v, lane);
+          } else if (f_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (j < n) o[(size_t)(c0 + j) * p.N + f] = __float2bfloat16_rn(v[j]);
+          }
+        }
+      } else if (p.out_bf16) {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m0 * p.N;
+        const bool capped = p.cap > 0.f;
+        for (int c0 = 0; c0 < t_end; c0 += 16) {
+          uint32_t a[16];
+          tc::tmem_ld_16(lane_addr + c0, a);
+          tc::tmem_ld_wait();
+          const int n = min(16, t_end - c0);
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(a[j]);
+          if (capped) {
+#pragma unroll 1
+            for (int j = 0; j < 16; ++j) v[j] = softcap(v[j], p.cap);
+          }
+          if (pairs) {
+            store_bf16_pairs(o, p.N, f, f_pair_ok, c0, n, v, lane);
+          } else if (f_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (j < n) o[(size_t)(c0 + j) * p.N + f] = __float2bfloat16_rn(v[j]);
+          }
+        }
+      } else {
+        float* o = reinterpret_cast<float*>(p.out) + (size_t)m0 * p.N + f;
+        const bool capped = p.cap > 0.f;
+        for (int c0 = 0; c0 < t_end; c0 += 16) {
+          uint32_t a[16];
+          tc::tmem_ld_16(lane_addr + c0, a);
+          tc::tmem_ld_wait();
+          const int n = min(16, t_end - c0);
+          if (f_ok) {
+            if (capped) {
+#pragma unroll 1
+              for (int j = 0; j < n; ++j) o[(size_t)(c0 + j) * p.N] = softcap(__uint_as_float(a[j]), p.cap);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (j < n) o[(size_t)(c0 + j) * p.N] = __uint_as_float(a[j]);
+            }
+          }
+        }
       }
     } else if (ok) {
       // partial sums of this split: workspace[tile][split][half][column][row]
