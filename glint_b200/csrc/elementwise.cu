@@ -384,6 +384,15 @@ __global__ void gated_act_kernel(const float* __restrict__ gu, S* __restrict__ o
   out[idx] = from_float<S>(a * u);
 }
 
+// ids[dst_rows[i]] = src[src_idx[i]]: tokens sampled by the previous step, which never left the device
+__global__ void place_tokens_kernel(int* __restrict__ ids, const int* __restrict__ dst_rows,
+                                    const int* __restrict__ src, const int* __restrict__ src_idx, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) ids[dst_rows[i]] = src[src_idx[i]];
+}
+
 __global__ void softcap_kernel(float* __restrict__ x, long long n, float cap) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx < n) x[idx] = softcap(x[idx], cap);
@@ -499,6 +508,13 @@ GLINT_API int glint_softcap(float* x, long long n, float cap, cudaStream_t strea
   if (n <= 0 || !(cap > 0.f)) return GLINT_OK;
   const int threads = 256;
   softcap_kernel<<<(unsigned)((n + threads - 1) / threads), threads, 0, stream>>>(x, n, cap);
+  return (int)cudaGetLastError();
+}
+
+GLINT_API int glint_place_tokens(int* ids, const int* dst_rows, const int* src, const int* src_idx, int n,
+                                 cudaStream_t stream) {
+  if (n <= 0) return GLINT_OK;
+  place_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(ids, dst_rows, src, src_idx, n);
   return (int)cudaGetLastError();
 }
 

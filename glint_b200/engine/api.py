@@ -23,11 +23,13 @@ class LLM:
     ``model_path``: folder with config.json and model.safetensors.  ``dtype``: 'bfloat16' (the
     serving kernels) or 'float32' (everything in true 32-bit).  ``cache_tokens``: how many
     tokens each cache group can hold in all (default: 4 contexts).  ``max_active``: requests
-    running at a time.  ``max_step_tokens``: token budget of one step.
+    running at a time.  ``max_step_tokens``: token budget of one step.  ``lookahead``: launch each
+    decode step with the previous step's sampled tokens still on the device and read them one step
+    late, so that the host's work overlaps the GPU's (same tokens as without it).
     """
 
     def __init__(self, model_path=None, dtype="bfloat16", device="cuda:0", cache_tokens=None, max_active=64,
-                 max_step_tokens=2048, page_size=16, kernels="auto", model=None):
+                 max_step_tokens=2048, page_size=16, kernels="auto", model=None, lookahead=True):
         try:
             self.model = model if model is not None else load_model(model_path, dtype, device, kernels)
         except GlintError as e:
@@ -38,7 +40,7 @@ class LLM:
         self.engine = build_engine(self.model, cache_tokens, num_slots=max_active, page_size=page_size)
         self.sampler = DeviceSampler(self.model.rt, spec.vocab_size)
         self.scheduler = Scheduler(self.engine, self.sampler, max_step_tokens=max_step_tokens,
-                                   max_active=max_active)
+                                   max_active=max_active, lookahead=lookahead)
         self.eos_token_id = spec.eos_token_id
         self._next_id = 0
 

@@ -49,10 +49,30 @@ class Request:
     preemptions: int = 0
     rng: Optional[Xorshift64] = None
     order: int = 0
+    unresolved: int = 0          # 1 while the newest token is still only on the device
+    pending_index: int = 0       # its place among the tokens sampled by that step
+    draining: bool = False       # reached its budget by count; finishes when its last token arrives
 
     @property
     def tokens(self):
         return self.prompt + self.output
+
+    @property
+    def num_tokens(self):
+        return len(self.prompt) + len(self.output) + self.unresolved
+
+    @property
+    def generated(self):
+        return len(self.output) + self.unresolved
+
+    def token_slice(self, lo, hi):
+        """tokens[lo:hi] without building the whole list."""
+        n = len(self.prompt)
+        if hi <= n:
+            return self.prompt[lo:hi]
+        if lo >= n:
+            return self.output[lo - n:hi - n]
+        return self.prompt[lo:] + self.output[:hi - n]
 
     @property
     def finished(self):
@@ -63,9 +83,17 @@ class Scheduler:
     """``engine`` offers ``open()``, ``close(slot)``, ``step(entries) -> logits`` and ``cache``;
     ``sampler.sample(logits, params, rngs, histories) -> tokens``."""
 
-    def __init__(self, engine, sampler, max_step_tokens=2048, max_active=None, context_length=None):
+    def __init__(self, engine, sampler, max_step_tokens=2048, max_active=None, context_length=None,
+                 lookahead=False):
         self.engine = engine
         self.sampler = sampler
+        # With ``lookahead`` the next step is launched with the sampled tokens still on the device,
+        # and the host reads them one step late (EOS is then seen one step late: the extra row is
+        # discarded).  Needs a sampler with ``sample_device``; rows with a repeat penalty fall back.
+        self.lookahead = bool(lookahead) and hasattr(sampler, "sample_device")
+        self._pending = None
+        self._host_tokens = [None, None]
+        self._host_flip = 0
         self.max_step_tokens = int(max_step_tokens)
         self.max_active = int(max_active or engine.cache.num_slots)
         self.context_length = int(context_length or engine.cache.max_positions)
@@ -99,7 +127,7 @@ class Scheduler:
 
     @property
     def idle(self):
-        return not self.waiting and not self.running
+        return not self.waiting and not self.running and self._pending is None
 
     # ---- planning ---------------------------------------------------------------------------------
 
@@ -114,21 +142,26 @@ class Scheduler:
         def fits(req, n):
             return cache.pages_short([(r.slot, k) for r, k in rows] + [(req.slot, n)]) is None
 
-        decoding = [r for r in self.running if r.computed == len(r.tokens) - 1 and r.output]
-        prefilling = [r for r in self.running if r not in decoding]
-        for r in decoding:
-            if budget >= 1 and fits(r, 1):
-                rows.append((r, 1))
-                budget -= 1
+        decoding = [r for r in self.running if r.computed == r.num_tokens - 1 and r.generated]
+        prefilling = [r for r in self.running if not (r.computed == r.num_tokens - 1 and r.generated)]
+        if decoding and len(decoding) <= budget and \
+                cache.pages_short([(r.slot, 1) for r in decoding]) is None:
+            rows = [(r, 1) for r in decoding]        # the usual case: every decoder fits, one check
+            budget -= len(decoding)
+        else:
+            for r in decoding:
+                if budget >= 1 and fits(r, 1):
+                    rows.append((r, 1))
+                    budget -= 1
         for r in prefilling:
-            n = min(len(r.tokens) - r.computed, budget)
+            n = min(r.num_tokens - r.computed, budget)
             if n > 0 and fits(r, n):   # a portion that does not fit waits for pages
                 rows.append((r, n))
                 budget -= n
         while (self.waiting and budget > 0 and len(self.running) < self.max_active
                and cache.free_slots > 0):
             r = self.waiting[0]
-            n = min(len(r.tokens) - r.computed, budget)
+            n = min(r.num_tokens - r.computed, budget)
             r.slot = self.engine.open()
             if not fits(r, n):
                 self.engine.close(r.slot)
@@ -143,7 +176,10 @@ class Scheduler:
     def _preempt_or_finish(self):
         """Nobody can run.  Free the request admitted last; if it is alone on an empty cache it
         can never run: end it with ``length``."""
+        self._resolve()
         if not self.running:
+            if not self.waiting:
+                return
             r = self.waiting.popleft()   # cannot even be admitted alone
             self._finish(r, FINISH_LENGTH)
             return
@@ -173,6 +209,10 @@ class Scheduler:
 
     def step(self):
         """Plan, run and sample one step.  Returns the requests that finished in it."""
+        if self.lookahead and all(r.params.repeat_penalty == 1.0 or r.params.greedy
+                                  for r in list(self.running) + list(self.waiting)):
+            return self._step_lookahead()
+        self._resolve()
         done_before = len(self.finished)
         rows = self.plan()
         while not rows and not self.idle:
@@ -184,8 +224,8 @@ class Scheduler:
         entries, sampled = [], []
         n_decode = n_prefill = 0
         for r, n in rows:
-            toks = r.tokens[r.computed:r.computed + n]
-            last = r.computed + n == len(r.tokens)
+            toks = r.token_slice(r.computed, r.computed + n)
+            last = r.computed + n == r.num_tokens
             entries.append(StepEntry(r.slot, toks, [n - 1] if last else []))
             if last:
                 sampled.append(r)
@@ -200,8 +240,9 @@ class Scheduler:
         for r, n in rows:
             r.computed += n
         if sampled:
-            tokens = self.sampler.sample(logits, [r.params for r in sampled], [r.rng for r in sampled],
-                                         [r.tokens for r in sampled])
+            histories = [r.tokens if (r.params.repeat_penalty != 1.0 and not r.params.greedy) else ()
+                         for r in sampled]
+            tokens = self.sampler.sample(logits, [r.params for r in sampled], [r.rng for r in sampled], histories)
             for r, tok in zip(sampled, tokens):
                 r.output.append(int(tok))
                 # the reference's order of checks (src/server/engine.rs:548-578)
@@ -209,12 +250,102 @@ class Scheduler:
                     self._finish(r, FINISH_STOP)
                 elif len(r.output) >= r.max_tokens:
                     self._finish(r, FINISH_LENGTH)
-                elif len(r.tokens) >= self.context_length:
+                elif r.num_tokens >= self.context_length:
                     self._finish(r, FINISH_LENGTH)
         self.step_log.append({"seconds": time.perf_counter() - t_start, "decode_rows": n_decode,
                               "prefill_tokens": n_prefill,
                               "h2d_bytes": getattr(self.engine, "last_h2d_bytes", 0),
                               "d2h_bytes": 4 * len(sampled) * (1 if all(r.params.greedy for r in sampled) else 2)})
+        return self.finished[done_before:]
+
+    # ---- one step with the sampled tokens left on the device ------------------------------------------
+
+    def _resolve(self):
+        """Read the tokens of the pending step (waits for it) and draw the consequences: append,
+        EOS, budget.  A request that met EOS keeps nothing of the step launched meanwhile."""
+        pend = self._pending
+        if pend is None:
+            return
+        self._pending = None
+        dev, host, event, sampled = pend
+        event.synchronize()
+        tokens = host[:len(sampled)].tolist()
+        for r, tok in zip(sampled, tokens):
+            if r.finished:
+                continue                       # met EOS a step ago; this token is the discarded one
+            r.output.append(int(tok))
+            r.unresolved = 0
+            if r.eos_token_id is not None and tok == r.eos_token_id:
+                self._finish(r, FINISH_STOP)
+            elif r.draining:
+                self._finish(r, FINISH_LENGTH)
+
+    def _step_lookahead(self):
+        import torch
+        done_before = len(self.finished)
+        rows = self.plan()
+        while not rows and not self.idle:
+            if self._pending is not None:
+                self._resolve()                # frees what finished; the plan may now have rows
+            else:
+                self._preempt_or_finish()
+            rows = self.plan()
+        if not rows:
+            return self.finished[done_before:]
+        t_start = time.perf_counter()
+        entries, sampled, src_idx, dst_rows = [], [], [], []
+        n_decode = n_prefill = offset = 0
+        for r, n in rows:
+            last = r.computed + n == r.num_tokens
+            if r.unresolved:                   # its newest token is the pending step's, on the device
+                toks = [0]
+                src_idx.append(r.pending_index)
+                dst_rows.append(offset)
+            else:
+                toks = r.token_slice(r.computed, r.computed + n)
+            entries.append(StepEntry(r.slot, toks, [n - 1] if last else []))
+            if last:
+                sampled.append(r)
+            if r.generated and n == 1 and last:
+                n_decode += 1
+            else:
+                n_prefill += n
+            offset += n
+        prev = self._pending
+        placed = (prev[0], src_idx, dst_rows) if src_idx else None
+        logits = self.engine.step(entries, device_tokens=placed)
+        self.counters["steps"] += 1
+        self.counters["decode_tokens"] += n_decode
+        self.counters["prefill_tokens"] += n_prefill
+        for r, n in rows:
+            r.computed += n
+        new_pending = None
+        if sampled:
+            dev = self.sampler.sample_device(logits, [r.params for r in sampled], [r.rng for r in sampled])
+            k = self._host_flip
+            self._host_flip ^= 1
+            host = self._host_tokens[k]
+            if host is None or host.numel() < len(sampled):
+                host = torch.empty(max(len(sampled), self.max_active), dtype=torch.int32).pin_memory()
+                self._host_tokens[k] = host
+            host[:len(sampled)].copy_(dev, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record()
+            new_pending = (dev, host, event, list(sampled))
+        self._resolve()                        # the previous step's tokens, while this step runs
+        for i, r in enumerate(sampled):
+            if r.finished:
+                continue                       # EOS came to light just now: this step's row is void
+            r.unresolved = 1
+            r.pending_index = i
+            if r.generated >= r.max_tokens or r.num_tokens >= self.context_length:
+                r.draining = True              # no further rows; it finishes when this token arrives
+                self.running.remove(r)
+        self._pending = new_pending
+        self.step_log.append({"seconds": time.perf_counter() - t_start, "decode_rows": n_decode,
+                              "prefill_tokens": n_prefill,
+                              "h2d_bytes": getattr(self.engine, "last_h2d_bytes", 0),
+                              "d2h_bytes": 4 * len(sampled)})
         return self.finished[done_before:]
 
     def run(self):

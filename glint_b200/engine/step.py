@@ -42,7 +42,7 @@ class StepContext:
     wanted.  The ``h_`` fields are host copies for planning launches.
     """
 
-    def __init__(self, cache, entries, meta_dev, staging):
+    def __init__(self, cache, entries, meta_dev, staging, extra=()):
         n = len(entries)
         lens = [len(e.tokens) for e in entries]
         T = sum(lens)
@@ -68,7 +68,7 @@ class StepContext:
         max_pages = [t.shape[1] for t in tables]
 
         # one packed int32 buffer -> one copy to the device
-        sizes = [T, T, T, n, n, n + 1, len(rows)] + [n * mp for mp in max_pages]
+        sizes = [T, T, T, n, n, n + 1, len(rows)] + [n * mp for mp in max_pages] + [len(x) for x in extra]
         offs, total = [], 0
         for s in sizes:
             offs.append(total)
@@ -86,6 +86,10 @@ class StepContext:
             pack[offs[6]:offs[6] + len(rows)] = rows
         for g, t in enumerate(tables):
             pack[offs[7 + g]:offs[7 + g] + t.size] = t.reshape(-1)
+        first_extra = 7 + len(tables)
+        for k, x in enumerate(extra):
+            if len(x):
+                pack[offs[first_extra + k]:offs[first_extra + k] + len(x)] = x
         dev = meta_dev(pack, total)
         self.h2d_bytes = total * 4
         cut = lambda k, size: dev[offs[k]:offs[k] + size]
@@ -97,6 +101,7 @@ class StepContext:
         self.cu_seqlens = cut(5, n + 1)
         self.logit_rows = cut(6, len(rows))
         self.block_tables = [cut(7 + g, n * mp).view(n, mp) for g, mp in enumerate(max_pages)]
+        self.extra = [cut(first_extra + k, len(x)) for k, x in enumerate(extra)]
 
     def block_table(self, group):
         """Device block table [requests of this step, max pages] of a cache group."""
@@ -181,7 +186,10 @@ class Engine:
             seen.add(e.slot)
             if len(e.tokens) == 0:
                 raise RequestError("an entry without tokens")
-            lo, hi = min(e.tokens), max(e.tokens)
+            if len(e.tokens) == 1:
+                lo = hi = e.tokens[0]
+            else:
+                lo, hi = min(e.tokens), max(e.tokens)
             if lo < 0 or hi >= self.vocab_size:
                 raise RequestError(f"token id {lo if lo < 0 else hi} lies outside the vocabulary of "
                                    f"{self.vocab_size}")
@@ -191,7 +199,9 @@ class Engine:
         device, in the order of the entries and of each ``want`` (``None`` if nothing is wanted).
         The tensor is valid until the next step.  ``device_tokens`` (int32 on the device, one
         per token of the step) replaces the entries' token ids, for callers whose tokens never
-        leave the device (the entries then carry placeholders of the right count).
+        leave the device (the entries then carry placeholders of the right count).  A tuple
+        ``(source, source_indices, token_rows)`` replaces only the listed token rows, each with
+        ``source[source_indices[i]]``.
 
         Raises ``PagePoolExhausted`` before anything ran when the cache cannot hold the new
         tokens; the cache is then unchanged apart from pages that a window had already passed.
@@ -200,8 +210,14 @@ class Engine:
         rows = [(e.slot, len(e.tokens)) for e in entries]
         self.cache.reserve(rows)
         with torch.cuda.device(self.rt.device):
-            ctx = StepContext(self.cache, entries, self._upload, self._stage)
-            if device_tokens is not None:
+            placed = isinstance(device_tokens, tuple)      # (source tensor, source indices, token rows)
+            extra = (device_tokens[1], device_tokens[2]) if placed else ()
+            ctx = StepContext(self.cache, entries, self._upload, self._stage, extra)
+            if placed:
+                from .. import ops
+                if len(device_tokens[1]):
+                    ops.place_tokens(ctx.token_ids, ctx.extra[1], device_tokens[0], ctx.extra[0])
+            elif device_tokens is not None:
                 ctx.token_ids.copy_(device_tokens, non_blocking=True)
             key = self._graph_key(entries, ctx)
             if key is None:

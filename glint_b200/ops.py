@@ -50,6 +50,7 @@ _CORE_SIGNATURES = {
     "glint_rope_kv_write": [_P, _P, _P, _P, _I, _P, _F, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "glint_gated_act": [_P, _P, _I, _I, _I, _I, _P],
     "glint_softcap": [_P, _L, _F, _P],
+    "glint_place_tokens": [_P, _P, _P, _P, _I, _P],
     "glint_gemm_plain": [_P, _P, _I, _P, _I, _I, _I, _F, _P],
     "glint_attention_plain": [_P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
     "glint_argmax": [_P, _L, _I, _I, _P, _P],
@@ -153,6 +154,12 @@ def gated_act(gu, out, activation):
     require(gu, torch.float32, "gu"); require(out, None, "out")
     check(core().glint_gated_act(ptr(gu), ptr(out), dtype_code(out.dtype), T, I, ACTIVATIONS[activation],
                                  stream()), "gated_act")
+
+
+def place_tokens(ids, dst_rows, src, src_idx):
+    """ids[dst_rows[i]] = src[src_idx[i]] (all int32 on the device)."""
+    check(core().glint_place_tokens(ptr(ids), ptr(dst_rows), ptr(src), ptr(src_idx), dst_rows.shape[0], stream()),
+          "place_tokens")
 
 
 def softcap_(x, cap):

@@ -80,6 +80,27 @@ class DeviceSampler:
             self._work = torch.empty((max(rows, 8), self.vocab_size), dtype=torch.float32, device=self.rt.device)
         return self._work[:rows]
 
+    def sample_device(self, logits, params, rngs):
+        """Like ``sample`` for rows without a repeat penalty, but the chosen tokens stay on the
+        device (int32 [rows]); nothing waits for the GPU.  Uniform draws are taken from the rows'
+        generators now, so the stream of draws is the same as with ``sample``."""
+        rows = logits.shape[0]
+        dev = logits.device
+        chosen = torch.empty(rows, dtype=torch.int32, device=dev)
+        if all(p.greedy for p in params):
+            ops.argmax(logits, chosen)
+            return chosen
+        ops.argmax(logits, chosen)
+        temp = [p.temperature if not p.greedy else 1.0 for p in params]
+        uniform = [float(r.next_f32()) if not p.greedy else 0.0 for p, r in zip(params, rngs)]
+        pack = torch.tensor([temp, uniform, [p.top_p for p in params], [p.min_p for p in params],
+                             [float(p.top_k) for p in params], [0.0 if p.greedy else 1.0 for p in params]],
+                            dtype=torch.float32).pin_memory().to(dev, non_blocking=True)
+        drawn = torch.empty(rows, dtype=torch.int32, device=dev)
+        ops.sample(logits, self._scratch(rows), pack[0].contiguous(), pack[4].to(torch.int32), pack[2].contiguous(),
+                   pack[3].contiguous(), pack[1].contiguous(), drawn)
+        return torch.where(pack[5] > 0, drawn, chosen)
+
     def sample(self, logits, params, rngs, histories):
         """``logits`` float32 [rows, vocab] on the device; per row its ``SamplingParams``, its
         ``Xorshift64`` and the tokens so far (for the repeat penalty).  Returns a list of ints."""
