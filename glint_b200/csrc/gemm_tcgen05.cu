@@ -313,9 +313,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
         for (int j = 0; j < 16; ++j) mine[(size_t)(c0 + j) * GEMM_BM + q * 32 + lane] = __uint_as_float(a[j]);
       }
-      __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (threadIdx.x == 64) {
+        __threadfence();                 // cumulative: orders the whole block's partial sums before the count
         const int prev = atomicAdd(&p.counters[tile_id], 1);
         sh->is_last = (prev == p.splits - 1);
       }
@@ -324,23 +324,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         __threadfence();
         const float* base = p.workspace + ((size_t)tile_id * p.splits * halves) * p.BN * GEMM_BM;
         const size_t split_stride = (size_t)halves * p.BN * GEMM_BM;
-        // 16 columns at a time, all their loads in flight together; splits are added in order
+        // 16 columns at a time; the loads of four splits are in flight together; splits are added in order
         for (int c0 = 0; c0 < p.BN; c0 += 16) {
           float a[16], b[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) a[j] = b[j] = 0.f;
-          for (int s = 0; s < p.splits; ++s) {
-            const float* src = base + s * split_stride + (size_t)c0 * GEMM_BM + q * 32 + lane;
-            float va[16], vb[16];
+          for (int s0 = 0; s0 < p.splits; s0 += 4) {
+            float va[4][16], vb[DUAL ? 4 : 1][16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              va[j] = __ldcg(src + (size_t)j * GEMM_BM);
-              if (DUAL) vb[j] = __ldcg(src + (size_t)(p.BN + j) * GEMM_BM);
+            for (int u = 0; u < 4; ++u) {
+              const bool in = s0 + u < p.splits;
+              const float* src = base + (size_t)(in ? s0 + u : s0) * split_stride + (size_t)c0 * GEMM_BM + q * 32 + lane;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                va[u][j] = in ? __ldcg(src + (size_t)j * GEMM_BM) : 0.f;
+                if (DUAL) vb[u][j] = in ? __ldcg(src + (size_t)(p.BN + j) * GEMM_BM) : 0.f;
+              }
             }
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              a[j] += va[j];
-              if (DUAL) b[j] += vb[j];
+            for (int u = 0; u < 4; ++u) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                a[j] += va[u][j];
+                if (DUAL) b[j] += vb[u][j];
+              }
             }
           }
 #pragma unroll
@@ -434,11 +441,19 @@ GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int ou
   if (force_splits > 0) {
     splits = force_splits;
   } else if (tiles <= 74) {
-    // one wave: as many blocks as fit the 148 SMs at once, each with at least two K blocks
-    splits = 148 / tiles;
-    const int max_by_k = p.total_kb / 2 > 0 ? p.total_kb / 2 : 1;
-    if (splits > max_by_k) splits = max_by_k;
-    if (splits > 32) splits = 32;
+    // One wave of at most 148 blocks.  Estimated time (microseconds, fitted to measurements): the
+    // K blocks a block streams at ~0.3 each, plus for a split launch the reduction through the
+    // workspace, which grows with the splits and the width of the token tile.
+    const int width = bn * (dual ? 2 : 1);
+    float best = 1e30f;
+    for (int cand = 1; cand <= 32 && tiles * cand <= 148 && cand <= p.total_kb; ++cand) {
+      const int per = (p.total_kb + cand - 1) / cand;
+      const float est = 0.3f * per + (cand > 1 ? 1.5f + 0.04f * width * cand : 0.f);
+      if (est < best) {
+        best = est;
+        splits = cand;
+      }
+    }
   }
   if (splits > p.total_kb) splits = p.total_kb;
   p.kb_per_split = (p.total_kb + splits - 1) / splits;
