@@ -11,7 +11,7 @@ import pytest
 import torch
 
 from tests import tracing
-from tests.helpers import ROOT, TINY, TOL, make_model_dir, plain_logits, random_tokens
+from tests.helpers import ROOT, TINY, make_model_dir, plain_logits, random_tokens, tolerance
 from tests.plain import model as plain
 from tests.plain import sampler as psampler
 
@@ -64,7 +64,7 @@ def test_greedy_generation_bfloat16_follows_plain(folders):
     want, margins = _plain_greedy(folders["B"], prompt, 12)
     for i, (a, b) in enumerate(zip(got, want)):
         if a != b:
-            assert margins[i] < TOL["bfloat16"], (i, got, want, margins)
+            assert margins[i] < 0.1, (i, got, want, margins)   # the top two were within bfloat16 rounding
             break
 
 
@@ -81,8 +81,9 @@ def test_long_decoding_and_first_tokens(folders, dtype):
     got = tracing.collect(steps, out, vocab)["r"]
     want = plain_logits(folders["C"], toks)
     diff = np.abs(got - want).max(axis=1)
-    assert diff[:3].max() <= TOL[dtype], diff[:3]                        # the first tokens of a sequence
-    assert diff.max() <= TOL[dtype], (int(np.argmax(diff > TOL[dtype])), diff.max())
+    tol = tolerance(dtype, want)
+    assert diff[:3].max() <= tol, diff[:3]                               # the first tokens of a sequence
+    assert diff.max() <= tol, (int(np.argmax(diff > tol)), diff.max())
 
 
 def test_temperature_sampling_is_seeded_and_follows_the_plain_sampler(folders):
@@ -121,7 +122,7 @@ def test_small_cache_preempts_and_still_gives_the_same_tokens(folders):
     assert tight.scheduler.counters["preemptions"] >= 1 or any(s["reuses"] > 0 for s in tight.cache_stats().values())
     assert all(s["live"] == 0 for s in tight.cache_stats().values())
     with pytest.raises(ValueError, match="empty"):
-        tight.generate([], max_tokens=3) if False else tight.generate([[]], max_tokens=3)
+        tight.generate([[]], max_tokens=3)
     with pytest.raises(ValueError, match="vocabulary"):
         tight.generate([vocab + 5], max_tokens=3)
 
