@@ -143,6 +143,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--page", type=int, default=16)
     a = ap.parse_args()
     out = []
     if a.what == "gemm":
@@ -161,10 +162,10 @@ def main():
         out.append(bench_attention_prefill(a.tokens, iters=a.iters, kernel="mma"))
         out.extend(bench_rows(a.tokens))
     elif a.what == "attention-decode":
-        out.append(bench_attention_decode(a.batch, a.context, window=a.window or None, splits=a.splits or None,
-                                          iters=a.iters))
+        out.append(bench_attention_decode(a.batch, a.context, page=a.page, window=a.window or None,
+                                          splits=a.splits or None, iters=a.iters))
     elif a.what == "attention-prefill":
-        out.append(bench_attention_prefill(a.tokens, window=a.window or None, iters=a.iters))
+        out.append(bench_attention_prefill(a.tokens, page=a.page, window=a.window or None, iters=a.iters))
     elif a.what == "rows":
         out.extend(bench_rows(a.batch))
     for row in out:

@@ -7,7 +7,7 @@
 //   warp 0     TMA: the query tile once (one 4-D box per 64 columns), then key and value tiles
 //              page by page into a two-deep ring (every lane issues one box)
 //   warp 1     tcgen05.mma: S = Q K^T into tensor memory, then O += P V (V is the MN-major operand)
-//   warps 2-5  softmax: each thread owns one row of S (tcgen05.ld), scales, soft-caps and masks it
+//   warps 2-9  softmax: two threads share one row of S (tcgen05.ld), scale, soft-cap and mask it
 //              by absolute position, keeps the running max and sum in 32-bit, writes P as bfloat16
 //              into shared memory in the swizzled operand layout, and rescales its row of O in
 //              tensor memory only when the running max grew by more than 8 (the result is the same:
@@ -22,7 +22,7 @@ namespace glint {
 
 constexpr int FA_M = 128;             // query rows per block
 constexpr int FA_N = 64;              // keys per tile
-constexpr int FA_THREADS = 192;
+constexpr int FA_THREADS = 320;      // TMA warp, MMA warp, 8 softmax warps
 constexpr int FA_Q_SUB = FA_M * 128;  // bytes of a 64-column slice of the query tile
 constexpr int FA_KV_SUB = FA_N * 128; // bytes of a 64-column slice of a key or value tile
 constexpr int FA_P_BYTES = FA_M * 128;
@@ -41,10 +41,13 @@ struct FaParams {
 };
 
 struct FaShared {
-  uint64_t q_full, s_full, p_ready, o_full;
-  uint64_t kv_full[2], kv_empty[2];
+  uint64_t q_full, p_ready, p_free, o_full;
+  uint64_t s_full[2];
+  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
   uint32_t tmem_base;
   int abort_flag;
+  float row_max[2][2][FA_M];     // [tile parity][column half][row]
+  float row_sum[2][FA_M];
 };
 
 __global__ void __launch_bounds__(FA_THREADS, 1)
@@ -78,12 +81,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
   if (threadIdx.x == 0) {
     tc::mbar_init(&sh->q_full, 1);
-    tc::mbar_init(&sh->s_full, 1);
-    tc::mbar_init(&sh->p_ready, 128);
+    tc::mbar_init(&sh->p_ready, 256);
+    tc::mbar_init(&sh->p_free, 1);
     tc::mbar_init(&sh->o_full, 1);
     for (int b = 0; b < 2; ++b) {
-      tc::mbar_init(&sh->kv_full[b], 1);
-      tc::mbar_init(&sh->kv_empty[b], 1);
+      tc::mbar_init(&sh->s_full[b], 1);
+      tc::mbar_init(&sh->k_full[b], 1);
+      tc::mbar_init(&sh->k_empty[b], 1);
+      tc::mbar_init(&sh->v_full[b], 1);
+      tc::mbar_init(&sh->v_empty[b], 1);
     }
     sh->abort_flag = 0;
     tc::fence_barrier_init();
@@ -95,8 +101,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   tc::fence_before_thread_sync();
   __syncthreads();
   tc::fence_after_thread_sync();
-  const uint32_t tmem_s = sh->tmem_base;
-  const uint32_t tmem_o = tmem_s + FA_N;
+  const uint32_t tmem_s = sh->tmem_base;          // two score tiles: columns [0, 64) and [64, 128)
+  const uint32_t tmem_o = tmem_s + 2 * FA_N;
   volatile int* abort_flag = &sh->abort_flag;
 
   if (warp == 0) {
@@ -107,33 +113,37 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         tc::tma_load_4d(sq + (size_t)sub * FA_Q_SUB, &map_q, &sh->q_full, sub * 64, 0, kvh, t_begin + tok0);
     }
     const int ppt = FA_N / p.page_size;                        // pages per tile
-    const int boxes = 2 * ppt * nsub;
+    bool return_early = false;
     const int* table = p.block_table + (size_t)seq * p.max_pages;
     const int page_lo = kv_first / p.page_size, page_hi = pos_last / p.page_size;
+    const int half_boxes = ppt * nsub;                         // boxes of the key tile (and of the value tile)
     for (int j = 0; j < n_tiles; ++j) {
       const int b = j & 1;
-      bool ok = true;
-      if (j >= 2) ok = tc::mbar_wait(&sh->kv_empty[b], ((j >> 1) - 1) & 1, abort_flag);
-      if (!__all_sync(0xffffffffu, ok)) break;
-      if (lane == 0) tc::mbar_expect_tx(&sh->kv_full[b], (uint32_t)2 * nsub * FA_KV_SUB);
-      __syncwarp();
       const int first_page = (kv_begin + j * FA_N) / p.page_size;
-      for (int bi = lane; bi < boxes; bi += 32) {
-        const int which = bi / (ppt * nsub);                   // 0: keys, 1: values
-        const int rem = bi % (ppt * nsub);
-        const int pi = rem / nsub, sub = rem % nsub;
-        const int page_idx = first_page + pi;
-        int page = 0;                                          // pages outside the range are masked below;
-        if (page_idx >= page_lo && page_idx <= page_hi) {      // they are filled from page 0 (finite values)
-          page = table[page_idx];
-          if (page < 0 || page >= p.num_pages) {
-            atomicExch(p.status, 3);
-            page = 0;
+      for (int which = 0; which < 2; ++which) {                // keys first: they are needed first
+        uint64_t* full = which ? &sh->v_full[b] : &sh->k_full[b];
+        bool ok = true;
+        if (j >= 2) ok = tc::mbar_wait(which ? &sh->v_empty[b] : &sh->k_empty[b], ((j >> 1) - 1) & 1, abort_flag);
+        if (!__all_sync(0xffffffffu, ok)) return_early = true;
+        if (return_early) break;
+        if (lane == 0) tc::mbar_expect_tx(full, (uint32_t)nsub * FA_KV_SUB);
+        __syncwarp();
+        for (int bi = lane; bi < half_boxes; bi += 32) {
+          const int pi = bi / nsub, sub = bi % nsub;
+          const int page_idx = first_page + pi;
+          int page = 0;                                        // pages outside the range are masked below;
+          if (page_idx >= page_lo && page_idx <= page_hi) {    // they are filled from page 0 (finite values)
+            page = table[page_idx];
+            if (page < 0 || page >= p.num_pages) {
+              atomicExch(p.status, 3);
+              page = 0;
+            }
           }
+          uint8_t* dst = (which ? sv : sk) + ((size_t)b * nsub + sub) * FA_KV_SUB + (size_t)pi * p.page_size * 128;
+          tc::tma_load_2d(dst, which ? &map_v : &map_k, full, sub * 64, (page * p.nkv + kvh) * p.page_size);
         }
-        uint8_t* dst = (which ? sv : sk) + ((size_t)b * nsub + sub) * FA_KV_SUB + (size_t)pi * p.page_size * 128;
-        tc::tma_load_2d(dst, which ? &map_v : &map_k, &sh->kv_full[b], sub * 64, (page * p.nkv + kvh) * p.page_size);
       }
+      if (return_early) break;
     }
   } else if (warp == 1) {
     // ---- MMA issuer -------------------------------------------------------------------------------
@@ -142,33 +152,60 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       const uint32_t idesc_o = tc::idesc_bf16_f32_b_mn(FA_M, hd);
       const uint32_t q_addr = tc::smem_u32(sq), k_addr = tc::smem_u32(sk), v_addr = tc::smem_u32(sv);
       const uint32_t p_addr = tc::smem_u32(sp);
+      // Order of issue: S(0), S(1), then for every tile j: O += P(j) V(j), S(j+2).  While the softmax
+      // warps work on S(j+1) the tensor pipe runs P(j) V(j) and S(j+2).  This one thread issues 20
+      // MMAs per tile, so its instruction count is what matters: every descriptor is a constant base
+      // plus a small offset (the address field counts 16 bytes).
+      const uint64_t qd0 = tc::smem_desc_k_sw128(q_addr);
+      const uint64_t pd0 = tc::smem_desc_k_sw128(p_addr);
+      uint64_t kd0[2], vd0[2];
+      for (int b = 0; b < 2; ++b) {
+        kd0[b] = tc::smem_desc_k_sw128(k_addr + b * nsub * FA_KV_SUB);
+        vd0[b] = tc::smem_desc_mn_sw128(v_addr + b * nsub * FA_KV_SUB, FA_KV_SUB, 1024);
+      }
+      auto issue_s = [&](int j) -> bool {
+        const int b = j & 1;
+        if (!tc::mbar_wait(&sh->k_full[b], (j >> 1) & 1, abort_flag)) return false;
+        tc::fence_after_thread_sync();
+        const uint32_t d = tmem_s + b * FA_N;
+#pragma unroll
+        for (int ks = 0; ks < 16; ++ks) {
+          if (ks < hd16) {
+            const uint32_t oq = ((ks >> 2) * FA_Q_SUB + (ks & 3) * 32) >> 4;     // compile-time constants
+            const uint32_t ok_ = ((ks >> 2) * FA_KV_SUB + (ks & 3) * 32) >> 4;
+            tc::mma_bf16_ss(d, qd0 + oq, kd0[b] + ok_, idesc_s, ks > 0 ? 1u : 0u);
+          }
+        }
+        tc::mma_commit(&sh->s_full[b]);
+        tc::mma_commit(&sh->k_empty[b]);
+        return true;
+      };
       bool ok = tc::mbar_wait(&sh->q_full, 0, abort_flag);
+      if (ok) ok = issue_s(0);
+      if (ok && n_tiles > 1) ok = issue_s(1);
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int b = j & 1;
-        ok = tc::mbar_wait(&sh->kv_full[b], (j >> 1) & 1, abort_flag);
-        if (!ok) break;
-        tc::fence_after_thread_sync();
-        for (int ks = 0; ks < hd16; ++ks) {
-          const uint32_t a = q_addr + (ks >> 2) * FA_Q_SUB + (ks & 3) * 32;
-          const uint32_t bb = k_addr + (b * nsub + (ks >> 2)) * FA_KV_SUB + (ks & 3) * 32;
-          tc::mma_bf16_ss(tmem_s, tc::smem_desc_k_sw128(a), tc::smem_desc_k_sw128(bb), idesc_s, ks > 0);
-        }
-        tc::mma_commit(&sh->s_full);
         ok = tc::mbar_wait(&sh->p_ready, j & 1, abort_flag);
+        if (ok) ok = tc::mbar_wait(&sh->v_full[b], (j >> 1) & 1, abort_flag);
         if (!ok) break;
         tc::fence_after_thread_sync();
-        for (int kk = 0; kk < FA_N / 16; ++kk) {
-          const uint64_t da = tc::smem_desc_k_sw128(p_addr + kk * 32);
-          const uint64_t db = tc::smem_desc_mn_sw128(v_addr + b * nsub * FA_KV_SUB + kk * 2048, FA_KV_SUB, 1024);
-          tc::mma_bf16_ss(tmem_o, da, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-        }
-        tc::mma_commit(&sh->kv_empty[b]);
+#pragma unroll
+        for (int kk = 0; kk < FA_N / 16; ++kk)
+          tc::mma_bf16_ss(tmem_o, pd0 + 2 * kk, vd0[b] + (2048 >> 4) * kk, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        tc::mma_commit(&sh->v_empty[b]);
+        tc::mma_commit(&sh->p_free);             // P and this row of O may be touched again
+        if (j + 2 < n_tiles) ok = issue_s(j + 2);
       }
       tc::mma_commit(&sh->o_full);
     }
   } else {
-    // ---- softmax, correction and epilogue: thread <-> row of the tile ---------------------------------
-    const int quarter = warp & 3;                              // the warp's 32 lanes of tensor memory
+    // ---- softmax, correction and epilogue: two threads per row of the tile ------------------------------
+    // Warps 2..5 take columns [0, 32) of the score tile, warps 6..9 columns [32, 64); a warp reaches
+    // the 32 lanes of tensor memory of its quarter (warp index mod 4).  Two warps per scheduler hide
+    // each other's latencies; the row maximum is exchanged through shared memory.
+    constexpr int HALF = FA_N / 2;
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const bool rv = r < n_rows;
     const int qpos = pos0 + (rv ? r / G : 0);
@@ -177,29 +214,54 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const float LOG2E = 1.4426950408889634f;
     const float in_scale = p.cap > 0.f ? p.multiplier / p.cap : p.multiplier;
     const float out_scale = p.cap > 0.f ? p.cap * LOG2E : LOG2E;   // scores are kept in log2 units
+    const int o_lo = half ? ((hd16 + 1) >> 1) * 16 : 0;            // this thread's columns of O
+    const int o_hi = half ? hd : ((hd16 + 1) >> 1) * 16;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      ok = tc::mbar_wait(&sh->s_full, j & 1, abort_flag);
+      ok = tc::mbar_wait(&sh->s_full[j & 1], (j >> 1) & 1, abort_flag);
       if (!ok) break;
       tc::fence_after_thread_sync();
-      uint32_t raw[FA_N];
+      uint32_t raw[HALF];
 #pragma unroll
-      for (int c0 = 0; c0 < FA_N; c0 += 16) tc::tmem_ld_16(tmem_s + lane_base + c0, raw + c0);
+      for (int c0 = 0; c0 < HALF; c0 += 16)
+        tc::tmem_ld_16(tmem_s + (j & 1) * FA_N + lane_base + half * HALF + c0, raw + c0);
       tc::tmem_ld_wait();
-      const int key0 = kv_begin + j * FA_N;
-      float x[FA_N];
-      float mt = -INFINITY;
+      const int key0 = kv_begin + j * FA_N + half * HALF;
+      float x[HALF];
+      float mt4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      // most tiles lie wholly inside every row's range: those skip the per-key comparisons
+      const bool inside = rv && key0 >= lo && key0 + HALF - 1 <= qpos;
+      if (__all_sync(0xffffffffu, inside)) {
+        if (p.cap > 0.f) {
 #pragma unroll
-      for (int c = 0; c < FA_N; ++c) {
-        const int key = key0 + c;
-        const bool valid = rv && key <= qpos && key >= lo;
-        float v = __uint_as_float(raw[c]) * in_scale;
-        if (p.cap > 0.f) v = tc::tanh_approx(v);
-        v = valid ? v * out_scale : -INFINITY;
-        x[c] = v;
-        mt = fmaxf(mt, v);
+          for (int c = 0; c < HALF; ++c) {
+            x[c] = tc::tanh_approx(__uint_as_float(raw[c]) * in_scale) * out_scale;
+            mt4[c & 3] = fmaxf(mt4[c & 3], x[c]);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < HALF; ++c) {
+            x[c] = __uint_as_float(raw[c]) * (in_scale * out_scale);
+            mt4[c & 3] = fmaxf(mt4[c & 3], x[c]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < HALF; ++c) {
+          const int key = key0 + c;
+          const bool valid = rv && key <= qpos && key >= lo;
+          float v = __uint_as_float(raw[c]) * in_scale;
+          if (p.cap > 0.f) v = tc::tanh_approx(v);
+          v = valid ? v * out_scale : -INFINITY;
+          x[c] = v;
+          mt4[c & 3] = fmaxf(mt4[c & 3], v);
+        }
       }
+      // the row's maximum over both halves
+      sh->row_max[j & 1][half][r] = fmaxf(fmaxf(mt4[0], mt4[1]), fmaxf(mt4[2], mt4[3]));
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      const float mt = fmaxf(sh->row_max[j & 1][0][r], sh->row_max[j & 1][1][r]);
       // rescale only when the running max grew by more than 8 (in natural units)
       const bool grow = mt > m_used + FA_RESCALE * LOG2E;
       float corr = 1.f;
@@ -208,8 +270,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         l *= corr;
         m_used = mt;
       }
+      // the previous tile's P V product must be complete before O or P is touched
+      if (j > 0) {
+        ok = tc::mbar_wait(&sh->p_free, (j - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc::fence_after_thread_sync();
+      }
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        for (int c0 = 0; c0 < hd; c0 += 16) {
+        for (int c0 = o_lo; c0 < o_hi; c0 += 16) {
           uint32_t o[16];
           tc::tmem_ld_16(tmem_o + lane_base + c0, o);
           tc::tmem_ld_wait();
@@ -221,13 +289,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       }
       const float base = m_used == -INFINITY ? 0.f : m_used;
       uint8_t* prow = sp + (size_t)r * 128;
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
+      for (int ch = 0; ch < HALF / 8; ++ch) {
         float pv[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           pv[i] = tc::exp2_approx(x[ch * 8 + i] - base);
-          l += pv[i];
+          l4[i & 3] += pv[i];
         }
         uint4 packed;
         __nv_bfloat162 h0 = __floats2bfloat162_rn(pv[0], pv[1]), h1 = __floats2bfloat162_rn(pv[2], pv[3]);
@@ -236,19 +305,23 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         packed.y = *reinterpret_cast<uint32_t*>(&h1);
         packed.z = *reinterpret_cast<uint32_t*>(&h2);
         packed.w = *reinterpret_cast<uint32_t*>(&h3);
-        *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = packed;
+        *reinterpret_cast<uint4*>(prow + (((half * (HALF / 8) + ch) ^ (r & 7)) << 4)) = packed;
       }
+      l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       tc::fence_proxy_async();                 // the MMA reads P through the async proxy
       tc::fence_before_thread_sync();
       tc::mbar_arrive(&sh->p_ready);
     }
-    // ---- epilogue: O / l as bfloat16 ----------------------------------------------------------------
+    // ---- epilogue: O / l as bfloat16; the row's sum is the two halves' sums ----------------------------
+    sh->row_sum[half][r] = l;
+    asm volatile("bar.sync 2, 256;" ::: "memory");
     if (ok) ok = tc::mbar_wait(&sh->o_full, 0, abort_flag);
     if (ok) {
       tc::fence_after_thread_sync();
-      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      const float total = sh->row_sum[0][r] + sh->row_sum[1][r];
+      const float inv = total > 0.f ? 1.0f / total : 0.f;
       __nv_bfloat16* orow = p.out + ((size_t)(t_begin + tok0 + (rv ? r / G : 0)) * p.nh + kvh * G + (rv ? r % G : 0)) * hd;
-      for (int c0 = 0; c0 < hd; c0 += 16) {
+      for (int c0 = o_lo; c0 < o_hi; c0 += 16) {
         uint32_t o[16];
         tc::tmem_ld_16(tmem_o + lane_base + c0, o);
         tc::tmem_ld_wait();
