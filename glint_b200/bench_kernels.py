@@ -44,7 +44,7 @@ def _copies(nbytes):
     return max(2, int(math.ceil(2.5 * L2_BYTES / max(nbytes, 1))))
 
 
-def bench_gemm(M, N, K, gated=False, splits=0, iters=20):
+def bench_gemm(M, N, K, gated=False, splits=0, iters=20, path=None):
     from . import ops_tensor
     rows = 2 * N if gated else N
     n = min(_copies(rows * K * 2), 64)
@@ -52,13 +52,13 @@ def bench_gemm(M, N, K, gated=False, splits=0, iters=20):
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16 if gated else torch.float32)
     if gated:
-        fn = lambda i: ops_tensor.gemm_gated(x, ws[i], out, "gelu_tanh", force_splits=splits)
+        fn = lambda i: ops_tensor.gemm_gated(x, ws[i], out, "gelu_tanh", force_splits=splits, path=path)
     else:
-        fn = lambda i: ops_tensor.gemm(x, ws[i], out, force_splits=splits)
+        fn = lambda i: ops_tensor.gemm(x, ws[i], out, force_splits=splits, path=path)
     us = _time(fn, n, iters)
     nbytes = rows * K * 2 + M * K * 2 + out.numel() * out.element_size()
     flops = 2.0 * M * rows * K
-    return {"kernel": "gemm_gated" if gated else "gemm", "M": M, "N": N, "K": K, "splits": splits, "us": round(us, 2),
+    return {"kernel": ("gemm_gated" if gated else "gemm") + ("_" + path if path else ""), "M": M, "N": N, "K": K, "splits": splits, "us": round(us, 2),
             "GB/s": round(nbytes / us / 1e3, 1), "TFLOP/s": round(flops / us / 1e6, 1)}
 
 
@@ -144,15 +144,17 @@ def main():
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--page", type=int, default=16)
+    ap.add_argument("--path", choices=["tcgen05", "skinny"], default=None,
+                    help="which product kernel (default: the one the engine would take)")
     a = ap.parse_args()
     out = []
     if a.what == "gemm":
-        out.append(bench_gemm(a.m, a.n, a.k, False, a.splits, a.iters))
+        out.append(bench_gemm(a.m, a.n, a.k, False, a.splits, a.iters, a.path))
     elif a.what == "gated":
-        out.append(bench_gemm(a.m, a.n, a.k, True, a.splits, a.iters))
+        out.append(bench_gemm(a.m, a.n, a.k, True, a.splits, a.iters, a.path))
     elif a.what == "decode-shapes":
         for name, M, N, K, gated in gemma2_2b_decode_cases(a.batch):
-            out.append(dict(bench_gemm(M, N, K, gated, 0, a.iters), name=name))
+            out.append(dict(bench_gemm(M, N, K, gated, 0, a.iters, a.path), name=name))
         out.append(bench_attention_decode(a.batch, a.context, iters=a.iters))
         out.extend(bench_rows(a.batch))
     elif a.what == "prefill-shapes":

@@ -79,7 +79,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_pages,
                         __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int* __restrict__ counters,
                         int nh, int nkv, int hd, int page_size, int num_pages, float multiplier, float cap,
-                        int window, int splits, int stages, int* __restrict__ status) {
+                        int window, int splits, int stages, int whole_page, int* __restrict__ status) {
   extern __shared__ uint8_t dec_raw[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dec_raw) + 1023) & ~(uintptr_t)1023);
   const int t = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -137,7 +137,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       for (int j = 0; j < 32 && base + j < n_iter; ++j) {
         const int it = base + j;
         const int pg = __shfl_sync(0xffffffffu, page, j);
-        if (lane == 0) {
+        if (tc::elect_one()) {                   // elect.sync: operands of the copies stay in uniform registers
           const int s = it % stages;
           bool ok = true;
           if (it >= stages) ok = tc::mbar_wait(&sh->empty[s], ((it / stages) - 1) & 1, abort_flag);
@@ -145,9 +145,14 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             uint8_t* kdst = ring + (size_t)s * 2 * page_bytes;
             const int row = (pg * nkv + kvh) * page_size;
             tc::mbar_expect_tx(&sh->full[s], 2 * page_bytes);
-            for (int sub = 0; sub < nsub; ++sub) {
-              tc::tma_load_2d(kdst + sub * sub_bytes, &map_k, &sh->full[s], sub * 64, row);
-              tc::tma_load_2d(kdst + page_bytes + sub * sub_bytes, &map_v, &sh->full[s], sub * 64, row);
+            if (whole_page) {      // one box per page: the copy unit spends about 65 cycles on every box
+              tc::tma_load_3d(kdst, &map_k, &sh->full[s], 0, row, 0);
+              tc::tma_load_3d(kdst + page_bytes, &map_v, &sh->full[s], 0, row, 0);
+            } else {
+              for (int sub = 0; sub < nsub; ++sub) {
+                tc::tma_load_2d(kdst + sub * sub_bytes, &map_k, &sh->full[s], sub * 64, row);
+                tc::tma_load_2d(kdst + page_bytes + sub * sub_bytes, &map_v, &sh->full[s], sub * 64, row);
+              }
             }
           }
         }
@@ -415,10 +420,22 @@ static EncodeTiledFn decode_encode_fn() {
 }
 
 // A pool [pages][kv heads][page_size][head_dim] viewed as rows of head_dim, in boxes of
-// page_size rows x 64 columns with the 128-byte swizzle.
-static int pool_map(CUtensorMap* map, const void* pool, long long rows, int hd, int page_size) {
+// page_size rows x 64 columns with the 128-byte swizzle.  When head_dim is a multiple of 64 the
+// 64-column slices become a third dimension, and one box brings a whole page as
+// [slice][row][64 columns], which is the layout the separate boxes give.
+static int pool_map(CUtensorMap* map, const void* pool, long long rows, int hd, int page_size, bool whole_page) {
   EncodeTiledFn fn = decode_encode_fn();
   if (!fn) return GLINT_ERR_BAD_ARG;
+  if (whole_page) {
+    cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(hd / 64)};
+    cuuint64_t strides[2] = {(cuuint64_t)hd * 2, 128};
+    cuuint32_t box[3] = {64, (cuuint32_t)page_size, (cuuint32_t)(hd / 64)};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(pool), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? GLINT_OK : GLINT_ERR_BAD_ARG;
+  }
   cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
   cuuint32_t box[2] = {64, (cuuint32_t)page_size};
@@ -458,9 +475,10 @@ GLINT_API int glint_attention_decode(const void* q, const void* k_pool, const vo
   if (((uintptr_t)k_pool | (uintptr_t)v_pool) & 15 || ((uintptr_t)q & 3)) return GLINT_ERR_UNSUPPORTED_SIZE;
   CUtensorMap map_k, map_v;
   const long long rows = (long long)num_pages * nkv * page_size;
-  int rc = pool_map(&map_k, k_pool, rows, hd, page_size);
+  const int whole_page = (hd % 64 == 0 && page_size <= 256) ? 1 : 0;
+  int rc = pool_map(&map_k, k_pool, rows, hd, page_size, whole_page);
   if (rc != GLINT_OK) return rc;
-  rc = pool_map(&map_v, v_pool, rows, hd, page_size);
+  rc = pool_map(&map_v, v_pool, rows, hd, page_size, whole_page);
   if (rc != GLINT_OK) return rc;
   const int G = nh / nkv;
   const int HP = G < DEC_HEADS ? G : DEC_HEADS;
@@ -482,7 +500,7 @@ GLINT_API int glint_attention_decode(const void* q, const void* k_pool, const vo
     if (e != cudaSuccess) return (int)e;                                                                        \
     e = launch_kernel(attention_decode_kernel<HD>, grid, dim3(DEC_BLOCK), (size_t)smem, stream, map_k, map_v, qq,      \
                       positions, token_seq, block_table, max_pages, oo, partial, counters, nh, nkv, hd, page_size,      \
-                      num_pages, multiplier, cap, window, splits, stages, status);                                    \
+                      num_pages, multiplier, cap, window, splits, stages, whole_page, status);                        \
     if (e != cudaSuccess) return (int)e;                                                                        \
   }
   if (hd <= 64) LAUNCH(64)

@@ -5,7 +5,7 @@
 // share every key/value tile.  Keys come in tiles of 64 whose boundaries are multiples of 64 in
 // absolute position.
 //   warp 0     TMA: the query tile once (one 4-D box per 64 columns), then key and value tiles
-//              page by page into a two-deep ring (every lane issues one box)
+//              page by page into two-deep rings (one elected thread issues every box)
 //   warp 1     tcgen05.mma: S = Q K^T into tensor memory, then O += P V (V is the MN-major operand)
 //   warps 2-9  softmax: two threads share one row of S (tcgen05.ld), scale, soft-cap and mask it
 //              by absolute position, keeps the running max and sum in 32-bit, writes P as bfloat16
@@ -107,47 +107,69 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
   if (warp == 0) {
     // ---- producer ---------------------------------------------------------------------------------
-    if (lane == 0) {
+    // One elected thread issues every copy: inside elect.sync the compiler keeps addresses and
+    // coordinates in uniform registers, which the TMA instructions take directly (a copy issued
+    // from a region that is merely "lane 0" costs about 100 cycles, here about 40).
+    if (tc::elect_one()) {
       tc::mbar_expect_tx(&sh->q_full, (uint32_t)nsub * tok_per_tile * G * 128);
       for (int sub = 0; sub < nsub; ++sub)
         tc::tma_load_4d(sq + (size_t)sub * FA_Q_SUB, &map_q, &sh->q_full, sub * 64, 0, kvh, t_begin + tok0);
-    }
-    const int ppt = FA_N / p.page_size;                        // pages per tile
-    bool return_early = false;
-    const int* table = p.block_table + (size_t)seq * p.max_pages;
-    const int page_lo = kv_first / p.page_size, page_hi = pos_last / p.page_size;
-    const int half_boxes = ppt * nsub;                         // boxes of the key tile (and of the value tile)
-    for (int j = 0; j < n_tiles; ++j) {
-      const int b = j & 1;
-      const int first_page = (kv_begin + j * FA_N) / p.page_size;
-      for (int which = 0; which < 2; ++which) {                // keys first: they are needed first
-        uint64_t* full = which ? &sh->v_full[b] : &sh->k_full[b];
-        bool ok = true;
-        if (j >= 2) ok = tc::mbar_wait(which ? &sh->v_empty[b] : &sh->k_empty[b], ((j >> 1) - 1) & 1, abort_flag);
-        if (!__all_sync(0xffffffffu, ok)) return_early = true;
-        if (return_early) break;
-        if (lane == 0) tc::mbar_expect_tx(full, (uint32_t)nsub * FA_KV_SUB);
-        __syncwarp();
-        for (int bi = lane; bi < half_boxes; bi += 32) {
-          const int pi = bi / nsub, sub = bi % nsub;
-          const int page_idx = first_page + pi;
-          int page = 0;                                        // pages outside the range are masked below;
-          if (page_idx >= page_lo && page_idx <= page_hi) {    // they are filled from page 0 (finite values)
-            page = table[page_idx];
-            if (page < 0 || page >= p.num_pages) {
-              atomicExch(p.status, 3);
-              page = 0;
+      const int ppt = FA_N / p.page_size;                        // pages per tile: 4, 2 or 1
+      const int* table = p.block_table + (size_t)seq * p.max_pages;
+      const int page_lo = kv_first / p.page_size, page_hi = pos_last / p.page_size;
+      // The table entries of the next tile are loaded while this tile's copies are issued, and are
+      // looked at only when they are used: a check right behind each load would make the thread
+      // sit out one memory latency per page.  Pages outside [page_lo, page_hi] are masked by the
+      // softmax; they are filled from page 0.
+      auto fetch = [&](int j, int pi) -> int {
+        const int page_idx = (kv_begin + j * FA_N) / p.page_size + pi;
+        return table[min(max(page_idx, page_lo), page_hi)];
+      };
+      auto resolve = [&](int j, int pi, int page) -> int {
+        const int page_idx = (kv_begin + j * FA_N) / p.page_size + pi;
+        if (page_idx < page_lo || page_idx > page_hi) return 0;
+        if (page < 0 || page >= p.num_pages) {
+          atomicExch(p.status, 3);
+          return 0;
+        }
+        return page;
+      };
+      int pages[4], next[4];
+#pragma unroll
+      for (int pi = 0; pi < 4; ++pi) next[pi] = pi < ppt ? fetch(0, pi) : 0;
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int b = j & 1;
+#pragma unroll
+        for (int pi = 0; pi < 4; ++pi) pages[pi] = pi < ppt ? resolve(j, pi, next[pi]) : 0;
+        if (j + 1 < n_tiles) {
+#pragma unroll
+          for (int pi = 0; pi < 4; ++pi) next[pi] = pi < ppt ? fetch(j + 1, pi) : 0;
+        }
+        for (int which = 0; which < 2 && ok; ++which) {          // keys first: they are needed first
+          uint64_t* full = which ? &sh->v_full[b] : &sh->k_full[b];
+          if (j >= 2) ok = tc::mbar_wait(which ? &sh->v_empty[b] : &sh->k_empty[b], ((j >> 1) - 1) & 1, abort_flag);
+          if (!ok) break;
+          tc::mbar_expect_tx(full, (uint32_t)nsub * FA_KV_SUB);
+          const CUtensorMap* map = which ? &map_v : &map_k;
+          uint8_t* ring = (which ? sv : sk) + (size_t)b * nsub * FA_KV_SUB;
+#pragma unroll
+          for (int pi = 0; pi < 4; ++pi) {
+            if (pi < ppt) {
+              const int row = (pages[pi] * p.nkv + kvh) * p.page_size;
+              uint8_t* dst = ring + (size_t)pi * p.page_size * 128;
+              for (int sub = 0; sub < nsub; ++sub) tc::tma_load_2d(dst + (size_t)sub * FA_KV_SUB, map, full, sub * 64, row);
             }
           }
-          uint8_t* dst = (which ? sv : sk) + ((size_t)b * nsub + sub) * FA_KV_SUB + (size_t)pi * p.page_size * 128;
-          tc::tma_load_2d(dst, which ? &map_v : &map_k, full, sub * 64, (page * p.nkv + kvh) * p.page_size);
         }
       }
-      if (return_early) break;
     }
+    __syncwarp();
   } else if (warp == 1) {
     // ---- MMA issuer -------------------------------------------------------------------------------
-    if (lane == 0) {
+    // elect.sync rather than "lane 0": descriptors then live in uniform registers and one MMA costs
+    // the issuing thread about 45 cycles instead of about 105.
+    if (tc::elect_one()) {
       const uint32_t idesc_s = tc::idesc_bf16_f32(FA_M, FA_N);
       const uint32_t idesc_o = tc::idesc_bf16_f32_b_mn(FA_M, hd);
       const uint32_t q_addr = tc::smem_u32(sq), k_addr = tc::smem_u32(sk), v_addr = tc::smem_u32(sv);
@@ -168,12 +190,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (!tc::mbar_wait(&sh->k_full[b], (j >> 1) & 1, abort_flag)) return false;
         tc::fence_after_thread_sync();
         const uint32_t d = tmem_s + b * FA_N;
+        const uint64_t kd = b ? kd0[1] : kd0[0];
 #pragma unroll
         for (int ks = 0; ks < 16; ++ks) {
           if (ks < hd16) {
             const uint32_t oq = ((ks >> 2) * FA_Q_SUB + (ks & 3) * 32) >> 4;     // compile-time constants
             const uint32_t ok_ = ((ks >> 2) * FA_KV_SUB + (ks & 3) * 32) >> 4;
-            tc::mma_bf16_ss(d, qd0 + oq, kd0[b] + ok_, idesc_s, ks > 0 ? 1u : 0u);
+            tc::mma_bf16_ss(d, qd0 + oq, kd + ok_, idesc_s, ks > 0 ? 1u : 0u);
           }
         }
         tc::mma_commit(&sh->s_full[b]);
@@ -189,15 +212,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (ok) ok = tc::mbar_wait(&sh->v_full[b], (j >> 1) & 1, abort_flag);
         if (!ok) break;
         tc::fence_after_thread_sync();
+        const uint64_t vd = b ? vd0[1] : vd0[0];
 #pragma unroll
         for (int kk = 0; kk < FA_N / 16; ++kk)
-          tc::mma_bf16_ss(tmem_o, pd0 + 2 * kk, vd0[b] + (2048 >> 4) * kk, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          tc::mma_bf16_ss(tmem_o, pd0 + 2 * kk, vd + (2048 >> 4) * kk, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         tc::mma_commit(&sh->v_empty[b]);
         tc::mma_commit(&sh->p_free);             // P and this row of O may be touched again
         if (j + 2 < n_tiles) ok = issue_s(j + 2);
       }
       tc::mma_commit(&sh->o_full);
     }
+    __syncwarp();
   } else {
     // ---- softmax, correction and epilogue: two threads per row of the tile ------------------------------
     // Warps 2..5 take columns [0, 32) of the score tile, warps 6..9 columns [32, 64); a warp reaches

@@ -28,7 +28,7 @@ NVCC_FLAGS = ARCH_FLAGS + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPI
 
 LIBRARIES = {
     "core": ["elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu", "sample_noalloc.cu"],
-    "tensor": ["gemm_tcgen05.cu", "attention_decode.cu", "attention_prefill.cu", "attention_tcgen05.cu"],
+    "tensor": ["gemm_tcgen05.cu", "gemm_skinny.cu", "attention_decode.cu", "attention_prefill.cu", "attention_tcgen05.cu"],
 }
 HEADERS = ["common.cuh", "tcgen05.cuh", "noalloc.h"]
 

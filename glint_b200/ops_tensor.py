@@ -1,6 +1,7 @@
 """Python face of the tensor-core kernels (bfloat16 only): tcgen05 matrix products."""
 from __future__ import annotations
 
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -12,6 +13,7 @@ _P, _I, _F, _L = c_void_p, c_int, c_float, c_longlong
 
 _SIGNATURES = {
     "glint_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _L, _F, _I, _I, _I, _P, _P, _P, _I, _P],
+    "glint_gemm_skinny": [_P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "glint_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P],
     "glint_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
     "glint_attention_tcgen05": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
@@ -45,7 +47,29 @@ def gemm_supported(M, N, K):
     return M > 0 and N > 0 and K > 0 and K % 8 == 0
 
 
-def gemm(a, w, out, cap=0.0, status=None, force_splits=0):
+SKINNY_MAX_TOKENS = int(os.environ.get("GLINT_SKINNY_MAX_TOKENS", "16"))   # 0 switches the kernel off
+SKINNY_MAX_FEATURES = 65536      # beyond this the tiled kernel streams at the memory's speed anyway
+SKINNY_WIDE_LIMIT = 12 << 20     # 9 to 16 tokens: only products whose launch cost outweighs their stream
+
+
+def skinny_supported(M, N, K):
+    return 1 <= M <= 16 and N >= 1 and K >= 64 and K % 64 == 0
+
+
+def takes_skinny(M, N, K, force_splits, path):
+    """Few tokens go to the weight-streaming kernel; ``path`` ("skinny", "tcgen05") overrides."""
+    if path == "tcgen05" or force_splits:
+        return False
+    if path == "skinny":
+        if not skinny_supported(M, N, K):
+            raise KernelError(f"the weight-streaming product takes up to 16 tokens and K in steps of 64, not M={M} K={K}")
+        return True
+    if M > SKINNY_MAX_TOKENS or N > SKINNY_MAX_FEATURES or not skinny_supported(M, N, K):
+        return False
+    return M <= 8 or N * K <= SKINNY_WIDE_LIMIT
+
+
+def gemm(a, w, out, cap=0.0, status=None, force_splits=0, path=None):
     """out[M, N] = a[M, K] @ w[N, K]^T with bfloat16 operands, float32 accumulation; ``out`` is
     float32 or bfloat16; ``cap`` > 0 applies the soft cap."""
     M, K = a.shape
@@ -53,6 +77,10 @@ def gemm(a, w, out, cap=0.0, status=None, force_splits=0):
     ops.require(a, torch.bfloat16, "a"); ops.require(w, torch.bfloat16, "w"); ops.require(out, None, "out")
     if w.shape[1] != K or tuple(out.shape) != (M, N) or out.dtype not in (torch.float32, torch.bfloat16):
         raise KernelError(f"gemm shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if takes_skinny(M, N, K, force_splits, path):
+        ops.check(lib().glint_gemm_skinny(ops.ptr(a), ops.ptr(w), ops.ptr(out), int(out.dtype == torch.bfloat16), M, N,
+                                          K, cap or 0.0, 0, 0, 0, ops.stream()), "gemm_skinny")
+        return
     ws, counters = scratch(a.device)
     st = status if status is not None else counters[-1:]
     ops.check(lib().glint_gemm_tcgen05(ops.ptr(a), ops.ptr(w), ops.ptr(out), int(out.dtype == torch.bfloat16), M, N,
@@ -60,7 +88,7 @@ def gemm(a, w, out, cap=0.0, status=None, force_splits=0):
                                        force_splits, ops.stream()), "gemm_tcgen05")
 
 
-def gemm_gated(a, w_gate_up, out, activation, status=None, force_splits=0):
+def gemm_gated(a, w_gate_up, out, activation, status=None, force_splits=0, path=None):
     """out[M, I] (bfloat16) = act(a @ w[:I]^T) * (a @ w[I:]^T) for w_gate_up [2I, K], in one kernel."""
     M, K = a.shape
     I = w_gate_up.shape[0] // 2
@@ -68,6 +96,10 @@ def gemm_gated(a, w_gate_up, out, activation, status=None, force_splits=0):
     if w_gate_up.shape[1] != K or tuple(out.shape) != (M, I):
         raise KernelError(f"gated gemm shapes do not fit: a {tuple(a.shape)}, w {tuple(w_gate_up.shape)}, "
                           f"out {tuple(out.shape)}")
+    if takes_skinny(M, I, K, force_splits, path):
+        ops.check(lib().glint_gemm_skinny(ops.ptr(a), ops.ptr(w_gate_up), ops.ptr(out), 1, M, I, K, 0.0, 1, I,
+                                          ops.ACTIVATIONS[activation], ops.stream()), "gemm_skinny (gated)")
+        return
     ws, counters = scratch(a.device)
     st = status if status is not None else counters[-1:]
     ops.check(lib().glint_gemm_tcgen05(ops.ptr(a), ops.ptr(w_gate_up), ops.ptr(out), 1, M, I, K, 2 * I, 0.0, 1, I,

@@ -25,10 +25,53 @@ def test_gemm_tcgen05_against_float32(M, N, K):
     w = _bf16(torch.randn(N, K, device=DEV) * 0.1)
     want = a.float() @ w.float().T
     out = torch.full((M, N), float("nan"), device=DEV)
-    ops_tensor.gemm(a, w, out)
+    ops_tensor.gemm(a, w, out, path="tcgen05")
     torch.cuda.synchronize()
     err = (out - want).abs().max().item()
     assert err <= 2e-3 * max(1.0, want.abs().max().item()), (M, N, K, err)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 4096, 2304), (5, 203, 192), (16, 2304, 2048), (3, 17, 9216),
+                                   (9, 1000, 320), (8, 16, 64), (13, 50, 576)])
+def test_gemm_skinny_against_float32(M, N, K):
+    """The weight-streaming product for a handful of tokens: odd widths, one token, sixteen."""
+    from glint_b200 import ops_tensor
+    torch.manual_seed(M * 11 + N)
+    a = _bf16(torch.randn(M, K, device=DEV))
+    w = _bf16(torch.randn(N, K, device=DEV) * 0.1)
+    want = a.float() @ w.float().T
+    out = torch.full((M, N), float("nan"), device=DEV)
+    ops_tensor.gemm(a, w, out, path="skinny")
+    again = torch.full((M, N), float("nan"), device=DEV)
+    ops_tensor.gemm(a, w, again, path="skinny")
+    torch.cuda.synchronize()
+    err = (out - want).abs().max().item()
+    assert err <= 2e-3 * max(1.0, want.abs().max().item()), (M, N, K, err)
+    assert torch.equal(out, again)                                   # the order of the sums is fixed
+    # a token's row alone and among others: up to 8 tokens the sums run in the same order (bit for
+    # bit); 9 to 16 tokens split K differently among the warps (float32 rounding of the sum)
+    alone = torch.empty(1, N, device=DEV)
+    ops_tensor.gemm(a[M - 1:].contiguous(), w, alone, path="skinny")
+    if M <= 8:
+        assert torch.equal(alone[0], out[M - 1])
+    else:
+        assert (alone[0] - out[M - 1]).abs().max().item() <= 2e-5 * max(1.0, want.abs().max().item())
+    out16 = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    ops_tensor.gemm(a, w, out16, cap=30.0, path="skinny")
+    capped = 30.0 * torch.tanh(want / 30.0)
+    assert (out16.float() - capped).abs().max().item() <= 1e-2 * max(1.0, capped.abs().max().item())
+
+
+def test_gemm_skinny_refuses_what_it_cannot_do():
+    from glint_b200 import ops_tensor
+    from glint_b200.errors import KernelError
+    a = _bf16(torch.randn(4, 72, device=DEV))
+    w = _bf16(torch.randn(32, 72, device=DEV))
+    with pytest.raises(KernelError):
+        ops_tensor.gemm(a, w, torch.empty(4, 32, device=DEV), path="skinny")       # K is no multiple of 64
+    out = torch.empty(4, 32, device=DEV)
+    ops_tensor.gemm(a, w, out)                                                     # the tiled kernel takes it
+    assert (out - a.float() @ w.float().T).abs().max().item() < 0.05
 
 
 @pytest.mark.parametrize("splits", [1, 2, 3, 7])
@@ -94,7 +137,25 @@ def test_gemm_gated_against_float32(M, I, K, act):
         else (lambda x: x * torch.sigmoid(x))
     want = actf(g) * u
     out = torch.empty(M, I, device=DEV, dtype=torch.bfloat16)
-    ops_tensor.gemm_gated(a, w, out, act)
+    ops_tensor.gemm_gated(a, w, out, act, path="tcgen05")
+    torch.cuda.synchronize()
+    err = (out.float() - want).abs().max().item()
+    assert err <= 1e-2 * max(1.0, want.abs().max().item()), err
+
+
+@pytest.mark.parametrize("M,I,K,act", [(7, 320, 128, "gelu_tanh"), (8, 9216, 2304, "gelu_tanh"), (16, 203, 192, "silu"),
+                                       (1, 24, 64, "silu")])
+def test_gemm_skinny_gated_against_float32(M, I, K, act):
+    from glint_b200 import ops_tensor
+    torch.manual_seed(4)
+    a = _bf16(torch.randn(M, K, device=DEV))
+    w = _bf16(torch.randn(2 * I, K, device=DEV) * 0.1)
+    g, u = a.float() @ w[:I].float().T, a.float() @ w[I:].float().T
+    actf = (lambda x: 0.5 * x * (1 + torch.tanh(0.7978846 * (x + 0.044715 * x ** 3)))) if act == "gelu_tanh" \
+        else (lambda x: x * torch.sigmoid(x))
+    want = actf(g) * u
+    out = torch.empty(M, I, device=DEV, dtype=torch.bfloat16)
+    ops_tensor.gemm_gated(a, w, out, act, path="skinny")
     torch.cuda.synchronize()
     err = (out.float() - want).abs().max().item()
     assert err <= 1e-2 * max(1.0, want.abs().max().item()), err
