@@ -44,11 +44,13 @@ def _copies(nbytes):
     return max(2, int(math.ceil(2.5 * L2_BYTES / max(nbytes, 1))))
 
 
-def bench_gemm(M, N, K, gated=False, splits=0, iters=20, path=None):
+def bench_gemm(M, N, K, gated=False, splits=0, iters=20, path=None, resident=False):
     from . import ops_tensor
     rows = 2 * N if gated else N
     n = min(_copies(rows * K * 2), 64)
-    ws = [torch.randn(rows, K, device=DEV).to(torch.bfloat16) * 0.05 for _ in range(n)]
+    ws = [torch.randn(rows, K, device=DEV).to(torch.bfloat16) * 0.05 for _ in range(1 if resident else n)]
+    if resident:
+        ws = ws * n                                           # the same weights every launch: they stay in L2
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16 if gated else torch.float32)
     if gated:
@@ -144,6 +146,7 @@ def main():
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--page", type=int, default=16)
+    ap.add_argument("--resident", action="store_true", help="products: reuse one set of weights (they stay in L2)")
     ap.add_argument("--path", choices=["tcgen05", "skinny"], default=None,
                     help="which product kernel (default: the one the engine would take)")
     a = ap.parse_args()
@@ -154,7 +157,7 @@ def main():
         out.append(bench_gemm(a.m, a.n, a.k, True, a.splits, a.iters, a.path))
     elif a.what == "decode-shapes":
         for name, M, N, K, gated in gemma2_2b_decode_cases(a.batch):
-            out.append(dict(bench_gemm(M, N, K, gated, 0, a.iters, a.path), name=name))
+            out.append(dict(bench_gemm(M, N, K, gated, 0, a.iters, a.path, a.resident), name=name))
         out.append(bench_attention_decode(a.batch, a.context, iters=a.iters))
         out.extend(bench_rows(a.batch))
     elif a.what == "prefill-shapes":

@@ -9,9 +9,11 @@
 // operands read straight from shared memory and nothing is padded to a 128-row tile.  Scores,
 // soft cap, running max/sum and the output accumulator are 32-bit (src/tensor/flash.rs:65-123);
 // probabilities are rounded to bfloat16 for the second product.  The four warps are merged in
-// shared memory in warp order.  With more than one split, partial results go to a workspace and
-// the block that arrives last at the (token, kv head) counter merges the splits in split order
-// and resets the counter: no spinning, no second launch, a fixed order of addition.
+// shared memory in warp order.  With more than one split, the splits of a (token, kv head) are
+// the blocks of one thread-block cluster: every block leaves its partial result in its own shared
+// memory, and after a cluster barrier each block adds up, in split order, its share of the output
+// elements from the shared memory of all of them (distributed shared memory): no workspace in
+// global memory, no counter, no second launch, a fixed order of addition.
 // Score = (q.k) * multiplier, then cap * tanh(score / cap) (src/tensor/flash.rs:76-87); keys from
 // max(0, pos - window + 1) to pos (src/transformer/forward.rs:574-582).
 #include "common.cuh"
@@ -23,7 +25,7 @@ constexpr int DEC_WARPS = 4;                      // consumer warps
 constexpr int DEC_THREADS = DEC_WARPS * 32;
 constexpr int DEC_BLOCK = DEC_THREADS + 32;       // plus the producer warp
 constexpr int DEC_MAX_STAGES = 12;
-constexpr int DEC_MAX_SPLITS = 64;
+constexpr int DEC_MAX_SPLITS = 16;                // blocks of a cluster
 constexpr int DEC_HEADS = 8;                      // query heads per pass (the MMA's N)
 constexpr int SUB_BYTES_PER_ROW = 128;            // one swizzle row: 64 bf16
 
@@ -66,10 +68,23 @@ struct DecodeShared {
   uint64_t full[DEC_MAX_STAGES];
   uint64_t empty[DEC_MAX_STAGES];
   int abort_flag;
-  int is_last;
-  float w[DEC_MAX_SPLITS];
-  float inv_l;
 };
+
+// ---- thread-block cluster -----------------------------------------------------------------------
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the address, in the cluster's shared window, of this block's shared address `addr` in block `rank`
+__device__ __forceinline__ uint32_t cluster_map(uint32_t addr, int rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float cluster_load(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
 
 // HD: register capacity (head_dim <= HD; head_dim and page_size are multiples of 16).
 template <int HD>
@@ -77,8 +92,7 @@ __global__ void __launch_bounds__(DEC_BLOCK, 2)
 attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                         const __nv_bfloat16* __restrict__ q, const int* __restrict__ positions,
                         const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_pages,
-                        __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int* __restrict__ counters,
-                        int nh, int nkv, int hd, int page_size, int num_pages, float multiplier, float cap,
+                        __nv_bfloat16* __restrict__ out, int nh, int nkv, int hd, int page_size, int num_pages, float multiplier, float cap,
                         int window, int splits, int stages, int whole_page, int* __restrict__ status) {
   extern __shared__ uint8_t dec_raw[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dec_raw) + 1023) & ~(uintptr_t)1023);
@@ -103,7 +117,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   const int stride_f = hd + 2;
 
   float* merge = reinterpret_cast<float*>(ring + (size_t)stages * 2 * page_bytes);
-  DecodeShared* sh = reinterpret_cast<DecodeShared*>(merge + (size_t)DEC_WARPS * HP * stride_f);
+  float* xchg = merge + (size_t)DEC_WARPS * HP * stride_f;      // [G][hd + 2]: what the other splits read
+  DecodeShared* sh = reinterpret_cast<DecodeShared*>(xchg + (splits > 1 ? (size_t)G * stride_f : 0));
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -111,7 +126,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       tc::mbar_init(&sh->empty[s], 1);
     }
     sh->abort_flag = 0;
-    sh->is_last = 0;
     tc::fence_barrier_init();
     tc::tma_prefetch_desc(&map_k);
     tc::tma_prefetch_desc(&map_v);
@@ -158,9 +172,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
       }
     }
-    return;
-  }
-
+  } else {
   // ---- consumer warps ----------------------------------------------------------------------------------
   const int g = lane >> 2, tq = lane & 3;
   const float score_scale = cap > 0.f ? multiplier / cap : multiplier;
@@ -318,85 +330,54 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         if (splits == 1) {
           out[((size_t)t * nh + head) * hd + d] = __float2bfloat16_rn(L > 0.f ? ov / L : 0.f);
         } else {
-          partial[(((size_t)t * nh + head) * splits + split) * stride_f + d] = ov;
+          xchg[(size_t)hg * stride_f + d] = ov;
         }
       }
       if (splits > 1 && threadIdx.x == 0) {
-        float* pp = partial + (((size_t)t * nh + head) * splits + split) * stride_f;
-        pp[hd] = M;
-        pp[hd + 1] = L;
+        xchg[(size_t)hg * stride_f + hd] = M;
+        xchg[(size_t)hg * stride_f + hd + 1] = L;
       }
     }
     consumer_sync();   // the merge area is reused by the next pass
   }
 
-  // ---- the last block of this (token, kv head) merges the splits, in split order ---------------------
+  }  // consumer warps
+
+  // ---- the splits of this (token, kv head) are merged across the cluster, in split order ------------
   if (splits > 1) {
-    __threadfence();
-    consumer_sync();
-    if (threadIdx.x == 0) {
-      const int prev = atomicAdd(&counters[t * nkv + kvh], 1);
-      sh->is_last = (prev == splits - 1);
-    }
-    consumer_sync();
-    if (sh->is_last) {
-      __threadfence();
-      for (int hg = 0; hg < G; ++hg) {
-        const size_t row = (size_t)t * nh + kvh * G + hg;
-        const float* p = partial + row * splits * stride_f;
-        if (threadIdx.x < 32) {
-          float ms[2], ls[2];
+    cluster_sync();                                  // every block's xchg is written and visible
+    if (warp < DEC_WARPS) {
+      const int total = G * hd;
+      const int per = (total + splits - 1) / splits; // this block's share of the output elements
+      const uint32_t xchg_addr = tc::smem_u32(xchg);
+      for (int e = split * per + (int)threadIdx.x; e < min(total, (split + 1) * per); e += DEC_THREADS) {
+        const int hg = e / hd, d = e - hg * hd;
+        const uint32_t row_addr = xchg_addr + (uint32_t)(hg * stride_f) * 4;
+        float ms[DEC_MAX_SPLITS], ls[DEC_MAX_SPLITS], os[DEC_MAX_SPLITS];
+        float M = -INFINITY;
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int s = threadIdx.x + 32 * u;
-            ms[u] = s < splits ? __ldcg(p + (size_t)s * stride_f + hd) : -INFINITY;
-            ls[u] = s < splits ? __ldcg(p + (size_t)s * stride_f + hd + 1) : 0.f;
-          }
-          const float M = warp_max(fmaxf(ms[0], ms[1]));
-          float L = 0.f;
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const float ws = ms[u] == -INFINITY ? 0.f : __expf(ms[u] - M);
-            sh->w[threadIdx.x + 32 * u] = ws;
-            L += ls[u] * ws;
-          }
-          L = warp_sum(L);
-          if (threadIdx.x == 0) sh->inv_l = L > 0.f ? 1.0f / L : 0.f;
-        }
-        consumer_sync();
-        // warp w adds splits w, w+4, ... (all their loads in flight); then the 4 warps are added in order
-        for (int d0 = 0; d0 < hd; d0 += 32 * 4) {
-          const int d = d0 + lane * 4;
-          if (d < hd) {
-            float4 ov = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-            for (int sidx = warp; sidx < splits; sidx += DEC_WARPS) {
-              const float2 lo = __ldcg(reinterpret_cast<const float2*>(p + (size_t)sidx * stride_f + d));
-              const float2 hi = __ldcg(reinterpret_cast<const float2*>(p + (size_t)sidx * stride_f + d + 2));
-              const float ws = sh->w[sidx];
-              ov.x += lo.x * ws;
-              ov.y += lo.y * ws;
-              ov.z += hi.x * ws;
-              ov.w += hi.y * ws;
-            }
-            float* dst = merge + (size_t)warp * stride_f + d;
-            dst[0] = ov.x;
-            dst[1] = ov.y;
-            dst[2] = ov.z;
-            dst[3] = ov.w;
+        for (int sidx = 0; sidx < DEC_MAX_SPLITS; ++sidx) {
+          if (sidx < splits) {
+            const uint32_t peer = cluster_map(row_addr, sidx);
+            ms[sidx] = cluster_load(peer + hd * 4);
+            ls[sidx] = cluster_load(peer + (hd + 1) * 4);
+            os[sidx] = cluster_load(peer + d * 4);
+            M = fmaxf(M, ms[sidx]);
           }
         }
-        consumer_sync();
-        for (int d = threadIdx.x; d < hd; d += DEC_THREADS) {
-          float ov = 0.f;
+        float L = 0.f, ov = 0.f;
 #pragma unroll
-          for (int wv = 0; wv < DEC_WARPS; ++wv) ov += merge[(size_t)wv * stride_f + d];
-          out[row * hd + d] = __float2bfloat16_rn(ov * sh->inv_l);
+        for (int sidx = 0; sidx < DEC_MAX_SPLITS; ++sidx) {
+          if (sidx < splits) {
+            const float ws = ms[sidx] == -INFINITY ? 0.f : __expf(ms[sidx] - M);
+            L += ls[sidx] * ws;
+            ov += os[sidx] * ws;
+          }
         }
-        consumer_sync();
+        out[((size_t)t * nh + kvh * G + hg) * hd + d] = __float2bfloat16_rn(L > 0.f ? ov / L : 0.f);
       }
-      if (threadIdx.x == 0) counters[t * nkv + kvh] = 0;   // ready for the next launch on this stream
     }
+    cluster_sync();                                  // nobody leaves while its shared memory is being read
   }
   if (threadIdx.x == 0 && sh->abort_flag) atomicExch(status, 4);
 }
@@ -450,27 +431,25 @@ static int pool_map(CUtensorMap* map, const void* pool, long long rows, int hd, 
 
 using namespace glint;
 
-GLINT_API long long glint_attention_decode_partial_floats(int T, int nh, int hd, int splits) {
-  return (long long)T * nh * splits * (hd + 2);
-}
+// Largest number of splits (blocks of one cluster) this device takes: 8 everywhere, 16 where the
+// driver schedules clusters of that size for this kernel's launch shape.
+GLINT_API int glint_attention_decode_max_splits() { return DEC_MAX_SPLITS; }
 
 GLINT_API int glint_attention_decode_supported(int nh, int nkv, int hd, int page_size) {
   return (nkv > 0 && nh % nkv == 0 && hd % 16 == 0 && hd >= 16 && hd <= 256 && page_size % 16 == 0 &&
           page_size >= 16 && page_size <= 256) ? 1 : 0;
 }
 
-// head_dim a multiple of 16 up to 256, page_size a multiple of 16 up to 256, splits up to 64.  When
-// splits > 1, `partial` must hold glint_attention_decode_partial_floats(...) floats and `counters`
-// T * nkv zeroed ints (the kernel leaves them zero).
+// head_dim a multiple of 16 up to 256, page_size a multiple of 16 up to 256, splits up to 16 (more
+// than 8 need a device that schedules such clusters; the launch fails with an error otherwise).
 GLINT_API int glint_attention_decode(const void* q, const void* k_pool, const void* v_pool, const int* positions,
                                      const int* token_seq, const int* block_table, int max_pages, void* out,
-                                     float* partial, int* counters, int T, int nh, int nkv, int hd, int page_size,
+                                     int T, int nh, int nkv, int hd, int page_size,
                                      int num_pages, float multiplier, float cap, int window, int splits,
                                      int* status, cudaStream_t stream) {
   if (T <= 0) return GLINT_OK;
   if (page_size <= 0 || splits < 1 || nkv <= 0) return GLINT_ERR_BAD_ARG;
   if (!glint_attention_decode_supported(nh, nkv, hd, page_size)) return GLINT_ERR_UNSUPPORTED_SIZE;
-  if (splits > 1 && (!partial || !counters)) return GLINT_ERR_BAD_ARG;
   if (nkv > 65535 || splits > DEC_MAX_SPLITS) return GLINT_ERR_UNSUPPORTED_SIZE;
   if (((uintptr_t)k_pool | (uintptr_t)v_pool) & 15 || ((uintptr_t)q & 3)) return GLINT_ERR_UNSUPPORTED_SIZE;
   CUtensorMap map_k, map_v;
@@ -483,7 +462,8 @@ GLINT_API int glint_attention_decode(const void* q, const void* k_pool, const vo
   const int G = nh / nkv;
   const int HP = G < DEC_HEADS ? G : DEC_HEADS;
   const long long page_bytes = (long long)((hd + 63) / 64) * page_size * SUB_BYTES_PER_ROW;
-  const long long fixed = (long long)DEC_WARPS * HP * (hd + 2) * 4 + sizeof(DecodeShared) + 1024 + 64;
+  const long long fixed = (long long)DEC_WARPS * HP * (hd + 2) * 4 + (splits > 1 ? (long long)G * (hd + 2) * 4 : 0) +
+                          sizeof(DecodeShared) + 1024 + 64;
   // a multiple of the consumer warps (see the kernel), as many as let two blocks share an SM
   int stages = (int)((110 * 1024 - fixed) / (2 * page_bytes)) / DEC_WARPS * DEC_WARPS;
   if (stages > DEC_MAX_STAGES) stages = DEC_MAX_STAGES;
@@ -498,9 +478,13 @@ GLINT_API int glint_attention_decode(const void* q, const void* k_pool, const vo
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                          (int)smem);                                                            \
     if (e != cudaSuccess) return (int)e;                                                                        \
-    e = launch_kernel(attention_decode_kernel<HD>, grid, dim3(DEC_BLOCK), (size_t)smem, stream, map_k, map_v, qq,      \
-                      positions, token_seq, block_table, max_pages, oo, partial, counters, nh, nkv, hd, page_size,      \
-                      num_pages, multiplier, cap, window, splits, stages, whole_page, status);                        \
+    if (splits > 8) {                                                                                           \
+      e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);   \
+      if (e != cudaSuccess) return (int)e;                                                                      \
+    }                                                                                                           \
+    e = launch_kernel_cluster(attention_decode_kernel<HD>, grid, dim3(DEC_BLOCK), (size_t)smem, stream, splits,  \
+                              map_k, map_v, qq, positions, token_seq, block_table, max_pages, oo, nh, nkv, hd,    \
+                              page_size, num_pages, multiplier, cap, window, splits, stages, whole_page, status); \
     if (e != cudaSuccess) return (int)e;                                                                        \
   }
   if (hd <= 64) LAUNCH(64)

@@ -14,7 +14,7 @@ _P, _I, _F, _L = c_void_p, c_int, c_float, c_longlong
 _SIGNATURES = {
     "glint_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _L, _F, _I, _I, _I, _P, _P, _P, _I, _P],
     "glint_gemm_skinny": [_P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
-    "glint_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P],
+    "glint_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P],
     "glint_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
     "glint_attention_tcgen05": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
 }
@@ -122,13 +122,17 @@ def prefill_supported(nh, nkv, hd):
     return nkv > 0 and nh % nkv == 0 and nh // nkv <= 64 and hd % 16 == 0 and 16 <= hd <= 256
 
 
-_partials = {}
-
-
 def decode_splits(tokens, nkv, max_context):
-    """One wave of blocks (2 fit on each of the 148 SMs), each split with at least 128 keys."""
+    """Blocks for about one wave (2 fit on each of the 148 SMs), each split with at least 128 keys;
+    the splits of a token are one thread-block cluster: a power of two up to 8 (measured: clusters
+    of 9 to 16 blocks, or of 6, take 1.5 times as long when there are many of them), 16 only for
+    one or two requests, where nothing else puts more SMs to work."""
     want = 296 // max(1, tokens * nkv)
-    return max(1, min(want, max_context // 128, 32))
+    limit = 16 if tokens * nkv <= 8 else 8
+    splits = max(1, min(want, max_context // 128, limit))
+    while splits & (splits - 1):          # a power of two: other cluster sizes are scheduled poorly
+        splits &= splits - 1
+    return splits
 
 
 def attention_decode(q, k_pool, v_pool, positions, token_seq, block_table, out, nh, nkv, hd, page_size, num_pages,
@@ -137,21 +141,11 @@ def attention_decode(q, k_pool, v_pool, positions, token_seq, block_table, out, 
     T = q.shape[0]
     ops.require(q, torch.bfloat16, "q"); ops.require(k_pool, torch.bfloat16, "k_pool")
     ops.require(v_pool, torch.bfloat16, "v_pool"); ops.require(out, torch.bfloat16, "out")
-    partial = counters = None
-    if splits > 1:
-        need = T * nh * splits * (hd + 2)
-        key = str(q.device)
-        entry = _partials.get(key)
-        if entry is None or entry[0].numel() < need or entry[1].numel() < T * nkv:
-            entry = (torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device),
-                     torch.zeros(max(T * nkv, 4096), dtype=torch.int32, device=q.device))
-            _partials[key] = entry
-        partial, counters = entry
     ops.check(lib().glint_attention_decode(ops.ptr(q), ops.ptr(k_pool), ops.ptr(v_pool), ops.ptr(positions),
                                            ops.ptr(token_seq), ops.ptr(block_table), block_table.shape[1],
-                                           ops.ptr(out), ops.ptr(partial), ops.ptr(counters), T, nh, nkv, hd,
-                                           page_size, num_pages, multiplier, cap or 0.0, window or 0, splits,
-                                           ops.ptr(status), ops.stream()), "attention_decode")
+                                           ops.ptr(out), T, nh, nkv, hd, page_size, num_pages, multiplier,
+                                           cap or 0.0, window or 0, splits, ops.ptr(status), ops.stream()),
+              "attention_decode")
 
 
 def attention_prefill(q, k_pool, v_pool, cu_seqlens, seq_start, block_table, out, n_seqs, max_q_len, nh, nkv, hd,
