@@ -87,7 +87,9 @@ static inline bool pdl_enabled() {
   return on != 0;
 }
 
-// `cluster_z` > 1 launches the grid as thread-block clusters of that many blocks along z.
+// `cluster_z` > 1 launches the grid as thread-block clusters of that many blocks along z.  Such a
+// launch does not start early under its predecessor: measured, clusters placed among the blocks
+// of a kernel that is still running cost a decode step 10 us per layer.
 template <typename... KArgs, typename... Args>
 static inline cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                                                 cudaStream_t stream, int cluster_z, Args... args) {
@@ -98,7 +100,7 @@ static inline cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 g
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  attr[0].val.programmaticStreamSerializationAllowed = (pdl_enabled() && cluster_z <= 1) ? 1 : 0;
   cfg.numAttrs = 1;
   if (cluster_z > 1) {
     attr[1].id = cudaLaunchAttributeClusterDimension;

@@ -52,12 +52,30 @@ struct SkinnyParams {
   float cap;
   int dual_offset;      // gated: row of w where the second (up) half begins
   int activation;       // gated: 0 gelu_tanh, 1 silu
+  // rotary mode: w is [q heads | k heads | v heads] x head_dim rows; q is rotated into q_out, k is
+  // rotated and v copied into the cache row of each token's position
+  const int* positions;
+  const int* token_slot;
+  const int* block_table;
+  int max_pages;
+  const float* inv_freq;
+  float factor;
+  __nv_bfloat16* q_out;
+  __nv_bfloat16* k_pool;
+  __nv_bfloat16* v_pool;
+  int nh, nkv, hd, page_size, num_pages;
+  int* status;
 };
 
-// NT: token tiles of 8; GATED: two weight rows per feature and act(gate) * up in the epilogue;
-// U: steps in flight per warp.
-template <int NT, bool GATED, int U>
+constexpr int SK_PLAIN = 0, SK_GATED = 1, SK_ROPE = 2;
+
+// NT: token tiles of 8; U: steps in flight per warp.  MODE: plain (soft cap in the epilogue), gated
+// (two weight rows per feature and act(gate) * up in the epilogue) or rotary (see SkinnyParams:
+// a block owns 8 rotation pairs (j, j + head_dim / 2) of one q or k head, or 16 dims of a v head,
+// so that the epilogue holds both halves of every pair it turns; src/tensor/ops.rs:212-245).
+template <int NT, int MODE, int U>
 __global__ void __launch_bounds__(SK_MAX_WARPS * 32) gemm_skinny_kernel(const SkinnyParams p) {
+  constexpr bool GATED = MODE == SK_GATED;
   constexpr int SETS = GATED ? 2 : 1;
   __shared__ float red[SK_MAX_WARPS][SETS][SK_ROWS][8 * NT + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -67,7 +85,20 @@ __global__ void __launch_bounds__(SK_MAX_WARPS * 32) gemm_skinny_kernel(const Sk
   const int K = p.K;
   const int n_steps = K / SK_STEP;
   // rows beyond N are clamped for the loads and masked at the store
-  const int ra = min(row0 + g, p.N - 1), rb = min(row0 + g + 8, p.N - 1);
+  int ra = min(row0 + g, p.N - 1), rb = min(row0 + g + 8, p.N - 1);
+  int rope_head = 0, rope_sub = 0;
+  if (MODE == SK_ROPE) {
+    const int per_head = p.hd >> 4;
+    rope_head = blockIdx.x / per_head;
+    rope_sub = blockIdx.x - rope_head * per_head;
+    if (rope_head < p.nh + p.nkv) {                  // q or k: dims 8 sub + g and that + head_dim / 2
+      ra = rope_head * p.hd + rope_sub * 8 + g;
+      rb = ra + (p.hd >> 1);
+    } else {                                         // v: 16 consecutive dims
+      ra = rope_head * p.hd + rope_sub * 16 + g;
+      rb = ra + 8;
+    }
+  }
   const __nv_bfloat16* wrow[SETS][2];
   wrow[0][0] = p.w + (size_t)ra * K + 8 * tq;
   wrow[0][1] = p.w + (size_t)rb * K + 8 * tq;
@@ -156,6 +187,52 @@ __global__ void __launch_bounds__(SK_MAX_WARPS * 32) gemm_skinny_kernel(const Sk
       red[warp][set][g + 8][nt * 8 + 2 * tq + 1] = acc[set][nt][3];
     }
   __syncthreads();
+  if (MODE == SK_ROPE) {
+    // thread (pair j, token): both halves of the pair, turned by the token's position
+    if (threadIdx.x < 64) {
+      const int j = threadIdx.x & 7, tok = threadIdx.x >> 3;
+      if (tok < p.M) {
+        float v0 = 0.f, v1 = 0.f;
+        for (int w = 0; w < n_warps; ++w) {
+          v0 += red[w][0][j][tok];
+          v1 += red[w][0][j + 8][tok];
+        }
+        const int pos = p.positions[tok];
+        const bool rotated = rope_head < p.nh + p.nkv;
+        int d0, d1;
+        if (rotated) {
+          d0 = rope_sub * 8 + j;
+          d1 = d0 + (p.hd >> 1);
+          float sn, cs;
+          sincosf(((float)pos / p.factor) * p.inv_freq[d0], &sn, &cs);
+          const float a = v0 * cs - v1 * sn, b = v0 * sn + v1 * cs;
+          v0 = a;
+          v1 = b;
+        } else {
+          d0 = rope_sub * 16 + j;
+          d1 = d0 + 8;
+        }
+        __nv_bfloat16* dst = nullptr;
+        if (rope_head < p.nh) {
+          dst = p.q_out + ((size_t)tok * p.nh + rope_head) * p.hd;
+        } else if (p.k_pool) {
+          const int page = p.block_table[(size_t)p.token_slot[tok] * p.max_pages + pos / p.page_size];
+          if (page < 0 || page >= p.num_pages) {
+            atomicExch(p.status, 2);
+          } else {
+            const bool is_k = rope_head < p.nh + p.nkv;
+            const int kvh = rope_head - p.nh - (is_k ? 0 : p.nkv);
+            dst = (is_k ? p.k_pool : p.v_pool) + (((size_t)page * p.nkv + kvh) * p.page_size + pos % p.page_size) * p.hd;
+          }
+        }
+        if (dst) {
+          dst[d0] = __float2bfloat16_rn(v0);
+          dst[d1] = __float2bfloat16_rn(v1);
+        }
+      }
+    }
+    return;
+  }
   // consecutive threads take consecutive features of one token: whole segments of the output row
   for (int e = threadIdx.x; e < SK_ROWS * 8 * NT; e += blockDim.x) {
     const int r = e % SK_ROWS, tok = e / SK_ROWS;
@@ -180,29 +257,11 @@ __global__ void __launch_bounds__(SK_MAX_WARPS * 32) gemm_skinny_kernel(const Sk
 
 using namespace glint;
 
-// Up to 16 tokens, K a multiple of 64, 16-byte aligned operands.
-GLINT_API int glint_gemm_skinny_supported(int M, int N, int K) {
-  return (M >= 1 && M <= 16 && N >= 1 && K >= SK_STEP && K % SK_STEP == 0) ? 1 : 0;
-}
-
-// x [M, K], w [w_rows, K] bfloat16; out [M, N] float32 or bfloat16.  gated: feature f is
-// act(x . w[f]) * (x . w[dual_offset + f]), out is [M, N] with N the gated width.
-GLINT_API int glint_gemm_skinny(const void* x, const void* w, void* out, int out_bf16, int M, int N, int K, float cap,
-                                int gated, int dual_offset, int activation, cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return GLINT_OK;
-  if (!glint_gemm_skinny_supported(M, N, K)) return GLINT_ERR_UNSUPPORTED_SIZE;
-  if (((uintptr_t)x | (uintptr_t)w) & 15) return GLINT_ERR_UNSUPPORTED_SIZE;
-  if (gated && (activation < 0 || activation > 1)) return GLINT_ERR_BAD_ARG;
-  SkinnyParams p;
-  p.w = (const __nv_bfloat16*)w; p.x = (const __nv_bfloat16*)x; p.out = out; p.out_bf16 = out_bf16;
-  p.M = M; p.N = N; p.K = K; p.cap = cap; p.dual_offset = dual_offset; p.activation = activation;
-  // Every pass of a warp over its steps costs one memory latency.  When the blocks fill the SMs
-  // at most once, a block has 12 or 16 warps, whichever makes the passes fewest and leaves the
-  // fewest step slots empty: more bytes in flight per SM.  With more blocks than that, small
-  // blocks (8 warps) pack the SMs better.
-  const int U = M <= 8 ? (gated ? 2 : 4) : (gated ? 1 : 2);
-  const int n_steps = K / SK_STEP;
-  const int n_blocks = (N + SK_ROWS - 1) / SK_ROWS;
+// Every pass of a warp over its steps costs one memory latency.  When the blocks fill the SMs at
+// most once, a block has 12 or 16 warps, whichever makes the passes fewest and leaves the fewest
+// step slots empty: more bytes in flight per SM.  With more blocks than that, small blocks (8
+// warps) pack the SMs better.  GLINT_SKINNY_WARPS in the environment overrides the choice.
+static int skinny_warps(int U, int n_steps, int n_blocks) {
   int device = 0, sms = 148;
   if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   int warps = 8;
@@ -221,14 +280,64 @@ GLINT_API int glint_gemm_skinny(const void* x, const void* w, void* out, int out
     forced = e ? atoi(e) : 0;
   }
   if (forced >= 1 && forced <= SK_MAX_WARPS) warps = forced;
+  return warps;
+}
+
+
+// Up to 16 tokens, K a multiple of 64, 16-byte aligned operands.
+GLINT_API int glint_gemm_skinny_supported(int M, int N, int K) {
+  return (M >= 1 && M <= 16 && N >= 1 && K >= SK_STEP && K % SK_STEP == 0) ? 1 : 0;
+}
+
+// x [M, K], w [w_rows, K] bfloat16; out [M, N] float32 or bfloat16.  gated: feature f is
+// act(x . w[f]) * (x . w[dual_offset + f]), out is [M, N] with N the gated width.
+GLINT_API int glint_gemm_skinny(const void* x, const void* w, void* out, int out_bf16, int M, int N, int K, float cap,
+                                int gated, int dual_offset, int activation, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return GLINT_OK;
+  if (!glint_gemm_skinny_supported(M, N, K)) return GLINT_ERR_UNSUPPORTED_SIZE;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return GLINT_ERR_UNSUPPORTED_SIZE;
+  if (gated && (activation < 0 || activation > 1)) return GLINT_ERR_BAD_ARG;
+  SkinnyParams p;
+  p.w = (const __nv_bfloat16*)w; p.x = (const __nv_bfloat16*)x; p.out = out; p.out_bf16 = out_bf16;
+  p.M = M; p.N = N; p.K = K; p.cap = cap; p.dual_offset = dual_offset; p.activation = activation;
+  const int warps = skinny_warps(M <= 8 ? (gated ? 2 : 4) : (gated ? 1 : 2), K / SK_STEP, (N + SK_ROWS - 1) / SK_ROWS);
   const dim3 grid((N + SK_ROWS - 1) / SK_ROWS), block(warps * 32);
   cudaError_t e;
   if (M <= 8) {
-    if (gated) e = launch_kernel(gemm_skinny_kernel<1, true, 2>, grid, block, 0, stream, p);
-    else e = launch_kernel(gemm_skinny_kernel<1, false, 4>, grid, block, 0, stream, p);
+    if (gated) e = launch_kernel(gemm_skinny_kernel<1, SK_GATED, 2>, grid, block, 0, stream, p);
+    else e = launch_kernel(gemm_skinny_kernel<1, SK_PLAIN, 4>, grid, block, 0, stream, p);
   } else {
-    if (gated) e = launch_kernel(gemm_skinny_kernel<2, true, 1>, grid, block, 0, stream, p);
-    else e = launch_kernel(gemm_skinny_kernel<2, false, 2>, grid, block, 0, stream, p);
+    if (gated) e = launch_kernel(gemm_skinny_kernel<2, SK_GATED, 1>, grid, block, 0, stream, p);
+    else e = launch_kernel(gemm_skinny_kernel<2, SK_PLAIN, 2>, grid, block, 0, stream, p);
   }
   return (int)e;
+}
+
+// The q, k, v product of up to 8 tokens with the rotary encoding and the cache write in its
+// epilogue: x [M, K]; w [(nh + 2 nkv) * hd, K]; q_out [M, nh * hd]; pools [pages][nkv][page_size][hd]
+// (null: q only).  The whole head is rotated (pairs (j, j + hd / 2)); hd a multiple of 16.
+GLINT_API int glint_gemm_skinny_rope_supported(int M, int K, int hd) {
+  return (M >= 1 && M <= 8 && K >= SK_STEP && K % SK_STEP == 0 && hd >= 16 && hd % 16 == 0) ? 1 : 0;
+}
+
+GLINT_API int glint_gemm_skinny_rope(const void* x, const void* w, int M, int K, const int* positions,
+                                     const int* token_slot, const int* block_table, int max_pages,
+                                     const float* inv_freq, float factor, void* q_out, void* k_pool, void* v_pool,
+                                     int nh, int nkv, int hd, int page_size, int num_pages, int* status,
+                                     cudaStream_t stream) {
+  if (M <= 0) return GLINT_OK;
+  if (!glint_gemm_skinny_rope_supported(M, K, hd) || nh <= 0 || nkv < 0 || page_size <= 0 || factor == 0.f)
+    return GLINT_ERR_UNSUPPORTED_SIZE;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return GLINT_ERR_UNSUPPORTED_SIZE;
+  SkinnyParams p = {};
+  p.w = (const __nv_bfloat16*)w; p.x = (const __nv_bfloat16*)x; p.M = M; p.K = K;
+  const int heads = k_pool ? nh + 2 * nkv : nh;       // without a cache to write, k and v are not computed
+  p.N = heads * hd;
+  p.positions = positions; p.token_slot = token_slot; p.block_table = block_table; p.max_pages = max_pages;
+  p.inv_freq = inv_freq; p.factor = factor; p.q_out = (__nv_bfloat16*)q_out; p.k_pool = (__nv_bfloat16*)k_pool;
+  p.v_pool = (__nv_bfloat16*)v_pool; p.nh = nh; p.nkv = nkv; p.hd = hd; p.page_size = page_size;
+  p.num_pages = num_pages; p.status = status;
+  const int n_blocks = heads * (hd / 16);
+  const int warps = skinny_warps(4, K / SK_STEP, n_blocks);
+  return (int)launch_kernel(gemm_skinny_kernel<1, SK_ROPE, 4>, dim3(n_blocks), dim3(warps * 32), 0, stream, p);
 }

@@ -14,6 +14,7 @@ _P, _I, _F, _L = c_void_p, c_int, c_float, c_longlong
 _SIGNATURES = {
     "glint_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _L, _F, _I, _I, _I, _P, _P, _P, _I, _P],
     "glint_gemm_skinny": [_P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "glint_gemm_skinny_rope": [_P, _P, _I, _I, _P, _P, _P, _I, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "glint_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P],
     "glint_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
     "glint_attention_tcgen05": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
@@ -86,6 +87,35 @@ def gemm(a, w, out, cap=0.0, status=None, force_splits=0, path=None):
     ops.check(lib().glint_gemm_tcgen05(ops.ptr(a), ops.ptr(w), ops.ptr(out), int(out.dtype == torch.bfloat16), M, N,
                                        K, N, cap or 0.0, 0, 0, 0, ops.ptr(ws), ops.ptr(counters), ops.ptr(st),
                                        force_splits, ops.stream()), "gemm_tcgen05")
+
+
+FUSED_ROPE = os.environ.get("GLINT_FUSED_ROPE", "1") != "0"
+
+
+def qkv_rope_supported(M, K, hd, rotary_dim):
+    """The fused q/k/v product takes up to 8 tokens, K in steps of 64 and whole-head rotation."""
+    return (FUSED_ROPE and SKINNY_MAX_TOKENS > 0 and 1 <= M <= 8 and K >= 64 and K % 64 == 0 and hd % 16 == 0 and hd >= 16
+            and rotary_dim == hd)
+
+
+def qkv_rope(a, w_qkv, positions, token_slot, block_table, inv_freq, factor, q_out, k_pool, v_pool, nh, nkv, hd,
+             page_size, num_pages, status):
+    """q, k, v = a @ w_qkv^T for up to 8 tokens with the rotary encoding and the cache write in the
+    product's epilogue: rotated q goes to ``q_out`` [M, nh * hd], rotated k and v into the pages named
+    by ``block_table`` at each token's position (``k_pool`` None: q only)."""
+    M, K = a.shape
+    ops.require(a, torch.bfloat16, "a"); ops.require(w_qkv, torch.bfloat16, "w_qkv")
+    ops.require(q_out, torch.bfloat16, "q_out"); ops.require(k_pool, torch.bfloat16, "k_pool")
+    ops.require(v_pool, torch.bfloat16, "v_pool"); ops.require(inv_freq, torch.float32, "inv_freq")
+    ops.require(positions, torch.int32, "positions"); ops.require(token_slot, torch.int32, "token_slot")
+    ops.require(block_table, torch.int32, "block_table")
+    if w_qkv.shape != ((nh + 2 * nkv) * hd, K) or tuple(q_out.shape) != (M, nh * hd) or inv_freq.numel() != hd // 2:
+        raise KernelError(f"qkv_rope shapes do not fit: a {tuple(a.shape)}, w {tuple(w_qkv.shape)}, "
+                          f"q_out {tuple(q_out.shape)}, heads {nh}/{nkv} x {hd}")
+    ops.check(lib().glint_gemm_skinny_rope(ops.ptr(a), ops.ptr(w_qkv), M, K, ops.ptr(positions), ops.ptr(token_slot),
+                                           ops.ptr(block_table), block_table.shape[1], ops.ptr(inv_freq), factor,
+                                           ops.ptr(q_out), ops.ptr(k_pool), ops.ptr(v_pool), nh, nkv, hd, page_size,
+                                           num_pages, ops.ptr(status), ops.stream()), "gemm_skinny_rope")
 
 
 def gemm_gated(a, w_gate_up, out, activation, status=None, force_splits=0, path=None):

@@ -59,9 +59,12 @@ class Attention(Part):
     def forward(self, normed, ctx, view, state=None):
         rt = self.rt
         T = normed.shape[0]
-        qkv = linear(rt, normed, self.w_qkv)
         q = torch.empty((T, self.q_size), dtype=rt.dtype, device=normed.device)
-        self.position.encode_and_store(qkv, ctx, q, view, self.num_heads, self.num_kv_heads, self.head_dim)
+        fused = getattr(self.position, "project_encode_store", None)
+        if fused is None or not fused(normed, self.w_qkv, ctx, q, view, self.num_heads, self.num_kv_heads,
+                                      self.head_dim):
+            qkv = linear(rt, normed, self.w_qkv)
+            self.position.encode_and_store(qkv, ctx, q, view, self.num_heads, self.num_kv_heads, self.head_dim)
         out = torch.empty_like(q)
         self.attend(q, ctx, view, out)
         return linear(rt, out, self.w_o)

@@ -37,4 +37,21 @@ class Rotary(Part):
                           view.v if writes else None, nh, nkv, hd, view.page_size, view.num_pages,
                           self.rt.status)
 
+    def project_encode_store(self, x, w_qkv, ctx, q_out, view, nh, nkv, hd):
+        """The q/k/v product, the rotation and the cache write as one kernel, where there is one for
+        these sizes (a few single tokens in bfloat16); returns False when the caller has to run the
+        product and ``encode_and_store`` itself."""
+        rt = self.rt
+        if not (rt.tensor_cores and w_qkv.dtype == torch.bfloat16 and x.dtype == torch.bfloat16):
+            return False
+        from .. import ops_tensor
+        if not ops_tensor.qkv_rope_supported(x.shape[0], x.shape[1], hd, self.rotary_dim):
+            return False
+        writes = view.writes
+        ops_tensor.qkv_rope(x, w_qkv, ctx.positions, ctx.token_seq, ctx.block_table(view.group), self.inv_freq,
+                            self.factor, q_out, view.k if writes else None, view.v if writes else None, nh, nkv, hd,
+                            view.page_size, view.num_pages, rt.status)
+        return True
+
+
 register_part("position", "rope", Rotary)

@@ -161,6 +161,57 @@ def test_gemm_skinny_gated_against_float32(M, I, K, act):
     assert err <= 1e-2 * max(1.0, want.abs().max().item()), err
 
 
+@pytest.mark.parametrize("M,K,nh,nkv,hd,page,writes", [(8, 2304, 8, 4, 256, 16, True), (3, 192, 5, 1, 48, 32, True),
+                                                        (1, 64, 2, 2, 16, 16, True), (7, 320, 6, 3, 80, 16, False)])
+def test_qkv_product_with_rotation_and_cache_write_in_one_kernel(M, K, nh, nkv, hd, page, writes):
+    """Against float32 torch: the product, the turn of pairs (j, j + hd/2) by pos * theta^(-2j/hd), and
+    the rows of the cache it writes; every other row of the pools stays as it was."""
+    from glint_b200 import ops_tensor
+    torch.manual_seed(M + hd)
+    x = _bf16(torch.randn(M, K, device=DEV))
+    w = _bf16(torch.randn((nh + 2 * nkv) * hd, K, device=DEV) * 0.05)
+    positions = [37 * i + 5 for i in range(M)]                      # token i of request i
+    max_pages = max(positions) // page + 1
+    n_pages = M * max_pages + 2
+    perm = torch.randperm(n_pages)[:M * max_pages].reshape(M, max_pages).to(torch.int32).to(DEV)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))).to(DEV)
+    factor = 2.0
+    k_pool = torch.full((n_pages, nkv, page, hd), 7.0, device=DEV, dtype=torch.bfloat16)
+    v_pool = torch.full((n_pages, nkv, page, hd), -3.0, device=DEV, dtype=torch.bfloat16)
+    q = torch.full((M, nh * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    ops_tensor.qkv_rope(x, w, i32(positions), i32(list(range(M))), perm, inv_freq, factor, q,
+                        k_pool if writes else None, v_pool if writes else None, nh, nkv, hd, page, n_pages, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    qkv = (x.float() @ w.float().T).cpu()
+    pos = torch.tensor(positions, dtype=torch.float32)
+    ang = (pos[:, None] / factor) * inv_freq.cpu()[None, :]          # [M, hd/2]
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+    def turn(heads):                                                 # [M, n, hd]
+        lo, hi = heads[..., :hd // 2], heads[..., hd // 2:]
+        return torch.cat([lo * cos - hi * sin, lo * sin + hi * cos], dim=-1)
+
+    want_q = turn(qkv[:, :nh * hd].reshape(M, nh, hd))
+    tol = 2e-2 * max(1.0, qkv.abs().max().item())
+    assert (q.float().cpu().reshape(M, nh, hd) - want_q).abs().max().item() <= tol
+    if writes:
+        want_k = turn(qkv[:, nh * hd:(nh + nkv) * hd].reshape(M, nkv, hd))
+        want_v = qkv[:, (nh + nkv) * hd:].reshape(M, nkv, hd)
+        kc, vc = k_pool.float().cpu(), v_pool.float().cpu()
+        touched = torch.zeros(n_pages, page, dtype=torch.bool)
+        for t, p_ in enumerate(positions):
+            pg = int(perm[t, p_ // page])
+            assert (kc[pg, :, p_ % page] - want_k[t]).abs().max().item() <= tol
+            assert (vc[pg, :, p_ % page] - want_v[t]).abs().max().item() <= tol
+            touched[pg, p_ % page] = True
+        assert (kc.permute(0, 2, 1, 3)[~touched] == 7.0).all() and (vc.permute(0, 2, 1, 3)[~touched] == -3.0).all()
+    else:
+        assert (k_pool == 7.0).all() and (v_pool == -3.0).all()
+
+
 # ---- attention over a paged cache -----------------------------------------------------------------
 
 def _paged_case(seq_lens_before, seq_lens_new, nkv, hd, page_size, dtype, seed, hot=None, v_poison=float("nan")):
