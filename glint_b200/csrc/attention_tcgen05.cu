@@ -37,6 +37,7 @@ struct FaParams {
   int nh, nkv, hd, page_size, num_pages;
   float multiplier, cap;
   int window;
+  int whole;       // keys in boxes of 8 rows x head_dim, values in boxes of a page x head_dim (see the producer)
   int* status;
 };
 
@@ -107,64 +108,82 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
   if (warp == 0) {
     // ---- producer ---------------------------------------------------------------------------------
-    // One elected thread issues every copy: inside elect.sync the compiler keeps addresses and
-    // coordinates in uniform registers, which the TMA instructions take directly (a copy issued
-    // from a region that is merely "lane 0" costs about 100 cycles, here about 40).
+    // The whole warp walks the tiles: lane pi looks up the page pi of the next tile (its table entry
+    // is requested one tile ahead and looked at only when it is used), the page numbers go round by
+    // shuffle, and one elected thread issues the copies.  Inside elect.sync the compiler keeps
+    // addresses and coordinates in uniform registers, which the TMA instructions take directly; a
+    // table load inside that region would be waited for on the spot.
     if (tc::elect_one()) {
       tc::mbar_expect_tx(&sh->q_full, (uint32_t)nsub * tok_per_tile * G * 128);
       for (int sub = 0; sub < nsub; ++sub)
         tc::tma_load_4d(sq + (size_t)sub * FA_Q_SUB, &map_q, &sh->q_full, sub * 64, 0, kvh, t_begin + tok0);
-      const int ppt = FA_N / p.page_size;                        // pages per tile: 4, 2 or 1
-      const int* table = p.block_table + (size_t)seq * p.max_pages;
-      const int page_lo = kv_first / p.page_size, page_hi = pos_last / p.page_size;
-      // The table entries of the next tile are loaded while this tile's copies are issued, and are
-      // looked at only when they are used: a check right behind each load would make the thread
-      // sit out one memory latency per page.  Pages outside [page_lo, page_hi] are masked by the
-      // softmax; they are filled from page 0.
-      auto fetch = [&](int j, int pi) -> int {
-        const int page_idx = (kv_begin + j * FA_N) / p.page_size + pi;
-        return table[min(max(page_idx, page_lo), page_hi)];
-      };
-      auto resolve = [&](int j, int pi, int page) -> int {
-        const int page_idx = (kv_begin + j * FA_N) / p.page_size + pi;
-        if (page_idx < page_lo || page_idx > page_hi) return 0;
-        if (page < 0 || page >= p.num_pages) {
-          atomicExch(p.status, 3);
-          return 0;
-        }
-        return page;
-      };
-      int pages[4], next[4];
+    }
+    __syncwarp();
+    const int ppt = FA_N / p.page_size;                        // pages per tile: 4, 2 or 1
+    const int* table = p.block_table + (size_t)seq * p.max_pages;
+    const int page_lo = kv_first / p.page_size, page_hi = pos_last / p.page_size;
+    const int first_page = kv_begin / p.page_size;
+    // pages outside [page_lo, page_hi] are masked by the softmax; they are filled from page 0
+    auto fetch = [&](int j) -> int {
+      const int page_idx = first_page + j * ppt + lane;
+      return lane < ppt ? table[min(max(page_idx, page_lo), page_hi)] : 0;
+    };
+    int next = fetch(0);
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int b = j & 1;
+      int mine = next;
+      const int page_idx = first_page + j * ppt + lane;
+      if (lane >= ppt || page_idx < page_lo || page_idx > page_hi) {
+        mine = 0;
+      } else if (mine < 0 || mine >= p.num_pages) {
+        atomicExch(p.status, 3);
+        mine = 0;
+      }
+      if (j + 1 < n_tiles) next = fetch(j + 1);
+      int pages[4];
 #pragma unroll
-      for (int pi = 0; pi < 4; ++pi) next[pi] = pi < ppt ? fetch(0, pi) : 0;
-      bool ok = true;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int b = j & 1;
-#pragma unroll
-        for (int pi = 0; pi < 4; ++pi) pages[pi] = pi < ppt ? resolve(j, pi, next[pi]) : 0;
-        if (j + 1 < n_tiles) {
-#pragma unroll
-          for (int pi = 0; pi < 4; ++pi) next[pi] = pi < ppt ? fetch(j + 1, pi) : 0;
-        }
-        for (int which = 0; which < 2 && ok; ++which) {          // keys first: they are needed first
-          uint64_t* full = which ? &sh->v_full[b] : &sh->k_full[b];
-          if (j >= 2) ok = tc::mbar_wait(which ? &sh->v_empty[b] : &sh->k_empty[b], ((j >> 1) - 1) & 1, abort_flag);
-          if (!ok) break;
+      for (int pi = 0; pi < 4; ++pi) pages[pi] = __shfl_sync(0xffffffffu, mine, pi);
+      for (int which = 0; which < 2 && ok; ++which) {          // keys first: they are needed first
+        uint64_t* full = which ? &sh->v_full[b] : &sh->k_full[b];
+        if (j >= 2) ok = tc::mbar_wait(which ? &sh->v_empty[b] : &sh->k_empty[b], ((j >> 1) - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (tc::elect_one()) {
           tc::mbar_expect_tx(full, (uint32_t)nsub * FA_KV_SUB);
           const CUtensorMap* map = which ? &map_v : &map_k;
           uint8_t* ring = (which ? sv : sk) + (size_t)b * nsub * FA_KV_SUB;
+          if (p.whole && which) {
+            // values: one box per page, [slice][row of the page][64 columns]
 #pragma unroll
-          for (int pi = 0; pi < 4; ++pi) {
-            if (pi < ppt) {
-              const int row = (pages[pi] * p.nkv + kvh) * p.page_size;
-              uint8_t* dst = ring + (size_t)pi * p.page_size * 128;
-              for (int sub = 0; sub < nsub; ++sub) tc::tma_load_2d(dst + (size_t)sub * FA_KV_SUB, map, full, sub * 64, row);
+            for (int pi = 0; pi < 4; ++pi)
+              if (pi < ppt)
+                tc::tma_load_3d(ring + (size_t)pi * nsub * p.page_size * 128, map, full, 0,
+                                (pages[pi] * p.nkv + kvh) * p.page_size, 0);
+          } else if (p.whole) {
+            // keys: one box per 8 rows, [slice][8 rows][64 columns]; the groups of 8 rows of the tile are
+            // then nsub KB apart, which the operand descriptor takes as its stride
+#pragma unroll
+            for (int a = 0; a < FA_N / 8; ++a) {
+              const int key = a * 8;
+              const int pg = p.page_size == 16 ? pages[a >> 1] : p.page_size == 32 ? pages[a >> 2] : pages[0];
+              tc::tma_load_3d(ring + (size_t)a * nsub * 1024, map, full, 0,
+                              (pg * p.nkv + kvh) * p.page_size + (key & (p.page_size - 1)), 0);
+            }
+          } else {
+#pragma unroll
+            for (int pi = 0; pi < 4; ++pi) {
+              if (pi < ppt) {
+                const int row = (pages[pi] * p.nkv + kvh) * p.page_size;
+                uint8_t* dst = ring + (size_t)pi * p.page_size * 128;
+                for (int sub = 0; sub < nsub; ++sub) tc::tma_load_2d(dst + (size_t)sub * FA_KV_SUB, map, full, sub * 64, row);
+              }
             }
           }
         }
+        __syncwarp();
       }
     }
-    __syncwarp();
   } else if (warp == 1) {
     // ---- MMA issuer -------------------------------------------------------------------------------
     // elect.sync rather than "lane 0": descriptors then live in uniform registers and one MMA costs
@@ -180,11 +199,23 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       // plus a small offset (the address field counts 16 bytes).
       const uint64_t qd0 = tc::smem_desc_k_sw128(q_addr);
       const uint64_t pd0 = tc::smem_desc_k_sw128(p_addr);
+      // Two layouts of a key or value tile (see the producer).  Separate boxes per 64-column slice:
+      // [slice][64 keys][128 B].  Whole boxes: keys [group of 8][slice][8 rows][128 B], values
+      // [page][slice][rows of the page][128 B].
+      const uint32_t k_slice = p.whole ? 1024u : (uint32_t)FA_KV_SUB;          // bytes between slices of keys
+      const uint32_t k_sbo = p.whole ? (uint32_t)nsub * 1024u : 1024u;         // bytes between groups of 8 keys
+      const uint32_t v_lbo = p.whole ? (uint32_t)p.page_size * 128u : (uint32_t)FA_KV_SUB;
+      const uint32_t v_page = (uint32_t)nsub * p.page_size * 128u;             // whole boxes: bytes of a page
       uint64_t kd0[2], vd0[2];
       for (int b = 0; b < 2; ++b) {
-        kd0[b] = tc::smem_desc_k_sw128(k_addr + b * nsub * FA_KV_SUB);
-        vd0[b] = tc::smem_desc_mn_sw128(v_addr + b * nsub * FA_KV_SUB, FA_KV_SUB, 1024);
+        kd0[b] = tc::smem_desc_k_sw128_sbo(k_addr + b * nsub * FA_KV_SUB, k_sbo);
+        vd0[b] = tc::smem_desc_mn_sw128(v_addr + b * nsub * FA_KV_SUB, v_lbo, 1024);
       }
+      uint32_t v_step[FA_N / 16];                                              // start of keys 16 kk, in 16 bytes
+#pragma unroll
+      for (int kk = 0; kk < FA_N / 16; ++kk)
+        v_step[kk] = p.whole ? (((kk * 16) / p.page_size) * v_page + ((kk * 16) % p.page_size) * 128u) >> 4
+                             : (uint32_t)(kk * 2048) >> 4;
       auto issue_s = [&](int j) -> bool {
         const int b = j & 1;
         if (!tc::mbar_wait(&sh->k_full[b], (j >> 1) & 1, abort_flag)) return false;
@@ -195,7 +226,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         for (int ks = 0; ks < 16; ++ks) {
           if (ks < hd16) {
             const uint32_t oq = ((ks >> 2) * FA_Q_SUB + (ks & 3) * 32) >> 4;     // compile-time constants
-            const uint32_t ok_ = ((ks >> 2) * FA_KV_SUB + (ks & 3) * 32) >> 4;
+            const uint32_t ok_ = ((ks >> 2) * k_slice + (ks & 3) * 32) >> 4;
             tc::mma_bf16_ss(d, qd0 + oq, kd + ok_, idesc_s, ks > 0 ? 1u : 0u);
           }
         }
@@ -215,7 +246,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const uint64_t vd = b ? vd0[1] : vd0[0];
 #pragma unroll
         for (int kk = 0; kk < FA_N / 16; ++kk)
-          tc::mma_bf16_ss(tmem_o, pd0 + 2 * kk, vd + (2048 >> 4) * kk, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          tc::mma_bf16_ss(tmem_o, pd0 + 2 * kk, vd + v_step[kk], idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         tc::mma_commit(&sh->v_empty[b]);
         tc::mma_commit(&sh->p_free);             // P and this row of O may be touched again
         if (j + 2 < n_tiles) ok = issue_s(j + 2);
@@ -433,7 +464,20 @@ GLINT_API int glint_attention_tcgen05(const void* q, const void* k_pool, const v
     const int rc = fa_map(&map_q, q, 4, dims, strides, box);
     if (rc != GLINT_OK) return rc;
   }
-  {
+  // With head_dim a multiple of 64 the 64-column slices are a third dimension of the pools and one
+  // box brings all slices of its rows: 12 copies per tile of 64 keys instead of 32 with pages of 16
+  // (the copy unit spends about 65 cycles on a box whatever its size).
+  const int whole = hd % 64 == 0 ? 1 : 0;
+  if (whole) {
+    cuuint64_t dims[3] = {64, (cuuint64_t)num_pages * nkv * page_size, (cuuint64_t)(hd / 64)};
+    cuuint64_t strides[2] = {(cuuint64_t)hd * 2, 128};
+    cuuint32_t box_k[3] = {64, 8, (cuuint32_t)(hd / 64)};
+    cuuint32_t box_v[3] = {64, (cuuint32_t)page_size, (cuuint32_t)(hd / 64)};
+    int rc = fa_map(&map_k, k_pool, 3, dims, strides, box_k);
+    if (rc != GLINT_OK) return rc;
+    rc = fa_map(&map_v, v_pool, 3, dims, strides, box_v);
+    if (rc != GLINT_OK) return rc;
+  } else {
     cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)num_pages * nkv * page_size};
     cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
     cuuint32_t box[2] = {64, (cuuint32_t)page_size};
@@ -445,7 +489,7 @@ GLINT_API int glint_attention_tcgen05(const void* q, const void* k_pool, const v
   FaParams p;
   p.cu_seqlens = cu_seqlens; p.seq_start = seq_start; p.block_table = block_table; p.max_pages = max_pages;
   p.out = (__nv_bfloat16*)out; p.nh = nh; p.nkv = nkv; p.hd = hd; p.page_size = page_size; p.num_pages = num_pages;
-  p.multiplier = multiplier; p.cap = cap; p.window = window; p.status = status;
+  p.multiplier = multiplier; p.cap = cap; p.window = window; p.whole = whole; p.status = status;
   const int nsub = (hd + 63) / 64;
   const int smem = nsub * FA_Q_SUB + 4 * nsub * FA_KV_SUB + FA_P_BYTES + (int)sizeof(FaShared) + 1024 + 64;
   if (smem > 227 * 1024) return GLINT_ERR_UNSUPPORTED_SIZE;

@@ -132,6 +132,17 @@ __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// The same with the groups of 8 rows `sbo_bytes` apart (a tile assembled from several copies).
+__device__ __forceinline__ uint64_t smem_desc_k_sw128_sbo(uint32_t smem_addr, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
 // Instruction descriptor for kind::f16 with bf16 inputs, f32 accumulation, both K-major.
 __host__ __device__ constexpr uint32_t idesc_bf16_f32(uint32_t M, uint32_t N) {
   return (1u << 4)            // D format f32
