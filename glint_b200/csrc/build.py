@@ -25,6 +25,8 @@ CSRC = os.path.dirname(os.path.abspath(__file__))
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+# extra flags for a debugging build (for instance -DGLINT_WAIT_LIMIT_LOG2=16); they are part of the hash
+NVCC_FLAGS += os.environ.get("GLINT_NVCC_EXTRA", "").split()
 
 LIBRARIES = {
     "core": ["elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu", "sample_noalloc.cu"],

@@ -13,7 +13,10 @@ namespace tc {
 
 // A wait gives up after this many polls (each poll may suspend for a while in hardware), sets
 // the kernel's error word and lets the block run to its teardown instead of hanging the GPU.
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+#ifndef GLINT_WAIT_LIMIT_LOG2
+#define GLINT_WAIT_LIMIT_LOG2 22
+#endif
+constexpr uint32_t WAIT_LIMIT = 1u << GLINT_WAIT_LIMIT_LOG2;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
