@@ -89,6 +89,62 @@ argmax_kernel(const float* __restrict__ logits, long long row_stride, int V, int
   if (threadIdx.x == 0) out[blockIdx.x] = best.i < 0 ? 0 : best.i;
 }
 
+__device__ __forceinline__ unsigned ordered_key(float v);
+
+// The same over a wide row with several blocks: block (row, chunk) finds the best of its chunk,
+// the chunks meet in one 64-bit atomic maximum per row (value key above, index below, so that among
+// equal values the later index wins as in `better`), and the block that arrives last at the row's
+// counter writes the index and leaves key and counter zero for the next launch.  `keys` and
+// `counters` hold one zeroed entry per row.
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_wide_kernel(const float* __restrict__ logits, long long row_stride, int V, int chunk,
+                   unsigned long long* __restrict__ keys, int* __restrict__ counters, int* __restrict__ out) {
+  __shared__ ArgBest scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * row_stride;
+  const int begin = blockIdx.y * chunk, end = min(V, begin + chunk);     // chunk is a multiple of 4
+  ArgBest best{-INFINITY, -1};
+  if (((uintptr_t)(row + begin) & 15) == 0) {
+    const int n4 = (end - begin) >> 2;
+    const float4* row4 = reinterpret_cast<const float4*>(row + begin);
+    for (int i0 = threadIdx.x; i0 < n4; i0 += 4 * blockDim.x) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        v[u] = i < n4 ? row4[i] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < n4) {
+          best = better(best, ArgBest{v[u].x, begin + 4 * i});
+          best = better(best, ArgBest{v[u].y, begin + 4 * i + 1});
+          best = better(best, ArgBest{v[u].z, begin + 4 * i + 2});
+          best = better(best, ArgBest{v[u].w, begin + 4 * i + 3});
+        }
+      }
+    }
+    for (int i = begin + (n4 << 2) + threadIdx.x; i < end; i += blockDim.x) best = better(best, ArgBest{row[i], i});
+  } else {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) best = better(best, ArgBest{row[i], i});
+  }
+  best = block_argmax(best, scratch);
+  if (threadIdx.x == 0) {
+    if (best.i >= 0)   // -0 and +0 are equal to `better`: give them one key
+      atomicMax(&keys[r], ((unsigned long long)ordered_key(best.v + 0.0f) << 32) | (unsigned)best.i);
+    __threadfence();
+    if (atomicAdd(&counters[r], 1) == (int)gridDim.y - 1) {
+      __threadfence();
+      const unsigned long long k = atomicExch(&keys[r], 0ull);
+      out[r] = k ? (int)(unsigned)(k & 0xffffffffull) : 0;
+      counters[r] = 0;
+    }
+  }
+}
+
 // work[r, :] = logits[r, :]; then every (token, count) pair of row r divides a positive logit by
 // the penalty `count` times, or multiplies a non-positive one (src/sampling/sampler.rs:262-273
 // loops over every past occurrence).
@@ -286,6 +342,22 @@ GLINT_API int glint_argmax(const float* logits, long long row_stride, int rows, 
   if (V <= 0) return GLINT_ERR_BAD_ARG;
   const cudaError_t e = launch_kernel(argmax_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, row_stride,
                                       V, out);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
+// Rows of 64 K entries and more are shared by several blocks; `keys` (64-bit) and `counters` hold one
+// zeroed entry per row and are left zeroed.  Without them, or for narrow rows, one block per row.
+GLINT_API int glint_argmax_wide(const float* logits, long long row_stride, int rows, int V, int* out,
+                                unsigned long long* keys, int* counters, cudaStream_t stream) {
+  if (rows <= 0) return GLINT_OK;
+  if (V <= 0) return GLINT_ERR_BAD_ARG;
+  int chunks = V / 16384;
+  if (chunks > 32) chunks = 32;
+  if (!keys || !counters || chunks < 2 || rows > 65535) return glint_argmax(logits, row_stride, rows, V, out, stream);
+  const int chunk = (((V + chunks - 1) / chunks) + 3) & ~3;
+  chunks = (V + chunk - 1) / chunk;
+  const cudaError_t e = launch_kernel(argmax_wide_kernel, dim3(rows, chunks), dim3(SAMPLE_THREADS), 0, stream, logits,
+                                      row_stride, V, chunk, keys, counters, out);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 

@@ -54,6 +54,7 @@ _CORE_SIGNATURES = {
     "glint_gemm_plain": [_P, _P, _I, _P, _I, _I, _I, _F, _P],
     "glint_attention_plain": [_P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
     "glint_argmax": [_P, _L, _I, _I, _P, _P],
+    "glint_argmax_wide": [_P, _L, _I, _I, _P, _P, _P, _P],
     "glint_apply_penalty": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
     "glint_sample": [_P, _L, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P],
 }
@@ -190,11 +191,25 @@ def attention_plain(q, k_pool, v_pool, positions, token_slot, block_table, out, 
                                        ptr(status), stream()), "attention_plain")
 
 
+_argmax_scratch = {}
+
+
 def argmax(logits, out):
-    """out[r] = index of the largest logit of row r (the last one among equals)."""
+    """out[r] = index of the largest logit of row r (the last one among equals).  Wide rows are
+    shared by several blocks that meet in a per-row atomic (scratch kept per device, left zeroed)."""
     rows, V = logits.shape
     require(logits, torch.float32, "logits"); require(out, torch.int32, "out")
-    check(core().glint_argmax(ptr(logits), logits.stride(0), rows, V, ptr(out), stream()), "argmax")
+    keys = counters = None
+    if V >= 32768:
+        entry = _argmax_scratch.get(str(logits.device))
+        if entry is None or entry[0].numel() < rows:
+            n = max(rows, 1024)
+            entry = (torch.zeros(n, dtype=torch.int64, device=logits.device),
+                     torch.zeros(n, dtype=torch.int32, device=logits.device))
+            _argmax_scratch[str(logits.device)] = entry
+        keys, counters = entry
+    check(core().glint_argmax_wide(ptr(logits), logits.stride(0), rows, V, ptr(out), ptr(keys), ptr(counters),
+                                   stream()), "argmax")
 
 
 def apply_penalty(logits, work, offsets, tokens, counts, penalty):

@@ -427,6 +427,27 @@ def test_argmax_takes_the_last_maximum(V):
     assert out.tolist() == [int(torch.argmax(logits[0])), V - 3, 0]
 
 
+@pytest.mark.parametrize("V", [32768, 256000, 100003])
+def test_argmax_of_wide_rows_by_several_blocks(V):
+    """Rows shared by several blocks: equal maxima in different chunks, -0 against +0, a row of
+    -inf, twice in a row (the per-row scratch is left zeroed); with an odd width the rows start at
+    every alignment."""
+    from glint_b200 import ops
+    torch.manual_seed(V)
+    logits = torch.randn(5, V, device=DEV)
+    logits[1, 7] = logits[1, V - 2] = logits[1, V // 2] = 77.0
+    logits[2].fill_(-1.0)
+    logits[2, 3] = 0.0
+    logits[2, V - 5] = -0.0                                # equal to +0: the later index wins
+    logits[3].fill_(float("-inf"))
+    logits[4, 0] = 1e30
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        out.fill_(-7)
+        ops.argmax(logits, out)
+        assert out.tolist() == [int(torch.argmax(logits[0])), V - 2, V - 5, V - 1, 0]
+
+
 def test_sampling_kernel_against_the_plain_sampler():
     from glint_b200 import ops
     from tests.plain import sampler as ps
