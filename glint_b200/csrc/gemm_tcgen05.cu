@@ -32,6 +32,7 @@ constexpr int A_STAGE_BYTES = GEMM_BM * GEMM_BK * 2;
 struct GemmParams {
   int M, N, K;          // tokens, output features, reduction length
   int BN;               // tokens per tile
+  int m_tiles;          // token tiles (the fast index of blockIdx.x)
   int stages;
   int splits, kb_per_split, total_kb;
   int dual_offset;      // row offset of the second weight tile (dual kernels)
@@ -107,8 +108,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * GEMM_BM;
-  const int m0 = blockIdx.y * p.BN;
+  // blockIdx.x walks the token tiles of one feature tile first: the blocks that run at the same
+  // time then share their weight tiles, which come from HBM once and from L2 for the other token
+  // tiles (feature tiles first re-read the weights once per token tile: 346 MB instead of 94 MB for
+  // the gate/up product of a 2048-token portion).
+  const int m_tile = (int)blockIdx.x % p.m_tiles, n_tile = (int)blockIdx.x / p.m_tiles;
+  const int n0 = n_tile * GEMM_BM;
+  const int m0 = m_tile * p.BN;
   const int split = blockIdx.z;
   const int kb_begin = split * p.kb_per_split;
   const int kb_end = min(p.total_kb, kb_begin + p.kb_per_split);
@@ -225,7 +231,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const bool ok = sh->epilogue_ok != 0;   // one thread decides, so all 128 take the same branch
     tc::fence_after_thread_sync();
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+    const int tile_id = (int)blockIdx.x;
     const int halves = DUAL ? 2 : 1;
     if (ok && p.splits == 1) {
       // One row pointer per thread, advanced by a whole output row per token; the epilogue kind is
@@ -483,7 +489,8 @@ GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int ou
   rc = make_map(&map_x, x, M, K, bn);
   if (rc != GLINT_OK) return rc;
   const int smem_bytes = stages * stage_bytes + (int)sizeof(GemmShared) + 1024;
-  dim3 grid(n_tiles, m_tiles, splits);
+  p.m_tiles = m_tiles;
+  dim3 grid(n_tiles * m_tiles, 1, splits);
   cudaError_t e;
   if (dual) {
     e = cudaFuncSetAttribute(gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
