@@ -432,7 +432,9 @@ GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int ou
   if (((uintptr_t)x | (uintptr_t)w) & 15) return GLINT_ERR_UNSUPPORTED_SIZE;
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
-  const int m_tiles_256 = (M + 255) / 256;
+  int bn_max = 256;
+  if (const char* ov = getenv("GLINT_GEMM_BN")) { const int v = atoi(ov); if (v >= 16 && v <= 256 && v % 16 == 0) bn_max = v; }
+  const int m_tiles_256 = (M + bn_max - 1) / bn_max;
   int bn = ((M + m_tiles_256 - 1) / m_tiles_256 + 15) / 16 * 16;
   if (dual && bn > 256) bn = 256;
   p.BN = bn;
