@@ -1,5 +1,6 @@
-"""Each part alone against the plain implementation's function of the same name, and a toy mixer
-with state of its own that is registered, built and stepped without touching the package."""
+"""Each part alone against the plain implementation's function of the same name, and toy parts
+defined here (a mixer with state of its own, a feed-forward with routing, another position
+encoding) that are registered, built and stepped without touching the package."""
 import math
 import os
 
@@ -206,5 +207,154 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     assert (torch.cat(got_a) - whole_a).abs().max().item() < 1e-4
     assert (torch.cat(got_b) - whole_b).abs().max().item() < 1e-4
     assert whole_a.abs().max().item() > 1e-3
+    engine.close(sa); engine.close(sb)
+    model.rt.check_status()
+
+
+# ---- a toy feed-forward with routing and a toy position encoding, defined here -----------------------------
+
+
+def _register_routed_toy():
+    from glint_b200.config import BlockSpec, LayerCall, ModelSpec, PartSpec, register_architecture
+    from glint_b200.parts import Part, TensorNeed, register_part
+
+    class RoutedFeedForward(Part):
+        """Top-1 of E small experts: router logits in 32-bit, y = W2[e] silu(W1[e] x) * gate weight."""
+
+        def __init__(self, rt, params, tensors):
+            super().__init__(rt, params, tensors)
+            self.H, self.I, self.E = int(params["hidden_size"]), int(params["intermediate_size"]), int(params["experts"])
+
+        def needs(self):
+            n = self.names
+            need = [TensorNeed(n["router"], (self.E, self.H))]
+            for e in range(self.E):
+                need += [TensorNeed(f"{n['experts']}.{e}.w1", (self.I, self.H)),
+                         TensorNeed(f"{n['experts']}.{e}.w2", (self.H, self.I))]
+            return need
+
+        def bind(self, tensors):
+            n = self.names
+            self.router = tensors[n["router"]].float()
+            self.w1 = torch.stack([tensors[f"{n['experts']}.{e}.w1"].float() for e in range(self.E)])
+            self.w2 = torch.stack([tensors[f"{n['experts']}.{e}.w2"].float() for e in range(self.E)])
+
+        def forward(self, normed, ctx):
+            x = normed.float()
+            logits = x @ self.router.T                                  # routing is decided in 32-bit
+            weight, expert = torch.softmax(logits, dim=-1).max(dim=-1)
+            h = torch.nn.functional.silu(torch.einsum("tih,th->ti", self.w1[expert], x))
+            return torch.einsum("thi,ti->th", self.w2[expert], h) * weight[:, None]
+
+    class SinusoidOffset(Part):
+        """q and k get a sinusoid of the absolute position added (no rotation); v is stored as it is."""
+
+        def __init__(self, rt, params, tensors):
+            super().__init__(rt, params, tensors)
+            hd = int(params["head_dim"])
+            self.freq = (1.0 / (50.0 ** (torch.arange(hd, dtype=torch.float32) / hd))).to(rt.device)
+            self.amplitude = float(params["amplitude"])
+
+        def encode_and_store(self, qkv, ctx, q_out, view, nh, nkv, hd):
+            T = qkv.shape[0]
+            pos = ctx.positions[:T].long()
+            add = self.amplitude * torch.sin(pos[:, None].float() * self.freq[None, :])       # [T, hd]
+            q = qkv[:, :nh * hd].view(T, nh, hd) + add[:, None, :]
+            q_out.copy_(q.reshape(T, nh * hd).to(q_out.dtype))
+            if view.writes:
+                k = qkv[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd) + add[:, None, :]
+                v = qkv[:, (nh + nkv) * hd:].view(T, nkv, hd)
+                table = ctx.block_table(view.group).long()
+                pages = table[ctx.token_seq[:T].long(), pos // view.page_size]
+                view.k[pages, :, pos % view.page_size] = k.to(view.k.dtype)
+                view.v[pages, :, pos % view.page_size] = v.to(view.v.dtype)
+
+    class RoutedToyConfig:
+        def __init__(self, obj):
+            self.obj = obj
+
+        @classmethod
+        def from_dict(cls, obj):
+            return cls(obj)
+
+        def to_dict(self):
+            return dict(self.obj)
+
+        def model_spec(self):
+            o = self.obj
+            H, V, hd = o["hidden_size"], o["vocab_size"], 16
+            norm = lambda name: PartSpec("rmsnorm", {"size": H, "eps": 1e-5, "unit_offset": False}, {"weight": name})
+            attn = lambda i, position, window: PartSpec(
+                "attention", {"hidden_size": H, "num_heads": 3, "num_kv_heads": 1, "head_dim": hd,
+                              "score_multiplier": 0.25, "softcap": None, "window": window, "position": position},
+                {"q": f"l{i}.q", "k": f"l{i}.k", "v": f"l{i}.v", "o": f"l{i}.o"})
+            routed = PartSpec("routed_toy", {"hidden_size": H, "intermediate_size": 24, "experts": o["experts"]},
+                              {"router": "l0.router", "experts": "l0.experts"})
+            dense = PartSpec("gated", {"hidden_size": H, "intermediate_size": 40, "activation": "gelu_tanh"},
+                             {"gate": "l1.gate", "up": "l1.up", "down": "l1.down"})
+            blocks = [BlockSpec(attn(0, PartSpec("sinusoid_toy", {"head_dim": hd, "amplitude": 0.7}), None), routed,
+                                pre_mixer_norm=norm("l0.n1"), pre_ffn_norm=norm("l0.n2")),
+                      BlockSpec(attn(1, PartSpec("rope", {"head_dim": hd, "theta": 10000.0}), 8), dense,
+                                pre_mixer_norm=norm("l1.n1"), pre_ffn_norm=norm("l1.n2"))]
+            return ModelSpec("RoutedToyForCausalLM", V, H, o["max_position_embeddings"],
+                             PartSpec("embedding", {"vocab_size": V, "hidden_size": H, "scale": 1.0}, {"table": "embed"}),
+                             blocks, [LayerCall(0), LayerCall(1)], norm("final_norm"),
+                             PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "softcap": None, "tie": True},
+                                      {"weight": "head", "tied_to": "embed"}))
+
+    register_part("feed_forward", "routed_toy", RoutedFeedForward)
+    register_part("position", "sinusoid_toy", SinusoidOffset)
+    register_architecture("RoutedToyForCausalLM", RoutedToyConfig)
+    return RoutedToyConfig
+
+
+def test_toy_routed_feed_forward_and_toy_position_encoding(tmp_path):
+    """A feed-forward with routing and another position encoding, both defined in this file: chosen
+    layer by layer beside the package's own parts, and the logits do not depend on the cut."""
+    import json
+    from glint_b200.engine.loading import build_engine, load_model
+    from glint_b200.engine.step import StepEntry
+    from glint_b200.weights import model_needs, random_tensors, write_safetensors
+    Config = _register_routed_toy()
+    obj = {"architectures": ["RoutedToyForCausalLM"], "hidden_size": 48, "vocab_size": 131, "experts": 3,
+           "max_position_embeddings": 128}
+    folder = str(tmp_path / "routed")
+    os.makedirs(folder)
+    json.dump(obj, open(os.path.join(folder, "config.json"), "w"))
+    tensors = random_tensors(model_needs(Config(obj)), seed=5, std=0.2, norm_std=1.0, dtype=torch.float32)
+    for k in list(tensors):
+        if k.endswith("n1") or k.endswith("n2") or k == "final_norm":
+            tensors[k] = tensors[k].abs() + 0.5
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
+
+    model = load_model(folder, "float32")
+    assert type(model.blocks[0].feed_forward).__name__ == "RoutedFeedForward"
+    assert type(model.blocks[0].mixer.position).__name__ == "SinusoidOffset"
+    assert type(model.blocks[1].mixer.position).__name__ == "Rotary"
+    engine = build_engine(model, 256, num_slots=3, use_graphs=False)
+    assert len(engine.cache.groups) == 2                       # all keys / a window of 8: pages of their own
+
+    toks_a, toks_b = random_tokens(29, 131, 1), random_tokens(21, 131, 2)
+    s = engine.open()
+    whole_a = engine.step([StepEntry(s, toks_a, list(range(29)))]).cpu()
+    engine.close(s)
+    s = engine.open()
+    whole_b = engine.step([StepEntry(s, toks_b, list(range(21)))]).cpu()
+    engine.close(s)
+    sa, sb = engine.open(), engine.open()
+    got_a, got_b = [], []
+    got_a.append(engine.step([StepEntry(sa, toks_a[:11], list(range(11)))]).cpu())
+    out = engine.step([StepEntry(sb, toks_b[:2], [0, 1]), StepEntry(sa, toks_a[11:12], [0])]).cpu()
+    got_b.append(out[:2]); got_a.append(out[2:])
+    out = engine.step([StepEntry(sa, toks_a[12:], list(range(17))), StepEntry(sb, toks_b[2:20], list(range(18)))]).cpu()
+    got_a.append(out[:17]); got_b.append(out[17:])
+    got_b.append(engine.step([StepEntry(sb, toks_b[20:], [0])]).cpu())
+    assert (torch.cat(got_a) - whole_a).abs().max().item() < 1e-4
+    assert (torch.cat(got_b) - whole_b).abs().max().item() < 1e-4
+    # the toy position encoding is felt: the same tokens shifted by one position give other logits
+    s = engine.open()
+    shifted = engine.step([StepEntry(s, [toks_a[0]] + toks_a[:28], list(range(29)))]).cpu()
+    engine.close(s)
+    assert (shifted[1:] - whole_a[:28]).abs().max().item() > 1e-3
     engine.close(sa); engine.close(sb)
     model.rt.check_status()
