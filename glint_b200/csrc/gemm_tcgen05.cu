@@ -33,6 +33,7 @@ struct GemmParams {
   int M, N, K;          // tokens, output features, reduction length
   int BN;               // tokens per tile
   int m_tiles;          // token tiles (the fast index of blockIdx.x)
+  int tma_store;        // the epilogue stages the tile in shared memory and stores it with one bulk copy
   int stages;
   int splits, kb_per_split, total_kb;
   int dual_offset;      // row offset of the second weight tile (dual kernels)
@@ -62,6 +63,14 @@ __device__ __forceinline__ float gelu_tanh_fast(float v) {
 }
 
 
+// cap * tanh(v / cap) as cap * (1 - 2 / (exp(2 v / cap) + 1)) with the hardware exponential and
+// division: a few instructions, so that the epilogue loops can be unrolled without outgrowing the
+// instruction cache (the library tanhf is a long sequence); relative error about 1e-6, far inside
+// the bfloat16 operands' own rounding.  The 32-bit engine does not use this kernel.
+__device__ __forceinline__ float softcap_fast(float v, float cap, float two_over_cap) {
+  return cap * (1.0f - __fdividef(2.0f, __expf(v * two_over_cap) + 1.0f));
+}
+
 // Writes 16 token columns of one feature per lane as bfloat16 pairs: neighbouring lanes (features
 // f, f+1) swap halves so that an even lane stores (f, f+1) of token j and the odd lane (f-1, f) of
 // token j+1, four bytes each (two-byte stores are several times slower).  N must be even.
@@ -88,7 +97,7 @@ __device__ __forceinline__ void store_result(const GemmParams& p, int f, int t, 
     const float g = p.act == 0 ? gelu_tanh(a) : a * (1.0f / (1.0f + expf(-a)));
     y = g * b;
   } else {
-    y = softcap(a, p.cap);
+    y = p.cap > 0.f ? softcap_fast(a, p.cap, 2.0f / p.cap) : a;
   }
   if (p.out_bf16)
     reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.N + f] = __float2bfloat16_rn(y);
@@ -99,7 +108,7 @@ __device__ __forceinline__ void store_result(const GemmParams& p, int f, int t, 
 template <bool DUAL>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                    const GemmParams p) {
+                    const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int b_stage_bytes = p.BN * GEMM_BK * 2;
@@ -233,7 +242,54 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     const int tile_id = (int)blockIdx.x;
     const int halves = DUAL ? 2 : 1;
-    if (ok && p.splits == 1) {
+    if (ok && p.splits == 1 && p.tma_store) {
+      // Wide token tiles: the tile is staged in the stage ring (free now: every MMA has completed) as
+      // [token][128 features], 32 consecutive features per warp store, and leaves with one bulk tensor
+      // store, which clips it at the edges of the output.  256 shared-memory stores per thread instead
+      // of 256 global ones.
+      const int t_end = min(p.BN, p.M - m0);
+      const bool capped = p.cap > 0.f;
+      const float two_over_cap = capped ? 2.0f / p.cap : 0.f;
+      const int fl = q * 32 + lane;
+      for (int c0 = 0; c0 < t_end; c0 += 16) {
+        uint32_t a[16], b[16];
+        tc::tmem_ld_16(lane_addr + c0, a);
+        if (DUAL) tc::tmem_ld_16(lane_addr + p.BN + c0, b);
+        tc::tmem_ld_wait();
+        float v[16];
+        if (DUAL) {
+          if (p.act == 0) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = gelu_tanh_fast(__uint_as_float(a[j])) * __uint_as_float(b[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float g = __uint_as_float(a[j]);
+              v[j] = g * (1.0f / (1.0f + __expf(-g))) * __uint_as_float(b[j]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(a[j]);
+          if (capped) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = softcap_fast(v[j], p.cap, two_over_cap);
+          }
+        }
+        if (p.out_bf16) {
+          __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(smem) + (size_t)c0 * GEMM_BM + fl;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) st[(size_t)j * GEMM_BM] = __float2bfloat16_rn(v[j]);
+        } else {
+          float* st = reinterpret_cast<float*>(smem) + (size_t)c0 * GEMM_BM + fl;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) st[(size_t)j * GEMM_BM] = v[j];
+        }
+      }
+      tc::fence_proxy_async();                     // the bulk copy reads shared memory through the async proxy
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) tc::tma_store_2d_and_wait_read(smem, &map_out, n0, m0);
+    } else if (ok && p.splits == 1) {
       // One row pointer per thread, advanced by a whole output row per token; the epilogue kind is
       // chosen once, outside the loops, so that each loop body is a load, a little math and a store.
       const bool f_ok = f < p.N;
@@ -281,8 +337,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(a[j]);
           if (capped) {
-#pragma unroll 1
-            for (int j = 0; j < 16; ++j) v[j] = softcap(v[j], p.cap);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = softcap_fast(v[j], p.cap, 2.0f / p.cap);
           }
           if (pairs) {
             store_bf16_pairs(o, p.N, f, f_pair_ok, c0, n, v, lane);
@@ -295,6 +351,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       } else {
         float* o = reinterpret_cast<float*>(p.out) + (size_t)m0 * p.N + f;
         const bool capped = p.cap > 0.f;
+        const float two_over_cap = capped ? 2.0f / p.cap : 0.f;
         for (int c0 = 0; c0 < t_end; c0 += 16) {
           uint32_t a[16];
           tc::tmem_ld_16(lane_addr + c0, a);
@@ -302,8 +359,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           const int n = min(16, t_end - c0);
           if (f_ok) {
             if (capped) {
-#pragma unroll 1
-              for (int j = 0; j < n; ++j) o[(size_t)(c0 + j) * p.N] = softcap(__uint_as_float(a[j]), p.cap);
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (j < n) o[(size_t)(c0 + j) * p.N] = softcap_fast(__uint_as_float(a[j]), p.cap, two_over_cap);
             } else {
 #pragma unroll
               for (int j = 0; j < 16; ++j)
@@ -492,17 +550,36 @@ GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int ou
   if (rc != GLINT_OK) return rc;
   const int smem_bytes = stages * stage_bytes + (int)sizeof(GemmShared) + 1024;
   p.m_tiles = m_tiles;
+  // the staged epilogue: bfloat16 output (two-byte global stores are slow; for float32 the direct
+  // stores measured faster), token tiles of 64 and more, no split, output rows on 16-byte boundaries
+  CUtensorMap map_out = map_x;
+  const int es = out_bf16 ? 2 : 4;
+  p.tma_store = 0;
+  static int tma_store_on = -1;
+  if (tma_store_on < 0) { const char* ev = getenv("GLINT_GEMM_TMA_STORE"); tma_store_on = ev ? atoi(ev) : 1; }
+  if (tma_store_on && out_bf16 && splits == 1 && bn >= 64 && ((long long)N * es) % 16 == 0 && ((uintptr_t)out & 15) == 0 &&
+      (long long)bn * GEMM_BM * es <= (long long)stages * stage_bytes) {
+    EncodeTiledFn fn = encode_fn();
+    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    cuuint64_t strides[1] = {(cuuint64_t)N * es};
+    cuuint32_t box[2] = {(cuuint32_t)GEMM_BM, (cuuint32_t)bn};
+    cuuint32_t elem[2] = {1, 1};
+    if (fn && fn(&map_out, out_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, dims,
+                 strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+      p.tma_store = 1;
+  }
   dim3 grid(n_tiles * m_tiles, 1, splits);
   cudaError_t e;
   if (dual) {
     e = cudaFuncSetAttribute(gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) return (int)e;
-    e = launch_kernel(gemm_tcgen05_kernel<true>, grid, dim3(GEMM_THREADS), smem_bytes, stream, map_w, map_x, p);
+    e = launch_kernel(gemm_tcgen05_kernel<true>, grid, dim3(GEMM_THREADS), smem_bytes, stream, map_w, map_x, map_out, p);
     if (e != cudaSuccess) return (int)e;
   } else {
     e = cudaFuncSetAttribute(gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) return (int)e;
-    e = launch_kernel(gemm_tcgen05_kernel<false>, grid, dim3(GEMM_THREADS), smem_bytes, stream, map_w, map_x, p);
+    e = launch_kernel(gemm_tcgen05_kernel<false>, grid, dim3(GEMM_THREADS), smem_bytes, stream, map_w, map_x, map_out, p);
     if (e != cudaSuccess) return (int)e;
   }
   return (int)cudaGetLastError();
