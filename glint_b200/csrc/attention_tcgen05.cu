@@ -37,6 +37,7 @@ struct FaParams {
   int nh, nkv, hd, page_size, num_pages;
   float multiplier, cap;
   int window;
+  int q_tiles, n_seqs;
   int whole;       // keys in boxes of 8 rows x head_dim, values in boxes of a page x head_dim (see the producer)
   int* status;
 };
@@ -65,10 +66,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   uint8_t* sp = sv + (size_t)2 * nsub * FA_KV_SUB;
   FaShared* sh = reinterpret_cast<FaShared*>(sp + FA_P_BYTES);
 
-  const int seq = blockIdx.y, kvh = blockIdx.z;
+  // blockIdx.x counts (query tile from the last, request, kv head): the blocks with the most key tiles
+  // start first whatever their head (with heads in the slow grid dimensions the long tiles of the
+  // last heads started last: 4096 tokens 122 -> 91 us)
+  const int per_tile = p.n_seqs * p.nkv;
+  const int tile = p.q_tiles - 1 - (int)blockIdx.x / per_tile;
+  const int seq = ((int)blockIdx.x % per_tile) / p.nkv, kvh = (int)blockIdx.x % p.nkv;
   const int t_begin = p.cu_seqlens[seq];
   const int q_len = p.cu_seqlens[seq + 1] - t_begin;
-  const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;        // long tiles first
   const int tok0 = tile * tok_per_tile;
   if (tok0 >= q_len) return;
   const int n_tok = min(tok_per_tile, q_len - tok0);
@@ -493,8 +498,11 @@ GLINT_API int glint_attention_tcgen05(const void* q, const void* k_pool, const v
   const int nsub = (hd + 63) / 64;
   const int smem = nsub * FA_Q_SUB + 4 * nsub * FA_KV_SUB + FA_P_BYTES + (int)sizeof(FaShared) + 1024 + 64;
   if (smem > 227 * 1024) return GLINT_ERR_UNSUPPORTED_SIZE;
-  dim3 grid((max_q_len + tok_per_tile - 1) / tok_per_tile, n_seqs, nkv);
-  if (grid.y > 65535 || grid.z > 65535) return GLINT_ERR_UNSUPPORTED_SIZE;
+  p.q_tiles = (max_q_len + tok_per_tile - 1) / tok_per_tile;
+  p.n_seqs = n_seqs;
+  const long long blocks = (long long)p.q_tiles * n_seqs * nkv;
+  if (blocks > 0x7fffffffLL) return GLINT_ERR_UNSUPPORTED_SIZE;
+  dim3 grid((unsigned)blocks, 1, 1);
   cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return (int)e;
   attention_tcgen05_kernel<<<grid, FA_THREADS, smem, stream>>>(map_q, map_k, map_v, p);
