@@ -164,7 +164,7 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int* _
 // Fast forms of the row kernels for widths that are a multiple of 4: a row is loaded once into
 // registers as float4 (all loads in flight together), reduced, and written; nothing is re-read.
 // ---------------------------------------------------------------------------------------------
-constexpr int ROW_THREADS = 256;
+constexpr int ROW_THREADS = 256;   // the most; a launch takes 256, 192 or 128, see row_threads()
 
 template <typename S>
 __device__ __forceinline__ void store4(S* dst, float a, float b, float c, float d);
@@ -195,7 +195,7 @@ rmsnorm_fast_kernel(const float* __restrict__ x, const int* __restrict__ row_ind
   float4 xv[ITERS], wv[ITERS];
 #pragma unroll
   for (int it = 0; it < ITERS; ++it) {
-    const int i = threadIdx.x + it * ROW_THREADS;
+    const int i = threadIdx.x + it * blockDim.x;
     xv[it] = i < H4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     wv[it] = i < H4 ? w4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
   }
@@ -207,7 +207,7 @@ rmsnorm_fast_kernel(const float* __restrict__ x, const int* __restrict__ row_ind
   const float rs = 1.0f / sqrtf(ss / (float)H + eps);
 #pragma unroll
   for (int it = 0; it < ITERS; ++it) {
-    const int i = threadIdx.x + it * ROW_THREADS;
+    const int i = threadIdx.x + it * blockDim.x;
     if (i < H4)
       store4<S>(out + (size_t)r * H + 4 * i, xv[it].x * rs * (offset + wv[it].x), xv[it].y * rs * (offset + wv[it].y),
                 xv[it].z * rs * (offset + wv[it].z), xv[it].w * rs * (offset + wv[it].w));
@@ -230,7 +230,7 @@ add_rmsnorm_fast_kernel(float* __restrict__ x, const float* __restrict__ y, cons
   float4 xv[ITERS], yv[ITERS], wa[ITERS], wb[ITERS];
 #pragma unroll
   for (int it = 0; it < ITERS; ++it) {
-    const int i = threadIdx.x + it * ROW_THREADS;
+    const int i = threadIdx.x + it * blockDim.x;
     const bool in = i < H4;
     xv[it] = in ? xr[i] : zero;
     yv[it] = in ? yr[i] : zero;
@@ -249,7 +249,7 @@ add_rmsnorm_fast_kernel(float* __restrict__ x, const float* __restrict__ y, cons
   float ss_x = 0.f;
 #pragma unroll
   for (int it = 0; it < ITERS; ++it) {
-    const int i = threadIdx.x + it * ROW_THREADS;
+    const int i = threadIdx.x + it * blockDim.x;
     if (w_a) {
       xv[it].x += yv[it].x * rs_a * (offset_a + wa[it].x);
       xv[it].y += yv[it].y * rs_a * (offset_a + wa[it].y);
@@ -269,7 +269,7 @@ add_rmsnorm_fast_kernel(float* __restrict__ x, const float* __restrict__ y, cons
   const float rs_b = w_b ? 1.0f / sqrtf(ss_x / (float)H + eps_b) : 1.f;
 #pragma unroll
   for (int it = 0; it < ITERS; ++it) {
-    const int i = threadIdx.x + it * ROW_THREADS;
+    const int i = threadIdx.x + it * blockDim.x;
     if (i >= H4) continue;
     if (w_b)
       store4<S>(out + (size_t)r * H + 4 * i, xv[it].x * rs_b * (offset_b + wb[it].x),
@@ -415,10 +415,27 @@ using namespace glint;
 
 // Number of float4 loads per thread the fast row kernels need, or 0 when the row does not
 // qualify (width not a multiple of 4, too wide, or a pointer not 16-byte aligned).
+// Threads of a row block: of 256, 192 and 128 the count that leaves the fewest idle lanes in the
+// last pass over the row (a width of 2304 is three passes of 192 float4 exactly, against 2.25 of 256).
+static int row_threads(int H) {
+  const int H4 = H / 4;
+  int best = ROW_THREADS, best_waste = 1 << 30;
+  for (int t = ROW_THREADS; t >= 128; t -= 64) {
+    const int iters = (H4 + t - 1) / t;
+    const int waste = iters * t - H4;
+    if (iters <= 8 && waste < best_waste) {
+      best = t;
+      best_waste = waste;
+    }
+  }
+  return best;
+}
+
 static int fast_iters(int H, const void* a, const void* b, const void* c, const void* d) {
   if (H % 4 || H <= 0) return 0;
   if ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)c) | ((uintptr_t)d)) & 15) return 0;
-  const int iters = (H / 4 + ROW_THREADS - 1) / ROW_THREADS;
+  const int threads = row_threads(H);
+  const int iters = (H / 4 + threads - 1) / threads;
   return iters <= 8 ? iters : 0;
 }
 
@@ -437,7 +454,7 @@ GLINT_API int glint_rmsnorm(const float* x, const int* row_index, const float* w
   if (rows <= 0) return GLINT_OK;
   const int iters = fast_iters(H, x, w, out, nullptr);
   int rc = 0;
-#define RMS_FAST(N) DISPATCH(dtype, rc = (int)launch_kernel(rmsnorm_fast_kernel<S, N>, dim3(rows), dim3(ROW_THREADS), 0, stream, x, row_index, w, (S*)out, H, eps, offset))
+#define RMS_FAST(N) DISPATCH(dtype, rc = (int)launch_kernel(rmsnorm_fast_kernel<S, N>, dim3(rows), dim3(row_threads(H)), 0, stream, x, row_index, w, (S*)out, H, eps, offset))
   if (iters == 1) { RMS_FAST(1); }
   else if (iters == 2) { RMS_FAST(2); }
   else if (iters > 0 && iters <= 4) { RMS_FAST(4); }
@@ -457,7 +474,7 @@ GLINT_API int glint_add_rmsnorm(float* x, const float* y, const float* w_a, floa
   int iters = fast_iters(H, x, y, out, w_a);
   if (w_b && ((uintptr_t)w_b & 15)) iters = 0;
   int rc = 0;
-#define ADD_FAST(N) DISPATCH(dtype, rc = (int)launch_kernel(add_rmsnorm_fast_kernel<S, N>, dim3(rows), dim3(ROW_THREADS), 0, stream, x, y, w_a, eps_a, offset_a, (S*)out, w_b, eps_b, offset_b, H))
+#define ADD_FAST(N) DISPATCH(dtype, rc = (int)launch_kernel(add_rmsnorm_fast_kernel<S, N>, dim3(rows), dim3(row_threads(H)), 0, stream, x, y, w_a, eps_a, offset_a, (S*)out, w_b, eps_b, offset_b, H))
   if (iters == 1) { ADD_FAST(1); }
   else if (iters == 2) { ADD_FAST(2); }
   else if (iters <= 4 && iters > 0) { ADD_FAST(4); }
