@@ -296,6 +296,23 @@ rope_kv_write_fast_kernel(const float* __restrict__ qkv, const int* __restrict__
   const int pos = positions[t];
   const int half = hd >> 1;
   const float ps = (float)pos / factor;
+  const float* row = qkv + (size_t)t * (nh + 2 * nkv) * hd;
+  const int half4 = half >> 2;   // items: four adjacent j of one head (hd is a multiple of 8 here)
+  const int n_items = (nh + nkv) * half4;
+  // The first items' operands are requested before the sines and cosines are computed (accurate
+  // sincosf of a large angle is a long sequence): the memory latency passes meanwhile.  An item is
+  // read as two float4 and written as two groups of four values (two-byte stores are slow).
+  constexpr int HELD = 2;
+  float4 lo[HELD], hi[HELD];
+#pragma unroll
+  for (int u = 0; u < HELD; ++u) {
+    const int w = threadIdx.x + u * blockDim.x;
+    if (w < n_items) {
+      const float* src = row + (size_t)(w / half4) * hd + (w % half4) * 4;
+      lo[u] = *reinterpret_cast<const float4*>(src);
+      hi[u] = *reinterpret_cast<const float4*>(src + half);
+    }
+  }
   for (int j = threadIdx.x; j < half; j += blockDim.x) {
     float s, c;
     sincosf(ps * inv_freq[j], &s, &c);
@@ -312,25 +329,26 @@ rope_kv_write_fast_kernel(const float* __restrict__ qkv, const int* __restrict__
     }
   }
   __syncthreads();
-  const float* row = qkv + (size_t)t * (nh + 2 * nkv) * hd;
-  const int half2 = half >> 1;   // pairs of adjacent j
-  for (int w = threadIdx.x; w < (nh + nkv) * half2; w += blockDim.x) {
-    const int head = w / half2, j = (w % half2) * 2;
-    const float* src = row + (size_t)head * hd;
-    const float2 lo = *reinterpret_cast<const float2*>(src + j);
-    const float2 hi = *reinterpret_cast<const float2*>(src + j + half);
-    const float c0 = trig[j], c1 = trig[j + 1], s0 = trig[half + j], s1 = trig[half + j + 1];
-    const float a0 = lo.x * c0 - hi.x * s0, a1 = lo.y * c1 - hi.y * s1;
-    const float b0 = lo.x * s0 + hi.x * c0, b1 = lo.y * s1 + hi.y * c1;
+  auto rotate = [&](int w, float4 l, float4 h) {
+    const int head = w / half4, j = (w % half4) * 4;
+    const float4 c = *reinterpret_cast<const float4*>(trig + j), sn = *reinterpret_cast<const float4*>(trig + half + j);
     S* dst = nullptr;
     if (head < nh) dst = q_out + (size_t)t * nh * hd + (size_t)head * hd;
     else if (page_base >= 0) dst = k_pool + page_base + (long long)(head - nh) * page_size * hd;
     if (dst) {
-      dst[j] = from_float<S>(a0);
-      dst[j + 1] = from_float<S>(a1);
-      dst[j + half] = from_float<S>(b0);
-      dst[j + half + 1] = from_float<S>(b1);
+      store4<S>(dst + j, l.x * c.x - h.x * sn.x, l.y * c.y - h.y * sn.y, l.z * c.z - h.z * sn.z, l.w * c.w - h.w * sn.w);
+      store4<S>(dst + j + half, l.x * sn.x + h.x * c.x, l.y * sn.y + h.y * c.y, l.z * sn.z + h.z * c.z,
+                l.w * sn.w + h.w * c.w);
     }
+  };
+#pragma unroll
+  for (int u = 0; u < HELD; ++u) {
+    const int w = threadIdx.x + u * blockDim.x;
+    if (w < n_items) rotate(w, lo[u], hi[u]);
+  }
+  for (int w = threadIdx.x + HELD * blockDim.x; w < n_items; w += blockDim.x) {
+    const float* src = row + (size_t)(w / half4) * hd + (w % half4) * 4;
+    rotate(w, *reinterpret_cast<const float4*>(src), *reinterpret_cast<const float4*>(src + half));
   }
   if (page_base >= 0) {
     const float* vsrc = row + (size_t)(nh + nkv) * hd;
