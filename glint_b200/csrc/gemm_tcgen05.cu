@@ -33,6 +33,7 @@ struct GemmParams {
   int M, N, K;          // tokens, output features, reduction length
   int BN;               // tokens per tile
   int m_tiles;          // token tiles (the fast index of blockIdx.x)
+  int wide;             // dual kernel without gating: the second tile is the next 128 features (dual_offset 128)
   int tma_store;        // the epilogue stages the tile in shared memory and stores it with one bulk copy
   int stages;
   int splits, kb_per_split, total_kb;
@@ -122,7 +123,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   // tiles (feature tiles first re-read the weights once per token tile: 346 MB instead of 94 MB for
   // the gate/up product of a 2048-token portion).
   const int m_tile = (int)blockIdx.x % p.m_tiles, n_tile = (int)blockIdx.x / p.m_tiles;
-  const int n0 = n_tile * GEMM_BM;
+  const int n0 = n_tile * (p.wide ? 2 * GEMM_BM : GEMM_BM);
   const int m0 = m_tile * p.BN;
   const int split = blockIdx.z;
   const int kb_begin = split * p.kb_per_split;
@@ -298,7 +299,52 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       // partner and takes the scalar store)
       const bool pairs = (p.N & 1) == 0;
       const bool f_pair_ok = (f | 1) < p.N;
-      if (DUAL) {
+      if (DUAL && p.wide) {
+        // two plain tiles of 128 features side by side: a block of 256 features x 256 tokens takes in
+        // 64 KB per 8 MMAs where two blocks of 128 features take 96 KB, and one SM's intake from L2 is
+        // what bounds a 128 x 256 tile
+        const int f2 = f + GEMM_BM;
+        const bool f2_ok = f2 < p.N, f2_pair_ok = (f2 | 1) < p.N;
+        const bool capped = p.cap > 0.f;
+        const float two_over_cap = capped ? 2.0f / p.cap : 0.f;
+        for (int c0 = 0; c0 < t_end; c0 += 16) {
+          uint32_t a[16], b[16];
+          tc::tmem_ld_16(lane_addr + c0, a);
+          tc::tmem_ld_16(lane_addr + p.BN + c0, b);
+          tc::tmem_ld_wait();
+          const int n = min(16, t_end - c0);
+          float va[16], vb[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            va[j] = __uint_as_float(a[j]);
+            vb[j] = __uint_as_float(b[j]);
+            if (capped) {
+              va[j] = softcap_fast(va[j], p.cap, two_over_cap);
+              vb[j] = softcap_fast(vb[j], p.cap, two_over_cap);
+            }
+          }
+          if (p.out_bf16) {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m0 * p.N;
+            if (pairs) {
+              store_bf16_pairs(o, p.N, f, f_pair_ok, c0, n, va, lane);
+              store_bf16_pairs(o, p.N, f2, f2_pair_ok, c0, n, vb, lane);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (j < n && f_ok) o[(size_t)(c0 + j) * p.N + f] = __float2bfloat16_rn(va[j]);
+                if (j < n && f2_ok) o[(size_t)(c0 + j) * p.N + f2] = __float2bfloat16_rn(vb[j]);
+              }
+            }
+          } else {
+            float* o = reinterpret_cast<float*>(p.out) + (size_t)m0 * p.N;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (j < n && f_ok) o[(size_t)(c0 + j) * p.N + f] = va[j];
+              if (j < n && f2_ok) o[(size_t)(c0 + j) * p.N + f2] = vb[j];
+            }
+          }
+        }
+      } else if (DUAL) {
         __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m0 * p.N;
         for (int c0 = 0; c0 < t_end; c0 += 16) {
           uint32_t a[16], b[16];
@@ -497,7 +543,26 @@ GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int ou
   if (dual && bn > 256) bn = 256;
   p.BN = bn;
   const int m_tiles = (M + bn - 1) / bn;
-  const int n_tiles = (N + GEMM_BM - 1) / GEMM_BM;
+  int n_tiles = (N + GEMM_BM - 1) / GEMM_BM;
+  // A plain product whose 128-feature tiles would need more than one wave, and whose 256-feature
+  // tiles still fill three quarters of the SMs, runs as the dual kernel with two plain tiles.
+  static int sms = 0, wide_on = -1;
+  if (sms == 0) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  if (wide_on < 0) { const char* ev = getenv("GLINT_GEMM_WIDE"); wide_on = ev ? atoi(ev) : 1; }
+  const int n_tiles_wide = (N + 2 * GEMM_BM - 1) / (2 * GEMM_BM);
+  p.wide = 0;
+  if (wide_on && !dual && force_splits <= 1 && bn == 256 && (long long)n_tiles * m_tiles > sms &&
+      (long long)n_tiles_wide * m_tiles * 4 >= 3LL * sms) {
+    p.wide = 1;
+    dual = 1;
+    dual_offset = GEMM_BM;
+    n_tiles = n_tiles_wide;
+  }
   const int stage_bytes = A_STAGE_BYTES * (dual ? 2 : 1) + bn * GEMM_BK * 2;
   int stages = (227 * 1024 - 1024 - (int)sizeof(GemmShared) - 256) / stage_bytes;
   if (stages > GEMM_MAX_STAGES) stages = GEMM_MAX_STAGES;
@@ -557,7 +622,7 @@ GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int ou
   p.tma_store = 0;
   static int tma_store_on = -1;
   if (tma_store_on < 0) { const char* ev = getenv("GLINT_GEMM_TMA_STORE"); tma_store_on = ev ? atoi(ev) : 1; }
-  if (tma_store_on && out_bf16 && splits == 1 && bn >= 64 && ((long long)N * es) % 16 == 0 && ((uintptr_t)out & 15) == 0 &&
+  if (tma_store_on && !p.wide && out_bf16 && splits == 1 && bn >= 64 && ((long long)N * es) % 16 == 0 && ((uintptr_t)out & 15) == 0 &&
       (long long)bn * GEMM_BM * es <= (long long)stages * stage_bytes) {
     EncodeTiledFn fn = encode_fn();
     cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
