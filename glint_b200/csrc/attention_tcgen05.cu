@@ -1,15 +1,16 @@
 // Flash attention for prompt portions over the paged cache on the 5th-generation tensor cores.
 //
-// grid = (query tiles, requests of the step, kv heads); one block per SM.  A block owns 128
+// One block per (query tile, request, kv head), longest tiles first; one block per SM.  A block owns 128
 // query rows: rows are (token, query head of the group) pairs, so the heads that share a kv head
 // share every key/value tile.  Keys come in tiles of 64 whose boundaries are multiples of 64 in
 // absolute position.
 //   warp 0     TMA: the query tile once (one 4-D box per 64 columns), then key and value tiles
 //              page by page into two-deep rings (one elected thread issues every box)
-//   warp 1     tcgen05.mma: S = Q K^T into tensor memory, then O += P V (V is the MN-major operand)
+//   warp 1     tcgen05.mma: S = Q K^T into tensor memory (two buffers), then O += P V with P read from
+//              tensor memory as the A operand and V as the MN-major B operand
 //   warps 2-9  softmax: two threads share one row of S (tcgen05.ld), scale, soft-cap and mask it
 //              by absolute position, keeps the running max and sum in 32-bit, writes P as bfloat16
-//              into shared memory in the swizzled operand layout, and rescales its row of O in
+//              pairs into tensor memory (tcgen05.st, two buffers), and rescales its row of O in
 //              tensor memory only when the running max grew by more than 8 (the result is the same:
 //              the sum carries the same stale max)
 // Formulas: src/tensor/flash.rs:65-123 (online softmax), :76-87 (multiplier, cap * tanh(x / cap)),
@@ -25,7 +26,6 @@ constexpr int FA_N = 64;              // keys per tile
 constexpr int FA_THREADS = 320;      // TMA warp, MMA warp, 8 softmax warps
 constexpr int FA_Q_SUB = FA_M * 128;  // bytes of a 64-column slice of the query tile
 constexpr int FA_KV_SUB = FA_N * 128; // bytes of a 64-column slice of a key or value tile
-constexpr int FA_P_BYTES = FA_M * 128;
 constexpr float FA_RESCALE = 8.0f;
 
 struct FaParams {
@@ -43,7 +43,8 @@ struct FaParams {
 };
 
 struct FaShared {
-  uint64_t q_full, p_ready, p_free, o_full;
+  uint64_t q_full, p_ready, o_full;
+  uint64_t p_free[2];            // one per P buffer: the product that read it has completed
   uint64_t s_full[2];
   uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
   uint32_t tmem_base;
@@ -63,8 +64,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   uint8_t* sq = smem;
   uint8_t* sk = sq + (size_t)nsub * FA_Q_SUB;            // [2][nsub][64 keys x 128 B]
   uint8_t* sv = sk + (size_t)2 * nsub * FA_KV_SUB;
-  uint8_t* sp = sv + (size_t)2 * nsub * FA_KV_SUB;
-  FaShared* sh = reinterpret_cast<FaShared*>(sp + FA_P_BYTES);
+  FaShared* sh = reinterpret_cast<FaShared*>(sv + (size_t)2 * nsub * FA_KV_SUB);
 
   // blockIdx.x counts (query tile from the last, request, kv head): the blocks with the most key tiles
   // start first whatever their head (with heads in the slow grid dimensions the long tiles of the
@@ -88,7 +88,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   if (threadIdx.x == 0) {
     tc::mbar_init(&sh->q_full, 1);
     tc::mbar_init(&sh->p_ready, 256);
-    tc::mbar_init(&sh->p_free, 1);
+    tc::mbar_init(&sh->p_free[0], 1);
+    tc::mbar_init(&sh->p_free[1], 1);
     tc::mbar_init(&sh->o_full, 1);
     for (int b = 0; b < 2; ++b) {
       tc::mbar_init(&sh->s_full[b], 1);
@@ -109,6 +110,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   tc::fence_after_thread_sync();
   const uint32_t tmem_s = sh->tmem_base;          // two score tiles: columns [0, 64) and [64, 128)
   const uint32_t tmem_o = tmem_s + 2 * FA_N;
+  // P as bfloat16 pairs, two buffers of 32 columns behind O (head sizes up to 256: 128 + 256 + 64 <= 512)
+  const uint32_t tmem_p = tmem_o + 256;
   volatile int* abort_flag = &sh->abort_flag;
 
   if (warp == 0) {
@@ -197,13 +200,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       const uint32_t idesc_s = tc::idesc_bf16_f32(FA_M, FA_N);
       const uint32_t idesc_o = tc::idesc_bf16_f32_b_mn(FA_M, hd);
       const uint32_t q_addr = tc::smem_u32(sq), k_addr = tc::smem_u32(sk), v_addr = tc::smem_u32(sv);
-      const uint32_t p_addr = tc::smem_u32(sp);
       // Order of issue: S(0), S(1), then for every tile j: O += P(j) V(j), S(j+2).  While the softmax
       // warps work on S(j+1) the tensor pipe runs P(j) V(j) and S(j+2).  This one thread issues 20
       // MMAs per tile, so its instruction count is what matters: every descriptor is a constant base
       // plus a small offset (the address field counts 16 bytes).
       const uint64_t qd0 = tc::smem_desc_k_sw128(q_addr);
-      const uint64_t pd0 = tc::smem_desc_k_sw128(p_addr);
       // Two layouts of a key or value tile (see the producer).  Separate boxes per 64-column slice:
       // [slice][64 keys][128 B].  Whole boxes: keys [group of 8][slice][8 rows][128 B], values
       // [page][slice][rows of the page][128 B].
@@ -251,9 +252,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const uint64_t vd = b ? vd0[1] : vd0[0];
 #pragma unroll
         for (int kk = 0; kk < FA_N / 16; ++kk)
-          tc::mma_bf16_ss(tmem_o, pd0 + 2 * kk, vd + v_step[kk], idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          tc::mma_bf16_ts(tmem_o, tmem_p + (uint32_t)(j & 1) * 32 + 8 * kk, vd + v_step[kk], idesc_o,
+                          (j > 0 || kk > 0) ? 1u : 0u);
         tc::mma_commit(&sh->v_empty[b]);
-        tc::mma_commit(&sh->p_free);             // P and this row of O may be touched again
+        tc::mma_commit(&sh->p_free[j & 1]);      // this P buffer, and O, may be touched again
         if (j + 2 < n_tiles) ok = issue_s(j + 2);
       }
       tc::mma_commit(&sh->o_full);
@@ -331,13 +333,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         l *= corr;
         m_used = mt;
       }
-      // the previous tile's P V product must be complete before O or P is touched
-      if (j > 0) {
-        ok = tc::mbar_wait(&sh->p_free, (j - 1) & 1, abort_flag);
+      // P(j) goes into the buffer that the product of tile j-2 read: that one must be complete (it
+      // long is).  O is rescaled only after the product of tile j-1.
+      if (j > 1) {
+        ok = tc::mbar_wait(&sh->p_free[j & 1], ((j - 2) >> 1) & 1, abort_flag);
         if (!ok) break;
-        tc::fence_after_thread_sync();
       }
-      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+      const bool rescale = j > 0 && __any_sync(0xffffffffu, grow);
+      if (rescale) {
+        ok = tc::mbar_wait(&sh->p_free[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag);
+        if (!ok) break;
+      }
+      tc::fence_after_thread_sync();
+      if (rescale) {
         for (int c0 = o_lo; c0 < o_hi; c0 += 16) {
           uint32_t o[16];
           tc::tmem_ld_16(tmem_o + lane_base + c0, o);
@@ -349,27 +357,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         tc::tmem_st_wait();
       }
       const float base = m_used == -INFINITY ? 0.f : m_used;
-      uint8_t* prow = sp + (size_t)r * 128;
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t packed[HALF / 2];               // this thread's 32 keys of its row, two to a column
 #pragma unroll
-      for (int ch = 0; ch < HALF / 8; ++ch) {
-        float pv[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          pv[i] = tc::exp2_approx(x[ch * 8 + i] - base);
-          l4[i & 3] += pv[i];
-        }
-        uint4 packed;
-        __nv_bfloat162 h0 = __floats2bfloat162_rn(pv[0], pv[1]), h1 = __floats2bfloat162_rn(pv[2], pv[3]);
-        __nv_bfloat162 h2 = __floats2bfloat162_rn(pv[4], pv[5]), h3 = __floats2bfloat162_rn(pv[6], pv[7]);
-        packed.x = *reinterpret_cast<uint32_t*>(&h0);
-        packed.y = *reinterpret_cast<uint32_t*>(&h1);
-        packed.z = *reinterpret_cast<uint32_t*>(&h2);
-        packed.w = *reinterpret_cast<uint32_t*>(&h3);
-        *reinterpret_cast<uint4*>(prow + (((half * (HALF / 8) + ch) ^ (r & 7)) << 4)) = packed;
+      for (int c = 0; c < HALF; c += 2) {
+        const float p0 = tc::exp2_approx(x[c] - base), p1 = tc::exp2_approx(x[c + 1] - base);
+        l4[c & 3] += p0;
+        l4[(c + 1) & 3] += p1;
+        const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+        packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&h);
       }
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-      tc::fence_proxy_async();                 // the MMA reads P through the async proxy
+      tc::tmem_st_16(tmem_p + (uint32_t)(j & 1) * 32 + lane_base + half * (HALF / 2), packed);
+      tc::tmem_st_wait();
       tc::fence_before_thread_sync();
       tc::mbar_arrive(&sh->p_ready);
     }
@@ -496,7 +496,7 @@ GLINT_API int glint_attention_tcgen05(const void* q, const void* k_pool, const v
   p.out = (__nv_bfloat16*)out; p.nh = nh; p.nkv = nkv; p.hd = hd; p.page_size = page_size; p.num_pages = num_pages;
   p.multiplier = multiplier; p.cap = cap; p.window = window; p.whole = whole; p.status = status;
   const int nsub = (hd + 63) / 64;
-  const int smem = nsub * FA_Q_SUB + 4 * nsub * FA_KV_SUB + FA_P_BYTES + (int)sizeof(FaShared) + 1024 + 64;
+  const int smem = nsub * FA_Q_SUB + 4 * nsub * FA_KV_SUB + (int)sizeof(FaShared) + 1024 + 64;
   if (smem > 227 * 1024) return GLINT_ERR_UNSUPPORTED_SIZE;
   p.q_tiles = (max_q_len + tok_per_tile - 1) / tok_per_tile;
   p.n_seqs = n_seqs;
