@@ -1,5 +1,6 @@
-"""The kernels at the sizes of a real model: hidden 2304, 8 heads of 256 in 4 groups, feed-forward 9216,
-vocabulary 256000, window 4096 (two layers, random weights made on the device).
+"""The kernels at the sizes of real models: hidden 2304, 8 heads of 256 in 4 groups, feed-forward 9216, and
+hidden 4608, 32 heads of 128 in 16 groups, feed-forward 36864; vocabulary 256000, window 4096 (two layers,
+random weights made on the device).
 
 The tiny configurations of the other tests never reach the paths that these sizes take: whole-page TMA
 boxes over four 64-column slices, the dual-tile product, split factors and clusters chosen for 148 SMs,
@@ -22,16 +23,21 @@ CONFIG = {
     "max_position_embeddings": 8192, "tie_word_embeddings": True, "hidden_activation": "gelu_pytorch_tanh",
 }
 TAIL = 6
+SHAPES = {
+    "2b": {},
+    "27b": {"hidden_size": 4608, "num_attention_heads": 32, "num_key_value_heads": 16, "head_dim": 128,
+            "intermediate_size": 36864, "query_pre_attn_scalar": 144},
+}
 
 
-@pytest.fixture(scope="module")
-def engines():
+@pytest.fixture(scope="module", params=sorted(SHAPES))
+def engines(request):
     from glint_b200.config import config_from_dict
     from glint_b200.engine.loading import build_engine
     from glint_b200.engine.model import CausalLM
     from glint_b200.runtime import Runtime
     from glint_b200.weights.loader import kept_dtype
-    config = config_from_dict(CONFIG)
+    config = config_from_dict(dict(CONFIG, **SHAPES[request.param]))
     gen = torch.Generator(device="cuda:0")
     gen.manual_seed(11)
     made = {}
@@ -52,7 +58,9 @@ def engines():
         model.bind(tensors)
         out[dtype] = build_engine(model, 6144 if dtype == "bfloat16" else 1024, num_slots=4)
     made.clear()
-    return out
+    yield out
+    out.clear()
+    torch.cuda.empty_cache()
 
 
 def _whole(engine, toks):
