@@ -26,6 +26,7 @@ namespace glint {
 constexpr int GEMM_BM = 128;      // weight rows (output features) per tile
 constexpr int GEMM_BK = 64;       // K elements per stage: 128 bytes, one swizzle atom
 constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_SPREAD_DEPARTED = 4096;   // second half of the counters: blocks that have finished reading
 constexpr int GEMM_MAX_STAGES = 8;
 constexpr int A_STAGE_BYTES = GEMM_BM * GEMM_BK * 2;
 
@@ -34,6 +35,7 @@ struct GemmParams {
   int BN;               // tokens per tile
   int m_tiles;          // token tiles (the fast index of blockIdx.x)
   int wide;             // dual kernel without gating: the second tile is the next 128 features (dual_offset 128)
+  int spread;           // split-K: every block of a tile adds up a share of its columns (the grid fits the SMs at once)
   int tma_store;        // the epilogue stages the tile in shared memory and stores it with one bulk copy
   int stages;
   int splits, kb_per_split, total_kb;
@@ -427,7 +429,64 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         for (int j = 0; j < 16; ++j) mine[(size_t)(c0 + j) * GEMM_BM + q * 32 + lane] = __uint_as_float(a[j]);
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 64) {
+      if (p.spread) {
+        // Every block of the tile waits until all of them have written (they are all on an SM at the
+        // same time: the host takes this path only for grids of at most one block per SM) and adds up
+        // its share of the columns: one block alone would read all partial tiles through one SM.
+        int* arrived = &p.counters[tile_id];
+        int* departed = &p.counters[GEMM_SPREAD_DEPARTED + tile_id];
+        if (threadIdx.x == 64) {
+          __threadfence();
+          atomicAdd(arrived, 1);
+          int seen = 0;
+          for (uint32_t i = 0; i < tc::WAIT_LIMIT && seen < p.splits; ++i) seen = atomicAdd(arrived, 0);
+          if (seen < p.splits) *abort_flag = 1;
+          sh->is_last = seen >= p.splits;
+          __threadfence();
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (sh->is_last) {
+          const float* base = p.workspace + ((size_t)tile_id * p.splits * halves) * p.BN * GEMM_BM;
+          const size_t split_stride = (size_t)halves * p.BN * GEMM_BM;
+          const int per = (p.BN + p.splits - 1) / p.splits;
+          const int c_begin = split * per, c_end = min(p.BN, c_begin + per);
+          for (int c0 = c_begin; c0 < c_end; c0 += 4) {      // splits are added in order, four in flight
+            float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int s0 = 0; s0 < p.splits; s0 += 4) {
+              float va[4][4], vb[DUAL ? 4 : 1][4];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const bool in = s0 + u < p.splits;
+                const float* src = base + (size_t)(in ? s0 + u : s0) * split_stride + (size_t)c0 * GEMM_BM + q * 32 + lane;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const bool inj = in && c0 + j < c_end;
+                  va[u][j] = inj ? __ldcg(src + (size_t)j * GEMM_BM) : 0.f;
+                  if (DUAL) vb[u][j] = inj ? __ldcg(src + (size_t)(p.BN + j) * GEMM_BM) : 0.f;
+                }
+              }
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  a[j] += va[u][j];
+                  if (DUAL) b[j] += vb[u][j];
+                }
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (c0 + j < c_end) store_result<DUAL>(p, f, m0 + c0 + j, a[j], b[j]);
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (threadIdx.x == 64 && atomicAdd(departed, 1) == p.splits - 1) {   // everybody has read: ready for the next launch
+            *arrived = 0;
+            *departed = 0;
+          }
+        }
+        sh->is_last = 0;
+      }
+      if (!p.spread && threadIdx.x == 64) {
         __threadfence();                 // cumulative: orders the whole block's partial sums before the count
         const int prev = atomicAdd(&p.counters[tile_id], 1);
         sh->is_last = (prev == p.splits - 1);
@@ -571,6 +630,8 @@ GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int ou
   p.stages = stages;
   p.total_kb = (K + GEMM_BK - 1) / GEMM_BK;
   const int tiles = m_tiles * n_tiles;
+  static int spread_on = -1;
+  if (spread_on < 0) { const char* ev = getenv("GLINT_GEMM_SPREAD"); spread_on = ev ? atoi(ev) : 1; }
   int splits = 1;
   if (force_splits > 0) {
     splits = force_splits;
@@ -580,9 +641,11 @@ GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int ou
     // workspace, which grows with the splits and the width of the token tile.
     const int width = bn * (dual ? 2 : 1);
     float best = 1e30f;
-    for (int cand = 1; cand <= 32 && tiles * cand <= 148 && cand <= p.total_kb; ++cand) {
+    for (int cand = 1; cand <= 32 && tiles * cand <= sms && cand <= p.total_kb; ++cand) {
       const int per = (p.total_kb + cand - 1) / cand;
-      const float est = 0.3f * per + (cand > 1 ? 1.5f + 0.04f * width * cand : 0.f);
+      // spread over the tile's blocks, the reduction costs the wait for the slowest block and one tile's worth of reads
+      const float reduce = spread_on ? 4.0f + 0.04f * width : 1.5f + 0.04f * width * cand;
+      const float est = 0.3f * per + (cand > 1 ? reduce : 0.f);
       if (est < best) {
         best = est;
         splits = cand;
@@ -599,6 +662,7 @@ GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int ou
     p.kb_per_split = p.total_kb;
   }
   p.splits = splits;
+  p.spread = (spread_on && splits > 1 && (long long)tiles * splits <= sms && tiles <= GEMM_SPREAD_DEPARTED) ? 1 : 0;
   p.dual_offset = dual_offset;
   p.act = act;
   p.cap = cap;

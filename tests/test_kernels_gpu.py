@@ -74,21 +74,45 @@ def test_gemm_skinny_refuses_what_it_cannot_do():
     assert (out - a.float() @ w.float().T).abs().max().item() < 0.05
 
 
+@pytest.mark.parametrize("features", [300, 7700])
 @pytest.mark.parametrize("splits", [1, 2, 3, 7])
-def test_gemm_split_k_is_deterministic_and_equal(splits):
+def test_gemm_split_k_is_deterministic_and_equal(splits, features):
+    """With few tiles every block of a tile adds up a share of its columns; with more tiles than the SMs
+    hold at once (7700 features in 3 or 7 splits) the last block to finish adds up all of them."""
     from glint_b200 import ops_tensor
     torch.manual_seed(0)
-    a = _bf16(torch.randn(9, 1544, device=DEV))
-    w = _bf16(torch.randn(300, 1544, device=DEV) * 0.1)
+    a = _bf16(torch.randn(41, 1544, device=DEV))
+    w = _bf16(torch.randn(features, 1544, device=DEV) * 0.1)
     want = a.float() @ w.float().T
     outs = []
     for _ in range(3):
-        out = torch.empty(9, 300, device=DEV)
-        ops_tensor.gemm(a, w, out, force_splits=splits)
+        out = torch.empty(41, features, device=DEV)
+        ops_tensor.gemm(a, w, out, force_splits=splits, path="tcgen05")
         outs.append(out)
     torch.cuda.synchronize()
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     assert (outs[0] - want).abs().max().item() <= 2e-3 * want.abs().max().item()
+    one = torch.empty(41, features, device=DEV)
+    ops_tensor.gemm(a, w, one, force_splits=1, path="tcgen05")
+    assert (outs[0] - one).abs().max().item() <= 1e-5 * want.abs().max().item()
+
+
+@pytest.mark.parametrize("features", [200, 5000])
+@pytest.mark.parametrize("splits", [2, 5])
+def test_gated_gemm_split_k(splits, features):
+    from glint_b200 import ops_tensor
+    torch.manual_seed(1)
+    a = _bf16(torch.randn(37, 776, device=DEV))
+    w = _bf16(torch.randn(2 * features, 776, device=DEV) * 0.05)
+    g, u = a.float() @ w[:features].float().T, a.float() @ w[features:].float().T
+    want = torch.nn.functional.gelu(g, approximate="tanh") * u
+    outs = []
+    for _ in range(2):
+        out = torch.empty(37, features, device=DEV, dtype=torch.bfloat16)
+        ops_tensor.gemm_gated(a, w, out, "gelu_tanh", force_splits=splits, path="tcgen05")
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    assert (outs[0].float() - want).abs().max().item() <= 0.01 * want.abs().max().item()
 
 
 def test_gemm_rows_do_not_depend_on_the_batch():
