@@ -25,7 +25,8 @@ namespace glint {
 
 constexpr int GEMM_BM = 128;      // weight rows (output features) per tile
 constexpr int GEMM_BK = 64;       // K elements per stage: 128 bytes, one swizzle atom
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 192;        // TMA warp, MMA warp, four epilogue warps
+constexpr int GEMM_THREADS_WIDE = 320;   // eight epilogue warps: two per quarter of the accumulator lanes, on alternate 16-column groups
 constexpr int GEMM_SPREAD_DEPARTED = 4096;   // second half of the counters: blocks that have finished reading
 constexpr int GEMM_MAX_STAGES = 8;
 constexpr int A_STAGE_BYTES = GEMM_BM * GEMM_BK * 2;
@@ -92,6 +93,9 @@ __device__ __forceinline__ void store_bf16_pairs(__nv_bfloat16* out, size_t N, i
   }
 }
 
+// barrier of the epilogue warps alone
+__device__ __forceinline__ void epi_sync(int threads) { asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory"); }
+
 template <bool DUAL>
 __device__ __forceinline__ void store_result(const GemmParams& p, int f, int t, float a, float b) {
   if (f >= p.N || t >= p.M) return;
@@ -109,7 +113,7 @@ __device__ __forceinline__ void store_result(const GemmParams& p, int f, int t, 
 }
 
 template <bool DUAL>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS_WIDE, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -232,15 +236,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       tc::mma_commit(&sh->tmem_full);    // the accumulator is complete
     }
   } else {
-    // ---- epilogue: 4 warps, each owns the 32 accumulator lanes of its quarter --------------------
+    // ---- epilogue: each warp owns the 32 accumulator lanes of its quarter; with eight warps two share
+    // a quarter and take alternate groups of 16 columns (one warp per scheduler leaves the tensor
+    // memory loads, the activation and the stores of a wide tile waiting on each other) -------------
     pdl_wait();
     const int q = warp & 3;
+    const int ep_threads = (int)blockDim.x - 64;
+    const int eg = (warp - 2) >> 2, c_first = eg * 16, c_step = ep_threads >> 3;   // 16 or 32 columns
     const int f = n0 + q * 32 + lane;              // this thread's output feature
     tc::mbar_wait(&sh->tmem_full, 0, abort_flag);
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    epi_sync(ep_threads);
     if (threadIdx.x == 64) sh->epilogue_ok = !*abort_flag;
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    const bool ok = sh->epilogue_ok != 0;   // one thread decides, so all 128 take the same branch
+    epi_sync(ep_threads);
+    const bool ok = sh->epilogue_ok != 0;   // one thread decides, so all take the same branch
     tc::fence_after_thread_sync();
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     const int tile_id = (int)blockIdx.x;
@@ -254,7 +262,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const bool capped = p.cap > 0.f;
       const float two_over_cap = capped ? 2.0f / p.cap : 0.f;
       const int fl = q * 32 + lane;
-      for (int c0 = 0; c0 < t_end; c0 += 16) {
+      for (int c0 = c_first; c0 < t_end; c0 += c_step) {
         uint32_t a[16], b[16];
         tc::tmem_ld_16(lane_addr + c0, a);
         if (DUAL) tc::tmem_ld_16(lane_addr + p.BN + c0, b);
@@ -290,7 +298,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
       }
       tc::fence_proxy_async();                     // the bulk copy reads shared memory through the async proxy
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      epi_sync(ep_threads);
       if (threadIdx.x == 64) tc::tma_store_2d_and_wait_read(smem, &map_out, n0, m0);
     } else if (ok && p.splits == 1) {
       // One row pointer per thread, advanced by a whole output row per token; the epilogue kind is
@@ -309,7 +317,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const bool f2_ok = f2 < p.N, f2_pair_ok = (f2 | 1) < p.N;
         const bool capped = p.cap > 0.f;
         const float two_over_cap = capped ? 2.0f / p.cap : 0.f;
-        for (int c0 = 0; c0 < t_end; c0 += 16) {
+        for (int c0 = c_first; c0 < t_end; c0 += c_step) {
           uint32_t a[16], b[16];
           tc::tmem_ld_16(lane_addr + c0, a);
           tc::tmem_ld_16(lane_addr + p.BN + c0, b);
@@ -348,7 +356,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
       } else if (DUAL) {
         __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m0 * p.N;
-        for (int c0 = 0; c0 < t_end; c0 += 16) {
+        for (int c0 = c_first; c0 < t_end; c0 += c_step) {
           uint32_t a[16], b[16];
           tc::tmem_ld_16(lane_addr + c0, a);
           tc::tmem_ld_16(lane_addr + p.BN + c0, b);
@@ -376,7 +384,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       } else if (p.out_bf16) {
         __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m0 * p.N;
         const bool capped = p.cap > 0.f;
-        for (int c0 = 0; c0 < t_end; c0 += 16) {
+        for (int c0 = c_first; c0 < t_end; c0 += c_step) {
           uint32_t a[16];
           tc::tmem_ld_16(lane_addr + c0, a);
           tc::tmem_ld_wait();
@@ -400,7 +408,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         float* o = reinterpret_cast<float*>(p.out) + (size_t)m0 * p.N + f;
         const bool capped = p.cap > 0.f;
         const float two_over_cap = capped ? 2.0f / p.cap : 0.f;
-        for (int c0 = 0; c0 < t_end; c0 += 16) {
+        for (int c0 = c_first; c0 < t_end; c0 += c_step) {
           uint32_t a[16];
           tc::tmem_ld_16(lane_addr + c0, a);
           tc::tmem_ld_wait();
@@ -421,14 +429,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     } else if (ok) {
       // partial sums of this split: workspace[tile][split][half][column][row]
       float* mine = p.workspace + ((size_t)(tile_id * p.splits + split) * halves) * p.BN * GEMM_BM;
-      for (int c0 = 0; c0 < p.BN * halves; c0 += 16) {
+      for (int c0 = c_first; c0 < p.BN * halves; c0 += c_step) {
         uint32_t a[16];
         tc::tmem_ld_16(lane_addr + c0, a);
         tc::tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 16; ++j) mine[(size_t)(c0 + j) * GEMM_BM + q * 32 + lane] = __uint_as_float(a[j]);
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      epi_sync(ep_threads);
       if (p.spread) {
         // Every block of the tile waits until all of them have written (they are all on an SM at the
         // same time: the host takes this path only for grids of at most one block per SM) and adds up
@@ -444,13 +452,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           sh->is_last = seen >= p.splits;
           __threadfence();
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        epi_sync(ep_threads);
         if (sh->is_last) {
           const float* base = p.workspace + ((size_t)tile_id * p.splits * halves) * p.BN * GEMM_BM;
           const size_t split_stride = (size_t)halves * p.BN * GEMM_BM;
           const int per = (p.BN + p.splits - 1) / p.splits;
           const int c_begin = split * per, c_end = min(p.BN, c_begin + per);
-          for (int c0 = c_begin; c0 < c_end; c0 += 4) {      // splits are added in order, four in flight
+          for (int c0 = c_begin + eg * 4; c0 < c_end; c0 += c_step >> 2) {      // splits are added in order, four in flight
             float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
             for (int s0 = 0; s0 < p.splits; s0 += 4) {
               float va[4][4], vb[DUAL ? 4 : 1][4];
@@ -478,7 +486,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             for (int j = 0; j < 4; ++j)
               if (c0 + j < c_end) store_result<DUAL>(p, f, m0 + c0 + j, a[j], b[j]);
           }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
+          epi_sync(ep_threads);
           if (threadIdx.x == 64 && atomicAdd(departed, 1) == p.splits - 1) {   // everybody has read: ready for the next launch
             *arrived = 0;
             *departed = 0;
@@ -491,13 +499,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int prev = atomicAdd(&p.counters[tile_id], 1);
         sh->is_last = (prev == p.splits - 1);
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      epi_sync(ep_threads);
       if (sh->is_last) {
         __threadfence();
         const float* base = p.workspace + ((size_t)tile_id * p.splits * halves) * p.BN * GEMM_BM;
         const size_t split_stride = (size_t)halves * p.BN * GEMM_BM;
         // 16 columns at a time; the loads of four splits are in flight together; splits are added in order
-        for (int c0 = 0; c0 < p.BN; c0 += 16) {
+        for (int c0 = c_first; c0 < p.BN; c0 += c_step) {
           float a[16], b[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) a[j] = b[j] = 0.f;
@@ -698,17 +706,20 @@ GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int ou
                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
       p.tma_store = 1;
   }
+  static int wide_epilogue = -1;
+  if (wide_epilogue < 0) { const char* ev = getenv("GLINT_GEMM_EPILOGUE_WARPS"); wide_epilogue = ev ? (atoi(ev) >= 8) : 1; }
+  const int threads = (wide_epilogue && bn * (dual ? 2 : 1) >= 64) ? GEMM_THREADS_WIDE : GEMM_THREADS;
   dim3 grid(n_tiles * m_tiles, 1, splits);
   cudaError_t e;
   if (dual) {
     e = cudaFuncSetAttribute(gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) return (int)e;
-    e = launch_kernel(gemm_tcgen05_kernel<true>, grid, dim3(GEMM_THREADS), smem_bytes, stream, map_w, map_x, map_out, p);
+    e = launch_kernel(gemm_tcgen05_kernel<true>, grid, dim3(threads), smem_bytes, stream, map_w, map_x, map_out, p);
     if (e != cudaSuccess) return (int)e;
   } else {
     e = cudaFuncSetAttribute(gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) return (int)e;
-    e = launch_kernel(gemm_tcgen05_kernel<false>, grid, dim3(GEMM_THREADS), smem_bytes, stream, map_w, map_x, map_out, p);
+    e = launch_kernel(gemm_tcgen05_kernel<false>, grid, dim3(threads), smem_bytes, stream, map_w, map_x, map_out, p);
     if (e != cudaSuccess) return (int)e;
   }
   return (int)cudaGetLastError();
