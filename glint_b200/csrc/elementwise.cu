@@ -280,6 +280,22 @@ add_rmsnorm_fast_kernel(float* __restrict__ x, const float* __restrict__ y, cons
   }
 }
 
+// (cos, sin) of every token's rotation angles, [token][hd / 2]: the same expression as in the
+// kernels that compute them in place, once per step for the epilogue of the q/k/v product.
+__global__ void __launch_bounds__(128)
+rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, float factor,
+                  float2* __restrict__ out, int half) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float ps = (float)positions[t] / factor;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    float s, c;
+    sincosf(ps * inv_freq[j], &s, &c);
+    out[(size_t)t * half + j] = make_float2(c, s);
+  }
+}
+
 // Rotary encoding, fast form: the sines and cosines of the token's position are computed once
 // per block into shared memory, then every head reads them.  Same arithmetic as the plain form.
 template <typename S>
@@ -503,6 +519,15 @@ GLINT_API int glint_add_rmsnorm(float* x, const float* y, const float* w_a, floa
                                                                       eps_b, offset_b, H));
   }
 #undef ADD_FAST
+  return rc ? rc : (int)cudaGetLastError();
+}
+
+GLINT_API int glint_rope_table(const int* positions, const float* inv_freq, float factor, float* out, int T,
+                               int half, cudaStream_t stream) {
+  if (T <= 0 || half <= 0) return GLINT_OK;
+  if (factor <= 0.f) return GLINT_ERR_BAD_ARG;
+  const int rc = (int)launch_kernel(rope_table_kernel, dim3(T), dim3(half < 128 ? 64 : 128), 0, stream, positions,
+                                    inv_freq, factor, reinterpret_cast<float2*>(out), half);
   return rc ? rc : (int)cudaGetLastError();
 }
 

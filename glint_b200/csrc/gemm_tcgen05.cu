@@ -31,7 +31,24 @@ constexpr int GEMM_SPREAD_DEPARTED = 4096;   // second half of the counters: blo
 constexpr int GEMM_MAX_STAGES = 8;
 constexpr int A_STAGE_BYTES = GEMM_BM * GEMM_BK * 2;
 
+// The q/k/v product of a prompt portion with the rotary encoding and the cache write as its epilogue:
+// the dual kernel's two weight tiles are rows j and j + hd/2 of one head, so that a thread holds
+// both members of a rotation pair (hd a multiple of 256).
+struct RopeEpilogue {
+  int on;
+  const float2* trig;        // [tokens][hd / 2] (cos, sin) of every token's angles
+  const int* positions;      // [tokens]
+  const int* token_seq;      // [tokens] row of the block table
+  const int* block_table;    // [requests][max_pages]
+  int max_pages;
+  void* k_pool;              // [pages][nkv][page_size][hd] bf16; null: only q is computed
+  void* v_pool;
+  int nh, nkv, hd, page_size, num_pages;
+  int bn;                    // largest token tile (host side)
+};
+
 struct GemmParams {
+  RopeEpilogue rope;
   int M, N, K;          // tokens, output features, reduction length
   int BN;               // tokens per tile
   int m_tiles;          // token tiles (the fast index of blockIdx.x)
@@ -129,7 +146,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   // tiles (feature tiles first re-read the weights once per token tile: 346 MB instead of 94 MB for
   // the gate/up product of a 2048-token portion).
   const int m_tile = (int)blockIdx.x % p.m_tiles, n_tile = (int)blockIdx.x / p.m_tiles;
-  const int n0 = n_tile * (p.wide ? 2 * GEMM_BM : GEMM_BM);
+  const int rope_subs = (DUAL && p.rope.on) ? p.rope.hd / (2 * GEMM_BM) : 1;   // 128-pair groups per head
+  const int n0 = (DUAL && p.rope.on) ? (n_tile / rope_subs) * p.rope.hd + (n_tile % rope_subs) * GEMM_BM
+                                     : n_tile * (p.wide ? 2 * GEMM_BM : GEMM_BM);
   const int m0 = m_tile * p.BN;
   const int split = blockIdx.z;
   const int kb_begin = split * p.kb_per_split;
@@ -253,7 +272,71 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     const int tile_id = (int)blockIdx.x;
     const int halves = DUAL ? 2 : 1;
-    if (ok && p.splits == 1 && p.tma_store) {
+    if (DUAL && ok && p.rope.on) {
+      // q and k heads: (lo, hi) -> (lo cos - hi sin, lo sin + hi cos) with the token's angles from the
+      // table; v heads pass.  The tile is staged as [token][lo 128 | hi 128] bfloat16 and then copied
+      // row by row, 16 bytes per lane, to q_out or to each token's place in its page.
+      const RopeEpilogue& r = p.rope;
+      const int half = r.hd >> 1;
+      const int head = n_tile / rope_subs, sub = n_tile % rope_subs;
+      const bool rotate = head < r.nh + r.nkv;
+      const int fl = q * 32 + lane;
+      const int jt = sub * GEMM_BM + fl;                 // this thread's pair within the head
+      const int t_end = min(p.BN, p.M - m0);
+      __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(smem);
+      for (int c0 = c_first; c0 < t_end; c0 += c_step) {
+        uint32_t a[16], b[16];
+        tc::tmem_ld_16(lane_addr + c0, a);
+        tc::tmem_ld_16(lane_addr + p.BN + c0, b);
+        float2 cs[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int t = min(m0 + c0 + j, p.M - 1);
+          cs[j] = rotate ? __ldg(r.trig + (size_t)t * half + jt) : make_float2(1.f, 0.f);
+        }
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float lo = __uint_as_float(a[j]), hi = __uint_as_float(b[j]);
+          __nv_bfloat16* row = stage + (size_t)(c0 + j) * (2 * GEMM_BM);
+          row[fl] = __float2bfloat16_rn(rotate ? lo * cs[j].x - hi * cs[j].y : lo);
+          row[GEMM_BM + fl] = __float2bfloat16_rn(rotate ? lo * cs[j].y + hi * cs[j].x : hi);
+        }
+      }
+      epi_sync(ep_threads);
+      const int wi = warp - 2, n_w = ep_threads >> 5;
+      __nv_bfloat16* dst_base;
+      if (head < r.nh) dst_base = reinterpret_cast<__nv_bfloat16*>(p.out);
+      else if (head < r.nh + r.nkv) dst_base = reinterpret_cast<__nv_bfloat16*>(r.k_pool);
+      else dst_base = reinterpret_cast<__nv_bfloat16*>(r.v_pool);
+      const int kvh = head < r.nh ? 0 : (head - r.nh) % r.nkv;
+      // a lane's 16 bytes: lanes 0-15 the lo half, lanes 16-31 the hi half of the staged row
+      const int seg = (lane < 16 ? 0 : half) + sub * GEMM_BM + (lane & 15) * 8;
+      for (int base = 0; base < t_end; base += 32 * n_w) {
+        const int tl = base + lane * n_w + wi;           // this lane looks up one token's destination row
+        long long dst = -1;
+        if (tl < t_end) {
+          const int t = m0 + tl;
+          if (head < r.nh) {
+            dst = ((long long)t * r.nh + head) * r.hd;
+          } else {
+            const int pos = r.positions[t];
+            const int page = r.block_table[(size_t)r.token_seq[t] * r.max_pages + pos / r.page_size];
+            if (page < 0 || page >= r.num_pages) atomicExch(p.status, 2);
+            else dst = (((long long)page * r.nkv + kvh) * r.page_size + pos % r.page_size) * r.hd;
+          }
+        }
+        for (int l = 0; l < 32; ++l) {
+          const int tl2 = base + l * n_w + wi;
+          if (tl2 >= t_end) break;
+          const long long d = __shfl_sync(0xffffffffu, dst, l);
+          if (d >= 0) {
+            const uint4 v = *reinterpret_cast<const uint4*>(stage + (size_t)tl2 * (2 * GEMM_BM) + lane * 8);
+            *reinterpret_cast<uint4*>(dst_base + d + seg) = v;
+          }
+        }
+      }
+    } else if (ok && p.splits == 1 && p.tma_store) {
       // Wide token tiles: the tile is staged in the stage ring (free now: every MMA has completed) as
       // [token][128 features], 32 consecutive features per warp store, and leaves with one bulk tensor
       // store, which clips it at the edges of the output.  256 shared-memory stores per thread instead
@@ -591,26 +674,26 @@ GLINT_API int glint_gemm_tcgen05_supported(long long M, long long N, long long K
 GLINT_API long long glint_gemm_workspace_bytes() { return 16ll << 20; }
 GLINT_API int glint_gemm_counter_count() { return 8192; }
 
-// x: [M, K] bf16; w: [N (or 2N rows when dual), K] bf16; out: [M, N] float32 or bf16.
-// dual != 0: out = act(x w[0:N]^T) * (x w[dual_offset : dual_offset+N]^T), written as bf16.
-// workspace: glint_gemm_workspace_bytes() bytes; counters: glint_gemm_counter_count() zeroed ints.
-GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int out_bf16, int M, int N, int K,
-                                 long long w_rows, float cap, int dual, int dual_offset, int act,
-                                 float* workspace, int* counters, int* status, int force_splits,
-                                 cudaStream_t stream) {
+// The launch behind both entry points; ``rope`` selects the rotary epilogue of the dual kernel.
+static int gemm_launch(const void* x, const void* w, void* out, int out_bf16, int M, int N, int K,
+                       long long w_rows, float cap, int dual, int dual_offset, int act, float* workspace,
+                       int* counters, int* status, int force_splits, const RopeEpilogue* rope, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return GLINT_OK;
   if (!glint_gemm_tcgen05_supported(M, N, K)) return GLINT_ERR_UNSUPPORTED_SIZE;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return GLINT_ERR_UNSUPPORTED_SIZE;
   GemmParams p;
+  if (rope) p.rope = *rope;
+  else p.rope = RopeEpilogue{};
   p.M = M; p.N = N; p.K = K;
   int bn_max = 256;
-  if (const char* ov = getenv("GLINT_GEMM_BN")) { const int v = atoi(ov); if (v >= 16 && v <= 256 && v % 16 == 0) bn_max = v; }
+  if (rope) bn_max = rope->bn;
+  else if (const char* ov = getenv("GLINT_GEMM_BN")) { const int v = atoi(ov); if (v >= 16 && v <= 256 && v % 16 == 0) bn_max = v; }
   const int m_tiles_256 = (M + bn_max - 1) / bn_max;
   int bn = ((M + m_tiles_256 - 1) / m_tiles_256 + 15) / 16 * 16;
   if (dual && bn > 256) bn = 256;
   p.BN = bn;
   const int m_tiles = (M + bn - 1) / bn;
-  int n_tiles = (N + GEMM_BM - 1) / GEMM_BM;
+  int n_tiles = rope ? N / (2 * GEMM_BM) : (N + GEMM_BM - 1) / GEMM_BM;
   // A plain product whose 128-feature tiles would need more than one wave, and whose 256-feature
   // tiles still fill three quarters of the SMs, runs as the dual kernel with two plain tiles.
   static int sms = 0, wide_on = -1;
@@ -623,7 +706,7 @@ GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int ou
   if (wide_on < 0) { const char* ev = getenv("GLINT_GEMM_WIDE"); wide_on = ev ? atoi(ev) : 1; }
   const int n_tiles_wide = (N + 2 * GEMM_BM - 1) / (2 * GEMM_BM);
   p.wide = 0;
-  if (wide_on && !dual && force_splits <= 1 && bn == 256 && (long long)n_tiles * m_tiles > sms &&
+  if (wide_on && !dual && !rope && force_splits <= 1 && bn == 256 && (long long)n_tiles * m_tiles > sms &&
       (long long)n_tiles_wide * m_tiles * 4 >= 3LL * sms) {
     p.wide = 1;
     dual = 1;
@@ -694,7 +777,7 @@ GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int ou
   p.tma_store = 0;
   static int tma_store_on = -1;
   if (tma_store_on < 0) { const char* ev = getenv("GLINT_GEMM_TMA_STORE"); tma_store_on = ev ? atoi(ev) : 1; }
-  if (tma_store_on && !p.wide && out_bf16 && splits == 1 && bn >= 64 && ((long long)N * es) % 16 == 0 && ((uintptr_t)out & 15) == 0 &&
+  if (tma_store_on && !p.wide && !rope && out_bf16 && splits == 1 && bn >= 64 && ((long long)N * es) % 16 == 0 && ((uintptr_t)out & 15) == 0 &&
       (long long)bn * GEMM_BM * es <= (long long)stages * stage_bytes) {
     EncodeTiledFn fn = encode_fn();
     cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
@@ -723,4 +806,54 @@ GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int ou
     if (e != cudaSuccess) return (int)e;
   }
   return (int)cudaGetLastError();
+}
+
+// x: [M, K] bf16; w: [N (or 2N rows when dual), K] bf16; out: [M, N] float32 or bf16.
+// dual != 0: out = act(x w[0:N]^T) * (x w[dual_offset : dual_offset+N]^T), written as bf16.
+// workspace: glint_gemm_workspace_bytes() bytes; counters: glint_gemm_counter_count() zeroed ints.
+GLINT_API int glint_gemm_tcgen05(const void* x, const void* w, void* out, int out_bf16, int M, int N, int K,
+                                 long long w_rows, float cap, int dual, int dual_offset, int act,
+                                 float* workspace, int* counters, int* status, int force_splits,
+                                 cudaStream_t stream) {
+  return gemm_launch(x, w, out, out_bf16, M, N, K, w_rows, cap, dual, dual_offset, act, workspace, counters, status,
+                     force_splits, nullptr, stream);
+}
+
+// Head sizes the rotary epilogue takes: a thread of the dual kernel holds features j and j + 128 g.
+// The grid is heads x token tiles with no split of K, so it also wants enough tokens to fill half of the
+// SMs with tiles of 256 or of 128 tokens (``min_blocks`` 0: any number of tokens).
+static int rope_token_tile(long long M, int head_tiles, int min_blocks) {
+  for (int bn = 256; bn >= 128; bn >>= 1)
+    if (head_tiles * ((M + bn - 1) / bn) >= min_blocks) return bn;
+  return 0;
+}
+
+GLINT_API int glint_gemm_tcgen05_rope_supported(long long M, long long K, int hd, int heads, int min_blocks) {
+  if (!(M > 0 && K > 0 && K % 8 == 0 && hd >= 256 && hd % 256 == 0 && heads > 0)) return 0;
+  return rope_token_tile(M, heads * (hd / 256), min_blocks) ? 1 : 0;
+}
+
+// q, k, v = x w^T for w: [(nh + 2 nkv) hd, K] with the rotation by the angles of ``trig`` ([M][hd/2]
+// (cos, sin)) and the cache write in the epilogue: q to q_out [M, nh hd] bf16, k and v into the pages
+// named by block_table at each token's position (k_pool null: only q is computed).
+GLINT_API int glint_gemm_tcgen05_rope(const void* x, const void* w, int M, int K, const float* trig,
+                                      const int* positions, const int* token_seq, const int* block_table,
+                                      int max_pages, void* q_out, void* k_pool, void* v_pool, int nh, int nkv,
+                                      int hd, int page_size, int num_pages, int min_blocks, int* status,
+                                      cudaStream_t stream) {
+  if (M <= 0) return GLINT_OK;
+  if (nh <= 0 || nkv <= 0 || page_size <= 0 || !glint_gemm_tcgen05_rope_supported(M, K, hd, nh, 0)) return GLINT_ERR_UNSUPPORTED_SIZE;
+  if (!trig || !status || !q_out || (k_pool && !v_pool)) return GLINT_ERR_BAD_ARG;
+  if (((uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)trig) & 15) return GLINT_ERR_UNSUPPORTED_SIZE;
+  RopeEpilogue r;
+  r.on = 1;
+  r.trig = reinterpret_cast<const float2*>(trig);
+  r.positions = positions; r.token_seq = token_seq; r.block_table = block_table; r.max_pages = max_pages;
+  r.k_pool = k_pool; r.v_pool = v_pool;
+  r.nh = nh; r.nkv = nkv; r.hd = hd; r.page_size = page_size; r.num_pages = num_pages;
+  const long long rows = (long long)(nh + 2 * nkv) * hd;
+  const int heads = k_pool ? nh + 2 * nkv : nh;
+  r.bn = rope_token_tile(M, heads * (hd / 256), min_blocks);
+  if (r.bn == 0) r.bn = 128;
+  return gemm_launch(x, w, q_out, 1, M, heads * hd, K, rows, 0.f, 1, hd / 2, 0, nullptr, nullptr, status, 1, &r, stream);
 }

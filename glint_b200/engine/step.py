@@ -39,11 +39,14 @@ class StepContext:
     token's request within this step, which is also its row in every block table.
     ``seq_slot``, ``seq_start`` (tokens cached before the step), ``cu_seqlens`` (token offsets,
     one more than requests) are per request; ``logit_rows`` are the token rows whose logits are
-    wanted.  The ``h_`` fields are host copies for planning launches.
+    wanted.  The ``h_`` fields are host copies for planning launches.  ``memo`` is empty at the start of
+    a step: parts keep there what several layers of the step share (a table of rotation angles, say),
+    under a key of their own parameters.
     """
 
     def __init__(self, cache, entries, meta_dev, staging, extra=()):
         n = len(entries)
+        self.memo = {}
         lens = [len(e.tokens) for e in entries]
         T = sum(lens)
         self.num_tokens, self.num_seqs = T, n

@@ -47,6 +47,7 @@ _CORE_SIGNATURES = {
     "glint_embed_scale": [_P, _I, _P, _P, _I, _I, _F, _I, _P, _P],
     "glint_rmsnorm": [_P, _P, _P, _P, _I, _I, _I, _F, _F, _P],
     "glint_add_rmsnorm": [_P, _P, _P, _F, _F, _P, _I, _P, _F, _F, _I, _I, _P],
+    "glint_rope_table": [_P, _P, _F, _P, _I, _I, _P],
     "glint_rope_kv_write": [_P, _P, _P, _P, _I, _P, _F, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "glint_gated_act": [_P, _P, _I, _I, _I, _I, _P],
     "glint_softcap": [_P, _L, _F, _P],
@@ -147,6 +148,16 @@ def rope_kv_write(qkv, positions, token_slot, block_table, inv_freq, factor, rot
                                      block_table.shape[1], ptr(inv_freq), factor, rot, ptr(q_out), ptr(k_pool),
                                      ptr(v_pool), dtype_code(q_out.dtype), T, nh, nkv, hd, page_size, num_pages,
                                      ptr(status), stream()), "rope_kv_write")
+
+
+def rope_table(positions, inv_freq, factor, out):
+    """out[t, j] = (cos, sin) of (positions[t] / factor) * inv_freq[j]; out float32 [T, half, 2]."""
+    T, half = out.shape[0], inv_freq.numel()
+    require(positions, torch.int32, "positions"); require(inv_freq, torch.float32, "inv_freq")
+    require(out, torch.float32, "out")
+    if tuple(out.shape) != (positions.shape[0], half, 2):
+        raise KernelError(f"rope_table: out {tuple(out.shape)} does not fit {positions.shape[0]} tokens x {half} pairs")
+    check(core().glint_rope_table(ptr(positions), ptr(inv_freq), factor, ptr(out), T, half, stream()), "rope_table")
 
 
 def gated_act(gu, out, activation):

@@ -14,6 +14,7 @@ _P, _I, _F, _L = c_void_p, c_int, c_float, c_longlong
 _SIGNATURES = {
     "glint_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _L, _F, _I, _I, _I, _P, _P, _P, _I, _P],
     "glint_gemm_skinny": [_P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "glint_gemm_tcgen05_rope": [_P, _P, _I, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "glint_gemm_skinny_rope": [_P, _P, _I, _I, _P, _P, _P, _I, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "glint_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P],
     "glint_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
@@ -116,6 +117,41 @@ def qkv_rope(a, w_qkv, positions, token_slot, block_table, inv_freq, factor, q_o
                                            ops.ptr(block_table), block_table.shape[1], ops.ptr(inv_freq), factor,
                                            ops.ptr(q_out), ops.ptr(k_pool), ops.ptr(v_pool), nh, nkv, hd, page_size,
                                            num_pages, ops.ptr(status), ops.stream()), "gemm_skinny_rope")
+
+
+ROPE_TILED_MIN_BLOCKS = int(os.environ.get("GLINT_ROPE_TILED_MIN_BLOCKS", "74"))
+
+
+def qkv_rope_tiled_supported(M, K, hd, rotary_dim, heads, min_blocks=None):
+    """The tiled q/k/v product with the rotary epilogue: head sizes in steps of 256 (a thread holds
+    features j and j + hd/2 of a head), whole-head rotation, K in steps of 8, and, as its grid is heads x
+    token tiles with K unsplit, enough tokens for ``min_blocks`` blocks (default: half of a B200's SMs)."""
+    if not (FUSED_ROPE and M >= 1 and K % 8 == 0 and hd >= 256 and hd % 256 == 0 and rotary_dim == hd):
+        return False
+    mb = ROPE_TILED_MIN_BLOCKS if min_blocks is None else min_blocks
+    head_tiles = heads * (hd // 256)
+    return head_tiles * -(-M // 128) >= mb          # the kernel takes tiles of 256 tokens if they suffice, else of 128
+
+
+def qkv_rope_tiled(a, w_qkv, trig, positions, token_seq, block_table, q_out, k_pool, v_pool, nh, nkv, hd, page_size,
+                   num_pages, status, min_blocks=None):
+    """As ``qkv_rope`` for any number of tokens on the tiled kernel; ``trig`` [M, hd/2, 2] float32 holds
+    (cos, sin) of every token's angles (``ops.rope_table``)."""
+    M, K = a.shape
+    ops.require(a, torch.bfloat16, "a"); ops.require(w_qkv, torch.bfloat16, "w_qkv")
+    ops.require(q_out, torch.bfloat16, "q_out"); ops.require(k_pool, torch.bfloat16, "k_pool")
+    ops.require(v_pool, torch.bfloat16, "v_pool"); ops.require(trig, torch.float32, "trig")
+    ops.require(positions, torch.int32, "positions"); ops.require(token_seq, torch.int32, "token_seq")
+    ops.require(block_table, torch.int32, "block_table")
+    if (w_qkv.shape != ((nh + 2 * nkv) * hd, K) or tuple(q_out.shape) != (M, nh * hd)
+            or tuple(trig.shape) != (M, hd // 2, 2)):
+        raise KernelError(f"qkv_rope_tiled shapes do not fit: a {tuple(a.shape)}, w {tuple(w_qkv.shape)}, "
+                          f"q_out {tuple(q_out.shape)}, trig {tuple(trig.shape)}, heads {nh}/{nkv} x {hd}")
+    ops.check(lib().glint_gemm_tcgen05_rope(ops.ptr(a), ops.ptr(w_qkv), M, K, ops.ptr(trig), ops.ptr(positions),
+                                            ops.ptr(token_seq), ops.ptr(block_table), block_table.shape[1],
+                                            ops.ptr(q_out), ops.ptr(k_pool), ops.ptr(v_pool), nh, nkv, hd, page_size,
+                                            num_pages, ROPE_TILED_MIN_BLOCKS if min_blocks is None else min_blocks,
+                                            ops.ptr(status), ops.stream()), "gemm_tcgen05_rope")
 
 
 def gemm_gated(a, w_gate_up, out, activation, status=None, force_splits=0, path=None):

@@ -37,21 +37,39 @@ class Rotary(Part):
                           view.v if writes else None, nh, nkv, hd, view.page_size, view.num_pages,
                           self.rt.status)
 
+    def angles(self, ctx):
+        """(cos, sin) of every token's angles, float32 [tokens, rotary_dim / 2, 2]; computed by the first
+        layer of a step that asks and shared through ``ctx.memo`` by all layers with these parameters."""
+        key = ("rope_table", self.theta, self.factor, self.rotary_dim, self.head_dim)
+        table = ctx.memo.get(key)
+        if table is None:
+            table = torch.empty((ctx.num_tokens, self.rotary_dim // 2, 2), dtype=torch.float32, device=self.rt.device)
+            ops.rope_table(ctx.positions, self.inv_freq, self.factor, table)
+            ctx.memo[key] = table
+        return table
+
     def project_encode_store(self, x, w_qkv, ctx, q_out, view, nh, nkv, hd):
         """The q/k/v product, the rotation and the cache write as one kernel, where there is one for
-        these sizes (a few single tokens in bfloat16); returns False when the caller has to run the
-        product and ``encode_and_store`` itself."""
+        these sizes in bfloat16 (the weight-streaming kernel for a few single tokens, the tiled kernel
+        for heads in steps of 256); returns False when the caller has to run the product and
+        ``encode_and_store`` itself."""
         rt = self.rt
         if not (rt.tensor_cores and w_qkv.dtype == torch.bfloat16 and x.dtype == torch.bfloat16):
             return False
         from .. import ops_tensor
-        if not ops_tensor.qkv_rope_supported(x.shape[0], x.shape[1], hd, self.rotary_dim):
-            return False
         writes = view.writes
-        ops_tensor.qkv_rope(x, w_qkv, ctx.positions, ctx.token_seq, ctx.block_table(view.group), self.inv_freq,
-                            self.factor, q_out, view.k if writes else None, view.v if writes else None, nh, nkv, hd,
-                            view.page_size, view.num_pages, rt.status)
-        return True
+        k, v = (view.k, view.v) if writes else (None, None)
+        table = ctx.block_table(view.group)
+        if ops_tensor.qkv_rope_supported(x.shape[0], x.shape[1], hd, self.rotary_dim):
+            ops_tensor.qkv_rope(x, w_qkv, ctx.positions, ctx.token_seq, table, self.inv_freq, self.factor, q_out,
+                                k, v, nh, nkv, hd, view.page_size, view.num_pages, rt.status)
+            return True
+        if ops_tensor.qkv_rope_tiled_supported(x.shape[0], x.shape[1], hd, self.rotary_dim,
+                                               nh + 2 * nkv if writes else nh):
+            ops_tensor.qkv_rope_tiled(x, w_qkv, self.angles(ctx), ctx.positions, ctx.token_seq, table, q_out, k, v,
+                                      nh, nkv, hd, view.page_size, view.num_pages, rt.status)
+            return True
+        return False
 
 
 register_part("position", "rope", Rotary)

@@ -236,6 +236,68 @@ def test_qkv_product_with_rotation_and_cache_write_in_one_kernel(M, K, nh, nkv, 
         assert (k_pool == 7.0).all() and (v_pool == -3.0).all()
 
 
+@pytest.mark.parametrize("lens,starts,K,nh,nkv,hd,page,writes", [
+    ([300, 41, 2], [0, 77, 1000], 136, 3, 1, 256, 16, True),       # three requests, 343 tokens: two token tiles
+    ([5], [3], 64, 2, 2, 512, 32, True),                            # two groups of 128 pairs per head
+    ([600], [4090], 2304, 8, 4, 256, 16, True),
+    ([70, 9], [0, 5], 200, 1, 1, 256, 16, False)])
+def test_tiled_qkv_product_with_rotation_and_cache_write(lens, starts, K, nh, nkv, hd, page, writes):
+    """The same on the tiled kernel for portions of prompts: the angles come from a table made by
+    ``rope_table``; tokens of one request share its row of the block table."""
+    from glint_b200 import ops, ops_tensor
+    torch.manual_seed(sum(lens) + hd)
+    M = sum(lens)
+    x = _bf16(torch.randn(M, K, device=DEV))
+    w = _bf16(torch.randn((nh + 2 * nkv) * hd, K, device=DEV) * 0.05)
+    positions = [s + i for n, s in zip(lens, starts) for i in range(n)]
+    seq = [r for r, n in enumerate(lens) for _ in range(n)]
+    max_pages = max(positions) // page + 1
+    n_pages = len(lens) * max_pages + 2
+    perm = torch.randperm(n_pages)[:len(lens) * max_pages].reshape(len(lens), max_pages).to(torch.int32).to(DEV)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))).to(DEV)
+    factor = 1.0 if hd == 256 else 4.0
+    k_pool = torch.full((n_pages, nkv, page, hd), 7.0, device=DEV, dtype=torch.bfloat16)
+    v_pool = torch.full((n_pages, nkv, page, hd), -3.0, device=DEV, dtype=torch.bfloat16)
+    q = torch.full((M, nh * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    trig = torch.empty(M, hd // 2, 2, device=DEV)
+    ops.rope_table(i32(positions), inv_freq, factor, trig)
+    pos = torch.tensor(positions, dtype=torch.float32)
+    ang = (pos[:, None] / factor) * inv_freq.cpu()[None, :]          # [M, hd/2]
+    assert (trig[..., 0].cpu() - torch.cos(ang)).abs().max().item() < 1e-3     # float32 angles up to 4000 rad
+    assert (trig[..., 1].cpu() - torch.sin(ang)).abs().max().item() < 1e-3
+    assert ops_tensor.qkv_rope_tiled_supported(M, K, hd, hd, nh + 2 * nkv, min_blocks=0)
+    assert not ops_tensor.qkv_rope_tiled_supported(M, K, hd, hd, nh + 2 * nkv, min_blocks=10 ** 6)
+    ops_tensor.qkv_rope_tiled(x, w, trig, i32(positions), i32(seq), perm, q, k_pool if writes else None,
+                              v_pool if writes else None, nh, nkv, hd, page, n_pages, status, min_blocks=0)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    qkv = (x.float() @ w.float().T).cpu()
+    cos, sin = trig[..., 0].cpu()[:, None, :], trig[..., 1].cpu()[:, None, :]
+
+    def turn(heads):                                                 # [M, n, hd]
+        lo, hi = heads[..., :hd // 2], heads[..., hd // 2:]
+        return torch.cat([lo * cos - hi * sin, lo * sin + hi * cos], dim=-1)
+
+    want_q = turn(qkv[:, :nh * hd].reshape(M, nh, hd))
+    tol = 1e-2 * max(1.0, qkv.abs().max().item())
+    assert (q.float().cpu().reshape(M, nh, hd) - want_q).abs().max().item() <= tol
+    if writes:
+        want_k = turn(qkv[:, nh * hd:(nh + nkv) * hd].reshape(M, nkv, hd))
+        want_v = qkv[:, (nh + nkv) * hd:].reshape(M, nkv, hd)
+        kc, vc = k_pool.float().cpu(), v_pool.float().cpu()
+        rows = torch.tensor([int(perm[r, p_ // page]) for r, p_ in zip(seq, positions)])
+        slots = torch.tensor([p_ % page for p_ in positions])
+        assert (kc[rows, :, slots] - want_k).abs().max().item() <= tol
+        assert (vc[rows, :, slots] - want_v).abs().max().item() <= tol
+        touched = torch.zeros(n_pages, page, dtype=torch.bool)
+        touched[rows, slots] = True
+        assert (kc.permute(0, 2, 1, 3)[~touched] == 7.0).all() and (vc.permute(0, 2, 1, 3)[~touched] == -3.0).all()
+    else:
+        assert (k_pool == 7.0).all() and (v_pool == -3.0).all()
+
+
 # ---- attention over a paged cache -----------------------------------------------------------------
 
 def _paged_case(seq_lens_before, seq_lens_new, nkv, hd, page_size, dtype, seed, hot=None, v_poison=float("nan")):
