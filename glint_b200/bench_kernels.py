@@ -126,6 +126,30 @@ def bench_rows(rows, H=2304, iters=20):
     return res
 
 
+def prefill_step(tokens, layers, iters):
+    """One prompt portion through an engine of the Gemma-2-2B layer sizes with ``layers`` layers.  The
+    last step runs between cudaProfilerStart and cudaProfilerStop, so that a profiler started with
+    ``--profile-from-start off`` lists the launches of exactly one step."""
+    from . import bench as B
+    from .config import config_from_dict
+    from .engine.api import LLM
+    cfg = {"architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2", "num_hidden_layers": layers,
+           "hidden_size": 2304, "num_attention_heads": 8, "num_key_value_heads": 4, "head_dim": 256,
+           "intermediate_size": 9216, "vocab_size": 256000, "rope_theta": 10000.0, "sliding_window": 4096,
+           "attn_logit_softcapping": 50.0, "final_logit_softcapping": 30.0, "query_pre_attn_scalar": 256,
+           "rms_norm_eps": 1e-6, "max_position_embeddings": 8192, "tie_word_embeddings": True,
+           "hidden_activation": "gelu_pytorch_tanh"}
+    llm = LLM.from_config(config_from_dict(cfg), seed=2, std=0.02, norm_std=0.02, dtype="bfloat16",
+                          cache_tokens=2 * tokens + 256, max_active=2, max_step_tokens=max(tokens, 16))
+    ms = B.time_prefill(llm.engine, tokens, iters=iters, warmup=3, seed=30)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    B.time_prefill(llm.engine, tokens, iters=1, warmup=0, seed=31)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    return {"kernel": "prefill step", "tokens": tokens, "layers": layers, "ms": round(ms, 4)}
+
+
 def gemma2_2b_decode_cases(batch):
     H, I, V, QKV, Q = 2304, 9216, 256000, 4096, 2048
     return [("qkv", batch, QKV, H, False), ("o", batch, H, Q, False), ("gate_up", batch, I, H, True),
@@ -135,7 +159,7 @@ def gemma2_2b_decode_cases(batch):
 def main():
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("what", choices=["gemm", "gated", "decode-shapes", "prefill-shapes", "attention-decode",
-                                     "attention-prefill", "rows"])
+                                     "attention-prefill", "rows", "prefill-step"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=2304)
@@ -146,6 +170,7 @@ def main():
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--page", type=int, default=16)
+    ap.add_argument("--layers", type=int, default=2, help="prefill-step: layers of the engine")
     ap.add_argument("--resident", action="store_true", help="products: reuse one set of weights (they stay in L2)")
     ap.add_argument("--path", choices=["tcgen05", "skinny"], default=None,
                     help="which product kernel (default: the one the engine would take)")
@@ -173,6 +198,8 @@ def main():
         out.append(bench_attention_prefill(a.tokens, page=a.page, window=a.window or None, iters=a.iters))
     elif a.what == "rows":
         out.extend(bench_rows(a.batch))
+    elif a.what == "prefill-step":
+        out.append(prefill_step(a.tokens, a.layers, a.iters))
     for row in out:
         print(json.dumps(row))
 
