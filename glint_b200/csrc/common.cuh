@@ -69,6 +69,22 @@ __device__ __forceinline__ float gelu_tanh(float v) {
 }
 
 
+// ---- thread-block cluster -----------------------------------------------------------------------
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the address, in the cluster's shared window, of this block's shared address `addr` in block `rank`
+__device__ __forceinline__ uint32_t cluster_map(uint32_t addr, int rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float cluster_load(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+
 // ---- programmatic dependent launch ------------------------------------------------------------
 // A kernel launched with launch_kernel() may begin while its predecessor on the stream is still
 // finishing: everything up to pdl_wait() (set-up, loads of weights, which no kernel writes)

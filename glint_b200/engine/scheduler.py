@@ -27,7 +27,7 @@ from dataclasses import dataclass, field
 from typing import Optional
 
 from ..errors import RequestError
-from ..sampling import SamplingParams, Xorshift64
+from ..sampling import SamplingParams, TokenCounts, Xorshift64
 from .step import StepEntry
 
 FINISH_STOP = "stop"        # sampled the EOS token
@@ -51,11 +51,18 @@ class Request:
     order: int = 0
     unresolved: int = 0          # 1 while the newest token is still only on the device
     pending_index: int = 0       # its place among the tokens sampled by that step
+    counts: Optional[TokenCounts] = None   # token counts for the repeat penalty, made at first use
     draining: bool = False       # reached its budget by count; finishes when its last token arrives
 
     @property
     def tokens(self):
         return self.prompt + self.output
+
+    def token_counts(self):
+        """Counts of the tokens so far for the repeat penalty, brought up to date."""
+        if self.counts is None:
+            self.counts = TokenCounts()
+        return self.counts.update(self.prompt, self.output)
 
     @property
     def num_tokens(self):
@@ -89,7 +96,7 @@ class Scheduler:
         self.sampler = sampler
         # With ``lookahead`` the next step is launched with the sampled tokens still on the device,
         # and the host reads them one step late (EOS is then seen one step late: the extra row is
-        # discarded).  Needs a sampler with ``sample_device``; rows with a repeat penalty fall back.
+        # discarded).  Needs a sampler with ``sample_device(logits, params, rngs, histories)``.
         self.lookahead = bool(lookahead) and hasattr(sampler, "sample_device")
         self._pending = None
         self._host_tokens = [None, None]
@@ -209,8 +216,7 @@ class Scheduler:
 
     def step(self):
         """Plan, run and sample one step.  Returns the requests that finished in it."""
-        if self.lookahead and all(r.params.repeat_penalty == 1.0 or r.params.greedy
-                                  for r in list(self.running) + list(self.waiting)):
+        if self.lookahead:
             return self._step_lookahead()
         self._resolve()
         done_before = len(self.finished)
@@ -240,7 +246,7 @@ class Scheduler:
         for r, n in rows:
             r.computed += n
         if sampled:
-            histories = [r.tokens if (r.params.repeat_penalty != 1.0 and not r.params.greedy) else ()
+            histories = [r.token_counts() if (r.params.repeat_penalty != 1.0 and not r.params.greedy) else ()
                          for r in sampled]
             tokens = self.sampler.sample(logits, [r.params for r in sampled], [r.rng for r in sampled], histories)
             for r, tok in zip(sampled, tokens):
@@ -319,9 +325,15 @@ class Scheduler:
         self.counters["prefill_tokens"] += n_prefill
         for r, n in rows:
             r.computed += n
+        # The previous step's tokens: they were this step's input, so they have long arrived, and the
+        # repeat penalty of this step's rows counts them.
+        self._resolve()
         new_pending = None
         if sampled:
-            dev = self.sampler.sample_device(logits, [r.params for r in sampled], [r.rng for r in sampled])
+            histories = [r.token_counts() if (r.params.repeat_penalty != 1.0 and not r.params.greedy) else ()
+                         for r in sampled]
+            dev = self.sampler.sample_device(logits, [r.params for r in sampled], [r.rng for r in sampled],
+                                             histories)
             k = self._host_flip
             self._host_flip ^= 1
             host = self._host_tokens[k]
@@ -332,7 +344,6 @@ class Scheduler:
             event = torch.cuda.Event()
             event.record()
             new_pending = (dev, host, event, list(sampled))
-        self._resolve()                        # the previous step's tokens, while this step runs
         for i, r in enumerate(sampled):
             if r.finished:
                 continue                       # EOS came to light just now: this step's row is void

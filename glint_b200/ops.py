@@ -58,6 +58,7 @@ _CORE_SIGNATURES = {
     "glint_argmax_wide": [_P, _L, _I, _I, _P, _P, _P, _P],
     "glint_apply_penalty": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
     "glint_sample": [_P, _L, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P],
+    "glint_sample_rows": [_P, _L, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P],
 }
 
 _core = None
@@ -246,3 +247,27 @@ def sample(src, work, temperature, top_k, top_p, min_p, uniform, out):
     require(uniform, torch.float32, "uniform"); require(out, torch.int32, "out")
     check(core().glint_sample(ptr(src), src.stride(0), ptr(work), rows, V, ptr(temperature), ptr(top_k),
                               ptr(top_p), ptr(min_p), ptr(uniform), ptr(out), stream()), "sample")
+
+
+def sample_rows(logits, work, temperature, top_k, top_p, min_p, uniform, out, penalties=None):
+    """The whole choice for every row of ``logits`` [rows, V]: repeat penalty (``penalties`` = (offsets
+    [rows + 1], tokens, counts, penalty [rows]), a token once per row, or None), temperature, top-k,
+    min-p, softmax, top-p, draw with ``uniform``.  Rows of 16 K entries and more are shared by the blocks
+    of a cluster; ``work`` [rows, V] is scratch for narrower rows."""
+    rows, V = logits.shape
+    require(logits, torch.float32, "logits"); require(work, torch.float32, "work")
+    require(temperature, torch.float32, "temperature"); require(top_k, torch.int32, "top_k")
+    require(top_p, torch.float32, "top_p"); require(min_p, torch.float32, "min_p")
+    require(uniform, torch.float32, "uniform"); require(out, torch.int32, "out")
+    offsets = tokens = counts = penalty = None
+    if penalties is not None:
+        offsets, tokens, counts, penalty = penalties
+        require(offsets, torch.int32, "offsets"); require(tokens, torch.int32, "tokens")
+        require(counts, torch.int32, "counts"); require(penalty, torch.float32, "penalty")
+        if offsets.numel() != rows + 1 or penalty.numel() != rows or tokens.numel() != counts.numel():
+            raise KernelError("sample_rows: the penalty lists do not fit the rows")
+    if work.shape[0] < rows or work.shape[1] != V:
+        raise KernelError(f"sample_rows: work {tuple(work.shape)} does not fit {rows} rows of {V}")
+    check(core().glint_sample_rows(ptr(logits), logits.stride(0), ptr(work), rows, V, ptr(temperature), ptr(top_k),
+                                   ptr(top_p), ptr(min_p), ptr(uniform), ptr(offsets), ptr(tokens), ptr(counts),
+                                   ptr(penalty), ptr(out), stream()), "sample_rows")

@@ -1,4 +1,4 @@
 """Greedy and stochastic token choice."""
-from .sampler import SamplingParams, Xorshift64, DeviceSampler
+from .sampler import SamplingParams, Xorshift64, DeviceSampler, TokenCounts
 
-__all__ = ["SamplingParams", "Xorshift64", "DeviceSampler"]
+__all__ = ["SamplingParams", "Xorshift64", "DeviceSampler", "TokenCounts"]

@@ -9,7 +9,6 @@ state is the request's own, kept with the request so that batching never changes
 from __future__ import annotations
 
 import time
-from collections import Counter
 from dataclasses import dataclass
 from typing import Optional
 
@@ -67,6 +66,63 @@ class Xorshift64:
         return np.float32(self.next_u64() >> 40) / np.float32(1 << 24)
 
 
+class TokenCounts:
+    """How often each token occurs in a request's prompt and output, kept up to date as the output
+    grows: the repeat penalty wants every past token with its count at every step, and counting
+    thousands of tokens anew each time costs more than the step."""
+
+    def __init__(self):
+        self._reset()
+
+    def _reset(self):
+        self.index = {}                                  # token -> its place in the arrays
+        self.tokens = np.empty(256, dtype=np.int32)
+        self.counts = np.empty(256, dtype=np.int32)
+        self.n = 0
+        self.n_prompt = self.n_output = 0
+
+    def _add(self, tok):
+        at = self.index.get(tok)
+        if at is not None:
+            self.counts[at] += 1
+            return
+        if self.n == self.tokens.shape[0]:
+            self.tokens = np.concatenate([self.tokens, np.empty_like(self.tokens)])
+            self.counts = np.concatenate([self.counts, np.empty_like(self.counts)])
+        self.index[tok] = self.n
+        self.tokens[self.n] = tok
+        self.counts[self.n] = 1
+        self.n += 1
+
+    def update(self, prompt, output):
+        """Bring the counts up to ``prompt + output``; anything but a longer output starts over."""
+        if len(prompt) != self.n_prompt or len(output) < self.n_output:
+            self._reset()
+            if len(prompt):
+                toks, cnts = np.unique(np.asarray(prompt, dtype=np.int64), return_counts=True)
+                self.tokens, self.counts = toks.astype(np.int32), cnts.astype(np.int32)
+                self.n = len(toks)
+                self.index = {int(t): i for i, t in enumerate(toks.tolist())}
+            self.n_prompt = len(prompt)
+        for tok in output[self.n_output:]:
+            self._add(int(tok))
+        self.n_output = len(output)
+        return self
+
+    def arrays(self):
+        return self.tokens[:self.n], self.counts[:self.n]
+
+
+def _counts_of(history):
+    """(tokens, counts) int32 arrays of a row's history: a ``TokenCounts`` or a sequence of tokens."""
+    if isinstance(history, TokenCounts):
+        return history.arrays()
+    if len(history) == 0:
+        return np.empty(0, np.int32), np.empty(0, np.int32)
+    toks, cnts = np.unique(np.asarray(history, dtype=np.int64), return_counts=True)
+    return toks.astype(np.int32), cnts.astype(np.int32)
+
+
 class DeviceSampler:
     """Chooses one token per logits row with the CUDA kernels of ``csrc/sampling.cu``."""
 
@@ -74,61 +130,92 @@ class DeviceSampler:
         self.rt = rt
         self.vocab_size = vocab_size
         self._work = None
+        self._stage = [None] * 4          # pinned buffers for the per-row options
+        self._stage_next = 0
+        self._pen_stage = [None] * 4      # and for the repeat penalty's lists
+        self._pen_next = 0
 
     def _scratch(self, rows):
         if self._work is None or self._work.shape[0] < rows:
             self._work = torch.empty((max(rows, 8), self.vocab_size), dtype=torch.float32, device=self.rt.device)
         return self._work[:rows]
 
-    def sample_device(self, logits, params, rngs):
-        """Like ``sample`` for rows without a repeat penalty, but the chosen tokens stay on the
-        device (int32 [rows]); nothing waits for the GPU.  Uniform draws are taken from the rows'
-        generators now, so the stream of draws is the same as with ``sample``."""
+    def _options(self, params, rngs, dev):
+        """Per-row options as one upload: rows temperature, uniform draw, top-p, min-p, repeat penalty,
+        not-greedy (float32) and top-k (int32 in the same buffer).  Uniform draws are taken from the rows'
+        generators now; a greedy row takes none.  The upload goes from one of four pinned buffers in turn
+        and does not wait for the GPU: a copy from pageable memory would hold the host until the step
+        before it on the stream has run, and with it the preparation of the next step."""
+        rows = len(params)
+        k = self._stage_next
+        self._stage_next = (k + 1) % len(self._stage)
+        host = self._stage[k]
+        if host is None or host.shape[1] < rows:
+            host = torch.empty((7, max(rows, 64)), dtype=torch.float32).pin_memory()
+            self._stage[k] = host
+        pack = host.numpy()
+        for i, (p, r) in enumerate(zip(params, rngs)):
+            g = p.greedy
+            pack[0, i] = 1.0 if g else p.temperature
+            pack[1, i] = 0.0 if g else float(r.next_f32())
+            pack[2, i] = p.top_p
+            pack[3, i] = p.min_p
+            pack[4, i] = p.repeat_penalty
+            pack[5, i] = 0.0 if g else 1.0
+        pack[6].view(np.int32)[:rows] = [p.top_k for p in params]
+        d = host.to(dev, non_blocking=True)[:, :rows]          # the whole small buffer: a contiguous copy
+        return d, d[6].view(torch.int32)
+
+    def _penalties(self, params, histories, penalty_row, dev):
+        """The rows' (token, count) lists as one upload from a pinned buffer: offsets [rows + 1], tokens,
+        counts.  None when no row has a penalty."""
+        if histories is None or not any(p.repeat_penalty != 1.0 and not p.greedy for p in params):
+            return None
+        rows = len(params)
+        offsets, toks, counts = [0], [], []
+        for p, h in zip(params, histories):
+            if p.repeat_penalty != 1.0 and not p.greedy:
+                t, c = _counts_of(h)
+                toks.append(t)
+                counts.append(c)
+                offsets.append(offsets[-1] + len(t))
+            else:
+                offsets.append(offsets[-1])
+        n = offsets[-1]
+        m = max(n, 1)
+        size = rows + 1 + 2 * m
+        k = self._pen_next
+        self._pen_next = (k + 1) % len(self._pen_stage)
+        host = self._pen_stage[k]
+        if host is None or host.numel() < size:
+            host = torch.empty(max(2 * size, 4096), dtype=torch.int32).pin_memory()
+            self._pen_stage[k] = host
+        pack = host.numpy()
+        pack[:rows + 1] = offsets
+        pack[rows + 1:rows + 1 + 2 * m] = 0
+        if n:
+            pack[rows + 1:rows + 1 + n] = np.concatenate(toks)
+            pack[rows + 1 + m:rows + 1 + m + n] = np.concatenate(counts)
+        d = host[:size].to(dev, non_blocking=True)
+        return d[:rows + 1], d[rows + 1:rows + 1 + m], d[rows + 1 + m:rows + 1 + 2 * m], penalty_row
+
+    def sample_device(self, logits, params, rngs, histories=None):
+        """One token per row of ``logits`` (float32 [rows, vocab] on the device), left on the device
+        (int32 [rows]); nothing waits for the GPU.  Per row its ``SamplingParams``, its ``Xorshift64`` and,
+        for the repeat penalty, the tokens so far (a sequence, or a ``TokenCounts`` that the caller keeps
+        up to date)."""
         rows = logits.shape[0]
         dev = logits.device
         chosen = torch.empty(rows, dtype=torch.int32, device=dev)
-        if all(p.greedy for p in params):
-            ops.argmax(logits, chosen)
-            return chosen
         ops.argmax(logits, chosen)
-        temp = [p.temperature if not p.greedy else 1.0 for p in params]
-        uniform = [float(r.next_f32()) if not p.greedy else 0.0 for p, r in zip(params, rngs)]
-        pack = torch.tensor([temp, uniform, [p.top_p for p in params], [p.min_p for p in params],
-                             [float(p.top_k) for p in params], [0.0 if p.greedy else 1.0 for p in params]],
-                            dtype=torch.float32).pin_memory().to(dev, non_blocking=True)
+        if all(p.greedy for p in params):
+            return chosen
+        opt, top_k = self._options(params, rngs, dev)
+        penalties = self._penalties(params, histories, opt[4], dev)
         drawn = torch.empty(rows, dtype=torch.int32, device=dev)
-        ops.sample(logits, self._scratch(rows), pack[0].contiguous(), pack[4].to(torch.int32), pack[2].contiguous(),
-                   pack[3].contiguous(), pack[1].contiguous(), drawn)
-        return torch.where(pack[5] > 0, drawn, chosen)
+        ops.sample_rows(logits, self._scratch(rows), opt[0], top_k, opt[2], opt[3], opt[1], drawn, penalties)
+        return torch.where(opt[5] > 0, drawn, chosen)
 
     def sample(self, logits, params, rngs, histories):
-        """``logits`` float32 [rows, vocab] on the device; per row its ``SamplingParams``, its
-        ``Xorshift64`` and the tokens so far (for the repeat penalty).  Returns a list of ints."""
-        rows = logits.shape[0]
-        dev = logits.device
-        greedy_out = torch.empty(rows, dtype=torch.int32, device=dev)
-        ops.argmax(logits, greedy_out)
-        if all(p.greedy for p in params):
-            return [int(t) for t in greedy_out.tolist()]
-        temp = [p.temperature if not p.greedy else 1.0 for p in params]
-        uniform = [float(r.next_f32()) if not p.greedy else 0.0 for p, r in zip(params, rngs)]
-        work = self._scratch(rows)
-        src = logits
-        if any(p.repeat_penalty != 1.0 and not p.greedy for p in params):
-            offsets, toks, counts = [0], [], []
-            for p, h in zip(params, histories):
-                if p.repeat_penalty != 1.0 and not p.greedy:
-                    for tok, c in Counter(h).items():
-                        toks.append(tok)
-                        counts.append(c)
-                offsets.append(len(toks))
-            i32 = lambda v: torch.tensor(v or [0], dtype=torch.int32, device=dev)
-            pen = torch.tensor([p.repeat_penalty for p in params], dtype=torch.float32, device=dev)
-            ops.apply_penalty(logits, work, i32(offsets), i32(toks), i32(counts), pen)
-            src = work
-        f32 = lambda v: torch.tensor(v, dtype=torch.float32, device=dev)
-        out = torch.empty(rows, dtype=torch.int32, device=dev)
-        ops.sample(src, work, f32(temp), torch.tensor([p.top_k for p in params], dtype=torch.int32, device=dev),
-                   f32([p.top_p for p in params]), f32([p.min_p for p in params]), f32(uniform), out)
-        drawn, greedy = out.tolist(), greedy_out.tolist()
-        return [int(g if p.greedy else d) for p, g, d in zip(params, greedy, drawn)]
+        """The same with the tokens brought to the host: a list of ints."""
+        return [int(t) for t in self.sample_device(logits, params, rngs, histories).tolist()]

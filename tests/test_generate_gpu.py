@@ -110,6 +110,33 @@ def test_temperature_sampling_is_seeded_and_follows_the_plain_sampler(folders):
     assert agree >= 20, (agree, a[1])      # a draw within rounding of a boundary may differ late
 
 
+def test_all_sampling_options_with_and_without_lookahead(folders):
+    """top-k, top-p, min-p and the repeat penalty through the entry point: the tokens do not depend on
+    whether the next step is launched before the last tokens reach the host, and they are the plain
+    sampler's on the plain logits (the penalty counts every token so far, the newest one included)."""
+    from glint_b200 import LLM
+    vocab = TINY["B"][0]["vocab_size"]
+    prompts = [random_tokens(n, vocab, 50 + i) for i, n in enumerate([5, 40, 17])]
+    opts = dict(temperature=0.9, top_k=12, top_p=0.92, min_p=0.01, repeat_penalty=1.3)
+    outs = []
+    for lookahead in (True, False):
+        llm = LLM(folders["B"], dtype="float32", cache_tokens=1024, max_active=4, max_step_tokens=32, lookahead=lookahead)
+        outs.append(llm.generate(prompts, max_tokens=20, seed=3, stop_at_eos=False, **opts))
+    assert outs[0] == outs[1]
+    cfg, w = plain.read_config(folders["B"]), plain.read_weights(folders["B"])
+    rng = psampler.Xorshift64(3 + 2)                                       # request 2
+    toks = list(prompts[2])
+    agree = 0
+    for i in range(20):
+        logits = plain.forward(cfg, w, toks)[-1].numpy()
+        t = psampler.sample(logits, toks, rng, **opts)
+        if t != outs[0][2][i]:
+            break
+        agree += 1
+        toks.append(t)
+    assert agree >= 16, (agree, outs[0][2])
+
+
 def test_small_cache_preempts_and_still_gives_the_same_tokens(folders):
     from glint_b200 import LLM
     vocab = TINY["A"][0]["vocab_size"]

@@ -562,6 +562,87 @@ def test_sampling_kernel_against_the_plain_sampler():
     assert agree >= total - 2, (agree, total)
 
 
+def _exact_distribution(logits, past, temperature=1.0, top_k=0, top_p=1.0, min_p=0.0, repeat_penalty=1.0):
+    """The sampler's stages in float64 (tests/plain/sampler.py in higher precision; top-k keeps every
+    element equal to the k-th, as the device does): the final probabilities."""
+    x = np.asarray(logits, dtype=np.float64).copy()
+    for t in past:
+        x[t] = x[t] / repeat_penalty if x[t] > 0 else x[t] * repeat_penalty
+    x = x / temperature
+    if 0 < top_k < len(x):
+        kth = np.sort(x)[-top_k]
+        x[x < kth] = -np.inf
+    if min_p > 0.0:
+        x[x < x.max() + np.log(min_p)] = -np.inf
+    p = np.exp(x - x.max())
+    p /= p.sum()
+    if top_p < 1.0:
+        order = np.argsort(-p, kind="stable")
+        cut = int(np.searchsorted(np.cumsum(p[order]), top_p, side="left")) + 1
+        kept = np.zeros_like(p)
+        kept[order[:cut]] = p[order[:cut]]
+        p = kept / kept.sum()
+    return p
+
+
+@pytest.mark.parametrize("V", [16384, 100003, 256000])
+def test_sampling_of_wide_rows_by_a_cluster(V):
+    """Rows of 16 K entries and more are shared by the blocks of a cluster.  Peaked rows must give the
+    plain sampler's token; on flat rows, where thousands of tokens share the mass and 32-bit running sums
+    differ in their last digits, the token must be the one whose interval of the exact cumulative
+    distribution holds the draw, to within 1e-3 of mass.  All rows of a case go in one launch."""
+    from glint_b200 import ops
+    from tests.plain import sampler as ps
+    g = torch.Generator().manual_seed(V)
+    cases = [dict(temperature=0.8), dict(temperature=1.0, top_k=40), dict(temperature=0.7, top_p=0.9),
+             dict(temperature=1.0, min_p=0.05), dict(temperature=0.9, top_k=50, top_p=0.8, min_p=0.01),
+             dict(temperature=1.3, top_k=1), dict(temperature=1.0, top_p=0.3, repeat_penalty=1.7),
+             dict(temperature=0.6, top_k=2000, top_p=0.95, repeat_penalty=1.2)]
+    for spread, exact in ((9.0, True), (2.0, False)):
+        rows = len(cases)
+        logits = (torch.randn(rows, V, generator=g) * spread).float()
+        logits[1, 77] = logits[1, V - 5] = logits[1].max() + 1.0          # equal values at the top
+        pasts = [[] if "repeat_penalty" not in c else
+                 [int(t) for t in torch.topk(logits[i], 6).indices.tolist()] * 2 + [3, V - 1, 3]
+                 for i, c in enumerate(cases)]
+        us = [float(ps.Xorshift64(1000 * V + i).next_f32()) for i in range(rows)]
+        f32 = lambda v: torch.tensor(v, dtype=torch.float32, device=DEV)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        offsets, toks, counts = [0], [], []
+        for past in pasts:
+            uniq = sorted(set(past))
+            toks += uniq
+            counts += [past.count(t) for t in uniq]
+            offsets.append(len(toks))
+        out = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
+        work = torch.empty(rows, V, device=DEV)
+        dev_logits = logits.to(DEV)
+        args = (dev_logits, work, f32([c["temperature"] for c in cases]), i32([c.get("top_k", 0) for c in cases]),
+                f32([c.get("top_p", 1.0) for c in cases]), f32([c.get("min_p", 0.0) for c in cases]), f32(us), out)
+        pens = (i32(offsets), i32(toks), i32(counts), f32([c.get("repeat_penalty", 1.0) for c in cases]))
+        ops.sample_rows(*args, penalties=pens)
+        got = out.tolist()
+        out.fill_(-1)
+        ops.sample_rows(*args, penalties=pens)
+        assert out.tolist() == got                                         # the same twice
+        assert torch.equal(dev_logits.cpu(), logits)                       # the logits are left as they were
+        agree = 0
+        for i, c in enumerate(cases):
+            p = _exact_distribution(logits[i].numpy(), pasts[i], **c)
+            cdf = np.cumsum(p)
+            j = got[i]
+            assert 0 <= j < V and p[j] > 0, (V, spread, i, j)
+            assert cdf[j] - p[j] - 1e-3 <= us[i] < cdf[j] + 1e-3, (V, spread, i, j, us[i], cdf[j] - p[j], cdf[j])
+            if exact:
+                class _U:                                                   # the plain sampler draws the same u
+                    def next_f32(self, u=us[i]):
+                        return np.float32(u)
+                agree += int(ps.sample(logits[i].numpy(), pasts[i], _U(), **c) == j)
+        if exact:
+            assert agree >= rows - 1, (V, agree)
+        assert got[5] == int(torch.argmax(logits[5]))                      # top_k = 1
+
+
 def test_repeat_penalty_kernel():
     from glint_b200 import ops
     V = 64

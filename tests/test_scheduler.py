@@ -164,3 +164,18 @@ def test_a_request_that_cannot_fit_alone_ends_with_length_and_the_engine_goes_on
     assert never.finish_reason == FINISH_LENGTH and never.output == []
     assert nxt.output == expected(nxt.prompt, 5)
     assert all(v["live"] == 0 for v in eng.cache.stats().values())
+def test_token_counts_follow_a_growing_output():
+    from glint_b200.sampling import TokenCounts
+    tc = TokenCounts()
+    prompt, output = [5, 7, 5, 9], []
+    for tok in [7, 11, 5, 11, 11]:
+        output.append(tok)
+        t, c = tc.update(prompt, output).arrays()
+        want = {}
+        for x in prompt + output:
+            want[x] = want.get(x, 0) + 1
+        assert dict(zip(t.tolist(), c.tolist())) == want
+    t, c = tc.update(prompt + output, [2]).arrays()                        # resumed: the output joined the prompt
+    assert dict(zip(t.tolist(), c.tolist())) == {5: 3, 7: 2, 9: 1, 11: 3, 2: 1}
+
+
