@@ -150,6 +150,25 @@ def prefill_step(tokens, layers, iters):
     return {"kernel": "prefill step", "tokens": tokens, "layers": layers, "ms": round(ms, 4)}
 
 
+def bench_sampling(rows, V, iters=20):
+    """The sampling kernel on random logits: temperature alone, with top-k, and with every stage."""
+    from . import ops
+    logits = torch.randn(rows, V, device=DEV) * 3
+    work = torch.empty(rows, V, device=DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    f32 = lambda v: torch.full((rows,), v, dtype=torch.float32, device=DEV)
+    i32 = lambda v: torch.full((rows,), v, dtype=torch.int32, device=DEV)
+    past = torch.arange(0, 2048, dtype=torch.int32, device=DEV).repeat(rows)
+    pens = (torch.arange(0, rows + 1, dtype=torch.int32, device=DEV) * 2048, past, torch.ones_like(past), f32(1.1))
+    res = []
+    for name, k, p, mp, pen in (("temperature", 0, 1.0, 0.0, None), ("top-k 40", 40, 1.0, 0.0, None),
+                                ("top-p 0.9", 0, 0.9, 0.0, None), ("top-k, top-p, min-p, penalty", 40, 0.9, 0.02, pens)):
+        args = (logits, work, f32(0.8), i32(k), f32(p), f32(mp), f32(0.37), out)
+        us = _time(lambda i: ops.sample_rows(*args, penalties=pen), 1, iters)
+        res.append({"kernel": "sample_rows", "rows": rows, "V": V, "stages": name, "us": round(us, 2)})
+    return res
+
+
 def gemma2_2b_decode_cases(batch):
     H, I, V, QKV, Q = 2304, 9216, 256000, 4096, 2048
     return [("qkv", batch, QKV, H, False), ("o", batch, H, Q, False), ("gate_up", batch, I, H, True),
@@ -159,7 +178,7 @@ def gemma2_2b_decode_cases(batch):
 def main():
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("what", choices=["gemm", "gated", "decode-shapes", "prefill-shapes", "attention-decode",
-                                     "attention-prefill", "rows", "prefill-step"])
+                                     "attention-prefill", "rows", "prefill-step", "sampling"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=2304)
@@ -198,6 +217,8 @@ def main():
         out.append(bench_attention_prefill(a.tokens, page=a.page, window=a.window or None, iters=a.iters))
     elif a.what == "rows":
         out.extend(bench_rows(a.batch))
+    elif a.what == "sampling":
+        out.extend(bench_sampling(a.batch, a.n if a.n != 4096 else 256000, a.iters))
     elif a.what == "prefill-step":
         out.append(prefill_step(a.tokens, a.layers, a.iters))
     for row in out:
