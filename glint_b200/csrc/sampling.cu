@@ -6,7 +6,9 @@
 // that land within rounding of a threshold: top-k and top-p keep every element equal to the
 // threshold value (the reference's unstable partial sort keeps an arbitrary subset), and sums
 // are block reductions rather than index-order running sums.  The draw walks the cumulative
-// distribution in index order as the reference does (:377-388).
+// distribution in index order as the reference does (:377-388).  The histograms of probabilities
+// behind top-p are added up with floating-point atomics, whose order is not fixed: a row whose top-p
+// boundary lies within rounding of a bin's edge may, from run to run, keep one token more or less.
 #include "common.cuh"
 
 namespace glint {
