@@ -236,12 +236,13 @@ def test_qkv_product_with_rotation_and_cache_write_in_one_kernel(M, K, nh, nkv, 
         assert (k_pool == 7.0).all() and (v_pool == -3.0).all()
 
 
-@pytest.mark.parametrize("lens,starts,K,nh,nkv,hd,page,writes", [
-    ([300, 41, 2], [0, 77, 1000], 136, 3, 1, 256, 16, True),       # three requests, 343 tokens: two token tiles
-    ([5], [3], 64, 2, 2, 512, 32, True),                            # two groups of 128 pairs per head
-    ([600], [4090], 2304, 8, 4, 256, 16, True),
-    ([70, 9], [0, 5], 200, 1, 1, 256, 16, False)])
-def test_tiled_qkv_product_with_rotation_and_cache_write(lens, starts, K, nh, nkv, hd, page, writes):
+@pytest.mark.parametrize("lens,starts,K,nh,nkv,hd,page,writes,min_blocks", [
+    ([300, 41, 2], [0, 77, 1000], 136, 3, 1, 256, 16, True, 0),    # three requests, 343 tokens: two token tiles
+    ([300, 41, 2], [0, 77, 1000], 136, 3, 1, 256, 16, True, 12),   # tiles of 128 tokens to have 12 blocks
+    ([5], [3], 64, 2, 2, 512, 32, True, 0),                         # two groups of 128 pairs per head
+    ([600], [4090], 2304, 8, 4, 256, 16, True, 0),
+    ([70, 9], [0, 5], 200, 1, 1, 256, 16, False, 0)])
+def test_tiled_qkv_product_with_rotation_and_cache_write(lens, starts, K, nh, nkv, hd, page, writes, min_blocks):
     """The same on the tiled kernel for portions of prompts: the angles come from a table made by
     ``rope_table``; tokens of one request share its row of the block table."""
     from glint_b200 import ops, ops_tensor
@@ -267,10 +268,10 @@ def test_tiled_qkv_product_with_rotation_and_cache_write(lens, starts, K, nh, nk
     ang = (pos[:, None] / factor) * inv_freq.cpu()[None, :]          # [M, hd/2]
     assert (trig[..., 0].cpu() - torch.cos(ang)).abs().max().item() < 1e-3     # float32 angles up to 4000 rad
     assert (trig[..., 1].cpu() - torch.sin(ang)).abs().max().item() < 1e-3
-    assert ops_tensor.qkv_rope_tiled_supported(M, K, hd, hd, nh + 2 * nkv, min_blocks=0)
+    assert ops_tensor.qkv_rope_tiled_supported(M, K, hd, hd, nh + 2 * nkv, min_blocks=min_blocks)
     assert not ops_tensor.qkv_rope_tiled_supported(M, K, hd, hd, nh + 2 * nkv, min_blocks=10 ** 6)
     ops_tensor.qkv_rope_tiled(x, w, trig, i32(positions), i32(seq), perm, q, k_pool if writes else None,
-                              v_pool if writes else None, nh, nkv, hd, page, n_pages, status, min_blocks=0)
+                              v_pool if writes else None, nh, nkv, hd, page, n_pages, status, min_blocks=min_blocks)
     torch.cuda.synchronize()
     assert status.item() == 0
     qkv = (x.float() @ w.float().T).cpu()
