@@ -18,6 +18,9 @@
 // (gate rows and up rows of the same features) act(gate) * up written as bfloat16.
 #include <stdlib.h>
 
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -647,18 +650,62 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// A [rows, K] bf16 row-major matrix viewed as tiles of box_rows x 64 with the 128-byte swizzle.
-static int make_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows) {
+// An encoded tensor map is a pure function of the address, the shape and the box: launches look theirs
+// up instead of encoding three per product (weights never move, and the allocator hands activations the
+// same addresses step after step).
+struct MapKey {
+  const void* base;
+  long long rows, cols;
+  int box_rows, box_cols, kind;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows && box_cols == o.box_cols &&
+           kind == o.kind;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base) * 0x9E3779B97F4A7C15ull;
+    h ^= (size_t)k.rows * 0xC2B2AE3D27D4EB4Full + (size_t)k.cols * 0x165667B19E3779F9ull;
+    h ^= ((size_t)k.box_rows << 40) ^ ((size_t)k.box_cols << 20) ^ (size_t)k.kind;
+    return h;
+  }
+};
+
+// kind 0: bf16 with the 128-byte swizzle (operands); 1: bf16, 2: float32 without swizzle (outputs)
+static int cached_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows, int box_cols,
+                      int kind) {
+  static std::mutex lock;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{base, rows, cols, box_rows, box_cols, kind};
+  {
+    std::lock_guard<std::mutex> g(lock);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *map = it->second;
+      return GLINT_OK;
+    }
+  }
   EncodeTiledFn fn = encode_fn();
   if (!fn) return GLINT_ERR_BAD_ARG;
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  cuuint32_t box[2] = {(cuuint32_t)GEMM_BK, (cuuint32_t)box_rows};
+  const int es = kind == 2 ? 4 : 2;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * es};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t elem[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  CUresult r = fn(map, kind == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  kind == 0 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? GLINT_OK : GLINT_ERR_BAD_ARG;
+  if (r != CUDA_SUCCESS) return GLINT_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> g(lock);
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, *map);
+  return GLINT_OK;
+}
+
+// A [rows, K] bf16 row-major matrix viewed as tiles of box_rows x 64 with the 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows) {
+  return cached_map(map, base, rows, K, box_rows, GEMM_BK, 0);
 }
 
 }  // namespace glint
@@ -687,7 +734,11 @@ static int gemm_launch(const void* x, const void* w, void* out, int out_bf16, in
   p.M = M; p.N = N; p.K = K;
   int bn_max = 256;
   if (rope) bn_max = rope->bn;
-  else if (const char* ov = getenv("GLINT_GEMM_BN")) { const int v = atoi(ov); if (v >= 16 && v <= 256 && v % 16 == 0) bn_max = v; }
+  else {
+    static int env_bn = -1;        // the environment is read once
+    if (env_bn < 0) { const char* ov = getenv("GLINT_GEMM_BN"); env_bn = ov ? atoi(ov) : 0; }
+    if (env_bn >= 16 && env_bn <= 256 && env_bn % 16 == 0) bn_max = env_bn;
+  }
   const int m_tiles_256 = (M + bn_max - 1) / bn_max;
   int bn = ((M + m_tiles_256 - 1) / m_tiles_256 + 15) / 16 * 16;
   if (dual && bn > 256) bn = 256;
@@ -716,7 +767,9 @@ static int gemm_launch(const void* x, const void* w, void* out, int out_bf16, in
   const int stage_bytes = A_STAGE_BYTES * (dual ? 2 : 1) + bn * GEMM_BK * 2;
   int stages = (227 * 1024 - 1024 - (int)sizeof(GemmShared) - 256) / stage_bytes;
   if (stages > GEMM_MAX_STAGES) stages = GEMM_MAX_STAGES;
-  if (const char* ov = getenv("GLINT_GEMM_STAGES")) { const int v = atoi(ov); if (v >= 2 && v < stages) stages = v; }
+  static int env_stages = -1;
+  if (env_stages < 0) { const char* ov = getenv("GLINT_GEMM_STAGES"); env_stages = ov ? atoi(ov) : 0; }
+  if (env_stages >= 2 && env_stages < stages) stages = env_stages;
   if (stages < 2) return GLINT_ERR_UNSUPPORTED_SIZE;
   p.stages = stages;
   p.total_kb = (K + GEMM_BK - 1) / GEMM_BK;
@@ -779,32 +832,29 @@ static int gemm_launch(const void* x, const void* w, void* out, int out_bf16, in
   if (tma_store_on < 0) { const char* ev = getenv("GLINT_GEMM_TMA_STORE"); tma_store_on = ev ? atoi(ev) : 1; }
   if (tma_store_on && !p.wide && !rope && out_bf16 && splits == 1 && bn >= 64 && ((long long)N * es) % 16 == 0 && ((uintptr_t)out & 15) == 0 &&
       (long long)bn * GEMM_BM * es <= (long long)stages * stage_bytes) {
-    EncodeTiledFn fn = encode_fn();
-    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
-    cuuint64_t strides[1] = {(cuuint64_t)N * es};
-    cuuint32_t box[2] = {(cuuint32_t)GEMM_BM, (cuuint32_t)bn};
-    cuuint32_t elem[2] = {1, 1};
-    if (fn && fn(&map_out, out_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, dims,
-                 strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
-      p.tma_store = 1;
+    if (cached_map(&map_out, out, M, N, bn, GEMM_BM, out_bf16 ? 1 : 2) == GLINT_OK) p.tma_store = 1;
   }
   static int wide_epilogue = -1;
   if (wide_epilogue < 0) { const char* ev = getenv("GLINT_GEMM_EPILOGUE_WARPS"); wide_epilogue = ev ? (atoi(ev) >= 8) : 1; }
   const int threads = (wide_epilogue && bn * (dual ? 2 : 1) >= 64) ? GEMM_THREADS_WIDE : GEMM_THREADS;
   dim3 grid(n_tiles * m_tiles, 1, splits);
   cudaError_t e;
-  if (dual) {
-    e = cudaFuncSetAttribute(gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  // the shared-memory limit of each kernel is raised once, to the most a launch may ask for
+  static int limit_set[2] = {-1, -1};      // the device it was raised on
+  const int smem_limit = 227 * 1024;
+  int device_now = 0;
+  cudaGetDevice(&device_now);
+  if (limit_set[dual ? 1 : 0] != device_now) {
+    e = dual ? cudaFuncSetAttribute(gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_limit)
+             : cudaFuncSetAttribute(gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_limit);
     if (e != cudaSuccess) return (int)e;
-    e = launch_kernel(gemm_tcgen05_kernel<true>, grid, dim3(threads), smem_bytes, stream, map_w, map_x, map_out, p);
-    if (e != cudaSuccess) return (int)e;
-  } else {
-    e = cudaFuncSetAttribute(gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (e != cudaSuccess) return (int)e;
-    e = launch_kernel(gemm_tcgen05_kernel<false>, grid, dim3(threads), smem_bytes, stream, map_w, map_x, map_out, p);
-    if (e != cudaSuccess) return (int)e;
+    limit_set[dual ? 1 : 0] = device_now;
   }
+  if (dual)
+    e = launch_kernel(gemm_tcgen05_kernel<true>, grid, dim3(threads), smem_bytes, stream, map_w, map_x, map_out, p);
+  else
+    e = launch_kernel(gemm_tcgen05_kernel<false>, grid, dim3(threads), smem_bytes, stream, map_w, map_x, map_out, p);
+  if (e != cudaSuccess) return (int)e;
   return (int)cudaGetLastError();
 }
 

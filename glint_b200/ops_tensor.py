@@ -36,13 +36,13 @@ def lib():
 
 def scratch(device):
     """Split-K workspace and zeroed tile counters of a device (allocated once)."""
-    key = str(device)
-    if key not in _scratch:
+    entry = _scratch.get(device)
+    if entry is None:
         l = lib()
         ws = torch.empty(l.lib.glint_gemm_workspace_bytes() // 4, dtype=torch.float32, device=device)
         counters = torch.zeros(l.lib.glint_gemm_counter_count(), dtype=torch.int32, device=device)
-        _scratch[key] = (ws, counters)
-    return _scratch[key]
+        entry = _scratch[device] = (ws, counters)
+    return entry
 
 
 def gemm_supported(M, N, K):

@@ -59,15 +59,15 @@ class Attention(Part):
     def forward(self, normed, ctx, view, state=None):
         rt = self.rt
         T = normed.shape[0]
-        q = torch.empty((T, self.q_size), dtype=rt.dtype, device=normed.device)
+        q = rt.buffer("mixer.q", (T, self.q_size))
         fused = getattr(self.position, "project_encode_store", None)
         if fused is None or not fused(normed, self.w_qkv, ctx, q, view, self.num_heads, self.num_kv_heads,
                                       self.head_dim):
-            qkv = linear(rt, normed, self.w_qkv)
+            qkv = linear(rt, normed, self.w_qkv, out=rt.buffer("mixer.qkv", (T, self.w_qkv.shape[0]), torch.float32))
             self.position.encode_and_store(qkv, ctx, q, view, self.num_heads, self.num_kv_heads, self.head_dim)
-        out = torch.empty_like(q)
+        out = rt.buffer("mixer.out", (T, self.q_size))
         self.attend(q, ctx, view, out)
-        return linear(rt, out, self.w_o)
+        return linear(rt, out, self.w_o, out=rt.buffer("mixer.y", (T, self.w_o.shape[0]), torch.float32))
 
     def attend(self, q, ctx, view, out):
         rt = self.rt

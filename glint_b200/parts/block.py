@@ -48,7 +48,7 @@ class Block:
 
     def _add_then_norm(self, x, y, post_norm, next_norm, want_next):
         """x += post_norm(y); returns next_norm(x) in the activation dtype when wanted."""
-        out = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device) if want_next else None
+        out = self.rt.buffer("block.normed", tuple(x.shape)) if want_next else None
         if _fusable(post_norm, next_norm):
             ops.add_rmsnorm(x, y, _triple(post_norm), out, _triple(next_norm) if want_next else None)
             return out

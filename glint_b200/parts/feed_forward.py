@@ -39,7 +39,7 @@ class GatedFeedForward(Part):
     def forward(self, normed, ctx):
         rt = self.rt
         T = normed.shape[0]
-        act = torch.empty((T, self.intermediate_size), dtype=rt.dtype, device=normed.device)
+        act = rt.buffer("ffn.act", (T, self.intermediate_size))
         fused = False
         if rt.tensor_cores:
             from .. import ops_tensor
@@ -47,9 +47,9 @@ class GatedFeedForward(Part):
                 ops_tensor.gemm_gated(normed, self.w_gate_up, act, self.activation, rt.status)
                 fused = True
         if not fused:
-            gu = linear(rt, normed, self.w_gate_up)
+            gu = linear(rt, normed, self.w_gate_up, out=rt.buffer("ffn.gate_up", (T, 2 * self.intermediate_size), torch.float32))
             ops.gated_act(gu, act, self.activation)
-        return linear(rt, act, self.w_down)
+        return linear(rt, act, self.w_down, out=rt.buffer("ffn.y", (T, self.hidden_size), torch.float32))
 
     def parameter_bytes(self):
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()

@@ -42,6 +42,9 @@ class Runtime:
             raise KernelError("no CUDA device is available: the engine has no CPU path")
         ops.core()  # build or load the kernels now, loudly
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._backing = {}        # (role, dtype) -> flat tensor
+        self._views = {}          # (role, shape, dtype) -> view of the backing tensor
+        self._retired = []        # outgrown backing tensors: captured launches may still point into them
 
     @property
     def tensor_cores(self):
@@ -49,6 +52,34 @@ class Runtime:
 
     def empty(self, shape, dtype=None):
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+
+    def buffer(self, role, shape, dtype=None):
+        """A tensor of this shape for a value that lives from one kernel to the next within a step.  One
+        allocation per role serves every layer and every step: the kernels of a step run in order on
+        one stream, so whatever read the role's previous value was issued before the kernel that
+        writes the next one.  Two values that are alive at the same time need different roles; a part
+        that cannot promise that allocates with ``empty``.  (A step of a few hundred tokens is bound by
+        the host, and seven allocations per layer were a sixth of its time.)"""
+        dtype = dtype or self.dtype
+        key = (role, shape, dtype)
+        view = self._views.get(key)
+        if view is None:
+            n = 1
+            for d in shape:
+                n *= int(d)
+            base = self._backing.get((role, dtype))
+            if base is None or base.numel() < n:
+                grown = 2 * base.numel() if base is not None else 1      # what was outgrown stays allocated: keep it a fraction
+                if base is not None:
+                    self._retired.append(base)
+                    self._views = {k: v for k, v in self._views.items() if k[0] != role or k[2] != dtype}
+                base = torch.empty(max(n, grown), dtype=dtype, device=self.device)
+                self._backing[(role, dtype)] = base
+            if len(self._views) > 512:
+                self._views.clear()
+            view = base[:n].view(shape)
+            self._views[key] = view
+        return view
 
     def check_status(self):
         """Read the device status word (synchronizes); raise if a kernel reported a fault."""
