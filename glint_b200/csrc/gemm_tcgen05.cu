@@ -718,7 +718,8 @@ GLINT_API int glint_gemm_tcgen05_supported(long long M, long long N, long long K
   return (M > 0 && N > 0 && K > 0 && K % 8 == 0) ? 1 : 0;
 }
 
-GLINT_API long long glint_gemm_workspace_bytes() { return 16ll << 20; }
+// room for the partial tiles of one block per SM at the widest tile: 148 x 2 x 256 x 128 floats and some
+GLINT_API long long glint_gemm_workspace_bytes() { return 48ll << 20; }
 GLINT_API int glint_gemm_counter_count() { return 8192; }
 
 // The launch behind both entry points; ``rope`` selects the rotary epilogue of the dual kernel.
@@ -789,7 +790,8 @@ static int gemm_launch(const void* x, const void* w, void* out, int out_bf16, in
       const int per = (p.total_kb + cand - 1) / cand;
       // spread over the tile's blocks, the reduction costs the wait for the slowest block and one tile's worth of reads
       const float reduce = spread_on ? 4.0f + 0.04f * width : 1.5f + 0.04f * width * cand;
-      const float est = 0.3f * per + (cand > 1 ? reduce : 0.f);
+      const float kb_us = fmaxf(0.3f, 0.0015f * width);       // a K block: instruction-bound for narrow tiles, tensor-bound for wide ones
+      const float est = kb_us * per + (cand > 1 ? reduce : 0.f);
       if (est < best) {
         best = est;
         splits = cand;
@@ -801,7 +803,7 @@ static int gemm_launch(const void* x, const void* w, void* out, int out_bf16, in
   splits = (p.total_kb + p.kb_per_split - 1) / p.kb_per_split;
   const long long ws_need = (long long)tiles * splits * (dual ? 2 : 1) * bn * GEMM_BM * 4;
   if (splits > 1 && (ws_need > glint_gemm_workspace_bytes() || tiles > glint_gemm_counter_count() ||
-                     !workspace || !counters)) {
+                     !workspace || !counters)) {      // cannot happen while tiles x splits fit the SMs (see the workspace's size)
     splits = 1;
     p.kb_per_split = p.total_kb;
   }
