@@ -39,7 +39,10 @@ class StepContext:
     token's request within this step, which is also its row in every block table.
     ``seq_slot``, ``seq_start`` (tokens cached before the step), ``cu_seqlens`` (token offsets,
     one more than requests) are per request; ``logit_rows`` are the token rows whose logits are
-    wanted.  The ``h_`` fields are host copies for planning launches.  ``memo`` is empty at the start of
+    wanted.  ``leading_single`` counts the requests at the front of the step that bring a single
+    token (a scheduler puts its decoding requests first), ``leading_single_context`` is the longest
+    context among them.  The ``h_`` fields are host copies for
+    planning launches.  ``memo`` is empty at the start of
     a step: parts keep there what several layers of the step share (a table of rotation angles, say),
     under a key of their own parameters.
     """
@@ -57,7 +60,9 @@ class StepContext:
         for l in lens:
             self.h_cu_seqlens.append(self.h_cu_seqlens[-1] + l)
         self.max_seq_len = max(lens)
+        self.leading_single = next((i for i, l in enumerate(lens) if l != 1), n)   # requests in front that bring one token
         self.max_context = max(s + l for s, l in zip(self.h_seq_start, lens))
+        self.leading_single_context = max([s + 1 for s in self.h_seq_start[:self.leading_single]] or [0])
         rows = []
         for i, e in enumerate(entries):
             for w in e.want:

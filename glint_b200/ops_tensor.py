@@ -202,9 +202,10 @@ def decode_splits(tokens, nkv, max_context):
 
 
 def attention_decode(q, k_pool, v_pool, positions, token_seq, block_table, out, nh, nkv, hd, page_size, num_pages,
-                     multiplier, cap, window, status, splits):
-    """Every token attends alone (split over its keys): right for any batch, meant for single tokens."""
-    T = q.shape[0]
+                     multiplier, cap, window, status, splits, tokens=None):
+    """Every token attends alone (split over its keys): right for any batch, meant for single tokens.
+    ``tokens``: only the first so many rows of ``q``."""
+    T = q.shape[0] if tokens is None else tokens
     ops.require(q, torch.bfloat16, "q"); ops.require(k_pool, torch.bfloat16, "k_pool")
     ops.require(v_pool, torch.bfloat16, "v_pool"); ops.require(out, torch.bfloat16, "out")
     ops.check(lib().glint_attention_decode(ops.ptr(q), ops.ptr(k_pool), ops.ptr(v_pool), ops.ptr(positions),
@@ -243,10 +244,34 @@ def attention_tcgen05(q, k_pool, v_pool, cu_seqlens, seq_start, block_table, out
                                             ops.stream()), "attention_tcgen05")
 
 
+SPLIT_SINGLES_FROM = int(os.environ.get("GLINT_SPLIT_SINGLES_FROM", "4096"))   # context from which single tokens leave the tiled kernel
+SPLIT_SINGLES_UP_TO = 8            # so few of them leave it at any context
+
+
 def attention(q, view, ctx, out, nh, nkv, hd, multiplier, cap, window, status):
     """Route a step's attention: single tokens to the split kernel, portions to the tiled one."""
     table = ctx.block_table(view.group)
     if ctx.max_seq_len > 1 and tcgen05_attention_supported(nh, nkv, hd, view.page_size):
+        lead = getattr(ctx, "leading_single", 0)
+        if (lead > 0 and (lead <= SPLIT_SINGLES_UP_TO or getattr(ctx, "leading_single_context", 0) >= SPLIT_SINGLES_FROM)
+                and decode_supported(nh, nkv, hd, view.page_size)):
+            # Decoding requests in front of the prompt portions: in the tiled kernel one block walks all
+            # keys of such a row (8192 keys: 150 us, and the step waits for it); the split kernel shares
+            # them among a cluster (two requests at 7000 keys beside a portion of 1024 tokens: 9.2 -> 7.3
+            # ms a step).  Many requests with short contexts stay: their walks (2048 keys: 38 us) hide
+            # behind the portions' tiles, and the split kernel's time for 32 of them does not.  The
+            # portions keep their absolute token offsets.
+            attention_decode(q, view.k, view.v, ctx.positions, ctx.token_seq, table, out, nh, nkv, hd, view.page_size,
+                             view.num_pages, multiplier, cap, window, status,
+                             decode_splits(lead, nkv, ctx.max_context), tokens=lead)
+            key = ("portions behind single tokens", id(view.group), lead)
+            rest = ctx.memo.get(key)
+            if rest is None:
+                rest = ctx.memo[key] = (ctx.cu_seqlens[lead:], ctx.seq_start[lead:], table[lead:])
+            attention_tcgen05(q, view.k, view.v, rest[0], rest[1], rest[2], out, ctx.num_seqs - lead,
+                              ctx.max_seq_len, nh, nkv, hd, view.page_size, view.num_pages, multiplier, cap, window,
+                              status)
+            return
         attention_tcgen05(q, view.k, view.v, ctx.cu_seqlens, ctx.seq_start, table, out, ctx.num_seqs,
                           ctx.max_seq_len, nh, nkv, hd, view.page_size, view.num_pages, multiplier, cap, window,
                           status)

@@ -76,3 +76,41 @@ def test_replay_child_process(folders, expected, tmp_path, dtype):
     outputs = tracing.run_child(folders["B"], dtype, steps, str(tmp_path / "out"),
                                 tracing.max_live_tokens(steps), TINY["B"][0]["vocab_size"])
     _check("B", dtype, steps, outputs, want)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_single_tokens_in_front_of_portions(folders, expected, name, dtype, monkeypatch):
+    """A step with decoding requests first and prompt portions behind them (a scheduler's order) sends
+    the single tokens to the split attention kernel and the portions to the tiled one; the same step
+    with the portions first takes the tiled kernel for all.  Both must give the plain logits."""
+    from glint_b200 import ops_tensor
+    from glint_b200.engine.step import StepEntry
+    reqs, want = expected[name]
+    ids = sorted(reqs)
+    engine = _engine(folders[name], dtype, 512)
+    monkeypatch.setattr(ops_tensor, "SPLIT_SINGLES_FROM", 1)         # contexts of any length
+    monkeypatch.setattr(ops_tensor, "SPLIT_SINGLES_UP_TO", 0)
+    for portions_first in (False, True):
+        slots = {rid: engine.open() for rid in ids}
+        singles, portions = ids[2:], ids[:2]                     # the two longest requests decode
+        for rid in singles:                                       # all but their last token are in the cache
+            engine.step([StepEntry(slots[rid], reqs[rid][:-1], [])])
+        for rid in portions:                                      # the first two tokens of the portions too
+            engine.step([StepEntry(slots[rid], reqs[rid][:2], [])]) if len(reqs[rid]) > 3 else None
+        entries, order = [], []
+        for rid in (portions + singles if portions_first else singles + portions):
+            toks = reqs[rid]
+            if rid in singles:
+                entries.append(StepEntry(slots[rid], toks[-1:], [0]))
+            else:
+                at = 2 if len(toks) > 3 else 0
+                entries.append(StepEntry(slots[rid], toks[at:], [len(toks) - at - 1]))
+            order.append(rid)
+        got = engine.step(entries).float().cpu().numpy()
+        for row, rid in enumerate(order):
+            diff = np.abs(got[row] - want[rid][-1]).max()
+            assert diff <= tolerance(dtype, want[rid]), (name, dtype, portions_first, rid, diff)
+        for s_ in slots.values():
+            engine.close(s_)
+        engine.rt.check_status()
