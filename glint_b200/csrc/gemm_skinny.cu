@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(SK_MAX_WARPS * 32) gemm_skinny_kernel(const Sk
   __syncthreads();
   if (MODE == SK_ROPE) {
     // thread (pair j, token): both halves of the pair, turned by the token's position
-    if (threadIdx.x < 64) {
+    if (threadIdx.x < 64 * NT) {
       const int j = threadIdx.x & 7, tok = threadIdx.x >> 3;
       if (tok < p.M) {
         float v0 = 0.f, v1 = 0.f;
@@ -317,7 +317,7 @@ GLINT_API int glint_gemm_skinny(const void* x, const void* w, void* out, int out
 // epilogue: x [M, K]; w [(nh + 2 nkv) * hd, K]; q_out [M, nh * hd]; pools [pages][nkv][page_size][hd]
 // (null: q only).  The whole head is rotated (pairs (j, j + hd / 2)); hd a multiple of 16.
 GLINT_API int glint_gemm_skinny_rope_supported(int M, int K, int hd) {
-  return (M >= 1 && M <= 8 && K >= SK_STEP && K % SK_STEP == 0 && hd >= 16 && hd % 16 == 0) ? 1 : 0;
+  return (M >= 1 && M <= 16 && K >= SK_STEP && K % SK_STEP == 0 && hd >= 16 && hd % 16 == 0) ? 1 : 0;
 }
 
 GLINT_API int glint_gemm_skinny_rope(const void* x, const void* w, int M, int K, const int* positions,
@@ -338,6 +338,10 @@ GLINT_API int glint_gemm_skinny_rope(const void* x, const void* w, int M, int K,
   p.v_pool = (__nv_bfloat16*)v_pool; p.nh = nh; p.nkv = nkv; p.hd = hd; p.page_size = page_size;
   p.num_pages = num_pages; p.status = status;
   const int n_blocks = heads * (hd / 16);
+  if (M > 8) {
+    const int warps = skinny_warps(2, K / SK_STEP, n_blocks);
+    return (int)launch_kernel(gemm_skinny_kernel<2, SK_ROPE, 2>, dim3(n_blocks), dim3(warps * 32), 0, stream, p);
+  }
   const int warps = skinny_warps(4, K / SK_STEP, n_blocks);
   return (int)launch_kernel(gemm_skinny_kernel<1, SK_ROPE, 4>, dim3(n_blocks), dim3(warps * 32), 0, stream, p);
 }

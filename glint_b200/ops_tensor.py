@@ -94,14 +94,14 @@ FUSED_ROPE = os.environ.get("GLINT_FUSED_ROPE", "1") != "0"
 
 
 def qkv_rope_supported(M, K, hd, rotary_dim):
-    """The fused q/k/v product takes up to 8 tokens, K in steps of 64 and whole-head rotation."""
-    return (FUSED_ROPE and SKINNY_MAX_TOKENS > 0 and 1 <= M <= 8 and K >= 64 and K % 64 == 0 and hd % 16 == 0 and hd >= 16
+    """The fused q/k/v product takes up to 16 tokens, K in steps of 64 and whole-head rotation."""
+    return (FUSED_ROPE and 1 <= M <= min(16, SKINNY_MAX_TOKENS) and K >= 64 and K % 64 == 0 and hd % 16 == 0 and hd >= 16
             and rotary_dim == hd)
 
 
 def qkv_rope(a, w_qkv, positions, token_slot, block_table, inv_freq, factor, q_out, k_pool, v_pool, nh, nkv, hd,
              page_size, num_pages, status):
-    """q, k, v = a @ w_qkv^T for up to 8 tokens with the rotary encoding and the cache write in the
+    """q, k, v = a @ w_qkv^T for up to 16 tokens with the rotary encoding and the cache write in the
     product's epilogue: rotated q goes to ``q_out`` [M, nh * hd], rotated k and v into the pages named
     by ``block_table`` at each token's position (``k_pool`` None: q only)."""
     M, K = a.shape

@@ -186,7 +186,8 @@ def test_gemm_skinny_gated_against_float32(M, I, K, act):
 
 
 @pytest.mark.parametrize("M,K,nh,nkv,hd,page,writes", [(8, 2304, 8, 4, 256, 16, True), (3, 192, 5, 1, 48, 32, True),
-                                                        (1, 64, 2, 2, 16, 16, True), (7, 320, 6, 3, 80, 16, False)])
+                                                        (1, 64, 2, 2, 16, 16, True), (7, 320, 6, 3, 80, 16, False),
+                                                        (16, 2304, 8, 4, 256, 16, True), (11, 192, 3, 1, 48, 16, True)])
 def test_qkv_product_with_rotation_and_cache_write_in_one_kernel(M, K, nh, nkv, hd, page, writes):
     """Against float32 torch: the product, the turn of pairs (j, j + hd/2) by pos * theta^(-2j/hd), and
     the rows of the cache it writes; every other row of the pools stays as it was."""
