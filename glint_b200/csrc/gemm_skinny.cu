@@ -313,7 +313,7 @@ GLINT_API int glint_gemm_skinny(const void* x, const void* w, void* out, int out
   return (int)e;
 }
 
-// The q, k, v product of up to 8 tokens with the rotary encoding and the cache write in its
+// The q, k, v product of up to 16 tokens with the rotary encoding and the cache write in its
 // epilogue: x [M, K]; w [(nh + 2 nkv) * hd, K]; q_out [M, nh * hd]; pools [pages][nkv][page_size][hd]
 // (null: q only).  The whole head is rotated (pairs (j, j + hd / 2)); hd a multiple of 16.
 GLINT_API int glint_gemm_skinny_rope_supported(int M, int K, int hd) {
