@@ -358,3 +358,23 @@ def test_toy_routed_feed_forward_and_toy_position_encoding(tmp_path):
     assert (shifted[1:] - whole_a[:28]).abs().max().item() > 1e-3
     engine.close(sa); engine.close(sb)
     model.rt.check_status()
+
+
+def test_runtime_buffers_are_kept_per_role():
+    """``Runtime.buffer`` gives the same memory for a role again and again, different memory for
+    different roles, and keeps what a role has outgrown (captured launches may point into it)."""
+    from glint_b200.runtime import Runtime
+    rt = Runtime(DEV, "bfloat16")
+    a = rt.buffer("test.a", (8, 64))
+    b = rt.buffer("test.b", (8, 64))
+    assert a.dtype == torch.bfloat16 and a.shape == (8, 64) and a.data_ptr() != b.data_ptr()
+    assert rt.buffer("test.a", (8, 64)) is a                                  # the view itself is kept
+    assert rt.buffer("test.a", (4, 64)).data_ptr() == a.data_ptr()            # a smaller value: the same memory
+    f = rt.buffer("test.a", (8, 64), torch.float32)
+    assert f.dtype == torch.float32 and f.data_ptr() != a.data_ptr()          # another dtype: its own
+    a.fill_(3.0)
+    big = rt.buffer("test.a", (4096, 64))                                     # outgrown: new memory, the old is kept
+    assert big.data_ptr() != a.data_ptr() and any(t.data_ptr() == a.data_ptr() for t in rt._retired)
+    big.zero_()
+    assert float(a.float().sum()) == 3.0 * 8 * 64
+    assert rt.buffer("test.a", (8, 64)).data_ptr() == big.data_ptr()
