@@ -108,7 +108,7 @@ def cmd_inspect(args):
 def cmd_run(args):
     from .engine.api import LLM
     prompt = _ids(args.prompt)
-    llm = LLM(args.file, dtype=args.dtype, device=args.device)
+    llm = LLM(args.file, dtype=args.dtype, device=args.device, max_active=1)      # one prompt: a cache of four contexts
     print(f"Prompt: {prompt}")
     t0 = time.time()
     out = llm.generate(prompt, max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k,
@@ -122,7 +122,7 @@ def cmd_run(args):
 def cmd_generate(args):
     from .engine.api import LLM
     prompt = _ids(args.tokens)
-    llm = LLM(args.file, dtype=args.dtype, device=args.device)
+    llm = LLM(args.file, dtype=args.dtype, device=args.device, max_active=1)      # one prompt: a cache of four contexts
     out = llm.generate(prompt, max_tokens=args.max_tokens, temperature=0.0)
     print(f"Generated token ids: {prompt + out}")
     return 0

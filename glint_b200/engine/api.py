@@ -17,12 +17,28 @@ from .loading import build_engine, load_model, random_model
 from .scheduler import Request, Scheduler
 
 
+def default_cache_tokens(model, max_active, fraction=0.5):
+    """Room for ``max_active`` requests at full context, limited to ``fraction`` of the device memory
+    that is free now, and never below four contexts."""
+    import torch
+    from ..cache import PagedKVNeed
+    needs, cache_of = model.cache_needs()
+    width = 2 if model.rt.dtype == torch.bfloat16 else 4
+    per_token = sum(2 * n.num_kv_heads * n.head_dim * width
+                    for n, of in zip(needs, cache_of) if isinstance(n, PagedKVNeed) and of is None)
+    free, _ = torch.cuda.mem_get_info(model.rt.device)
+    fit = int(fraction * free) // max(per_token, 1)
+    contexts = model.spec.max_positions
+    return max(4 * contexts, min(max_active * contexts, fit))
+
+
 class LLM:
     """A loaded model ready to generate.
 
     ``model_path``: folder with config.json and model.safetensors.  ``dtype``: 'bfloat16' (the
     serving kernels) or 'float32' (everything in true 32-bit).  ``cache_tokens``: how many
-    tokens each cache group can hold in all (default: 4 contexts).  ``max_active``: requests
+    tokens each cache group can hold in all (default: a full context for every running request, as
+    far as half of the free device memory goes, and at least 4 contexts).  ``max_active``: requests
     running at a time.  ``max_step_tokens``: token budget of one step.  ``lookahead``: launch each
     decode step with the previous step's sampled tokens still on the device and read them one step
     late, so that the host's work overlaps the GPU's (same tokens as without it).
@@ -36,7 +52,7 @@ class LLM:
             raise ValueError(str(e)) from e
         spec = self.model.spec
         if cache_tokens is None:
-            cache_tokens = 4 * spec.max_positions
+            cache_tokens = default_cache_tokens(self.model, max_active)
         self.engine = build_engine(self.model, cache_tokens, num_slots=max_active, page_size=page_size)
         self.sampler = DeviceSampler(self.model.rt, spec.vocab_size)
         self.scheduler = Scheduler(self.engine, self.sampler, max_step_tokens=max_step_tokens,
