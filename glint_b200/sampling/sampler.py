@@ -206,15 +206,17 @@ class DeviceSampler:
         up to date)."""
         rows = logits.shape[0]
         dev = logits.device
-        chosen = torch.empty(rows, dtype=torch.int32, device=dev)
-        ops.argmax(logits, chosen)
-        if all(p.greedy for p in params):
-            return chosen
+        some_greedy = any(p.greedy for p in params)
+        if some_greedy:
+            chosen = torch.empty(rows, dtype=torch.int32, device=dev)
+            ops.argmax(logits, chosen)
+            if all(p.greedy for p in params):
+                return chosen
         opt, top_k = self._options(params, rngs, dev)
         penalties = self._penalties(params, histories, opt[4], dev)
         drawn = torch.empty(rows, dtype=torch.int32, device=dev)
         ops.sample_rows(logits, self._scratch(rows), opt[0], top_k, opt[2], opt[3], opt[1], drawn, penalties)
-        return torch.where(opt[5] > 0, drawn, chosen)
+        return torch.where(opt[5] > 0, drawn, chosen) if some_greedy else drawn
 
     def sample(self, logits, params, rngs, histories):
         """The same with the tokens brought to the host: a list of ints."""
