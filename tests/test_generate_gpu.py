@@ -137,6 +137,33 @@ def test_all_sampling_options_with_and_without_lookahead(folders):
     assert agree >= 16, (agree, outs[0][2])
 
 
+def test_sampling_over_a_wide_vocabulary_follows_the_plain_sampler(tmp_path):
+    """A vocabulary of 20011 entries takes the sampling kernel that shares a row among the blocks of a
+    cluster; with top-k the distribution is peaked enough for the plain sampler to agree token by token."""
+    from glint_b200 import LLM
+    from glint_b200.weights import write_random_model
+    cfg = dict(TINY["A"][0], vocab_size=20011)
+    folder = os.path.join(str(tmp_path), "wide_vocab")
+    write_random_model(dict(cfg), folder, seed=4, std=0.05, norm_std=0.1)
+    prompts = [random_tokens(n, cfg["vocab_size"], 70 + i) for i, n in enumerate([12, 3])]
+    opts = dict(temperature=0.9, top_k=6, top_p=0.95, repeat_penalty=1.2)
+    llm = LLM(folder, dtype="float32", cache_tokens=512, max_active=2)
+    got = llm.generate(prompts, max_tokens=16, seed=9, stop_at_eos=False, **opts)
+    assert got == llm.generate(prompts, max_tokens=16, seed=9, stop_at_eos=False, **opts)
+    pcfg, w = plain.read_config(folder), plain.read_weights(folder)
+    for r, prompt in enumerate(prompts):
+        rng = psampler.Xorshift64(9 + r)
+        toks = list(prompt)
+        agree = 0
+        for i in range(16):
+            t = psampler.sample(plain.forward(pcfg, w, toks)[-1].numpy(), toks, rng, **opts)
+            if t != got[r][i]:
+                break
+            agree += 1
+            toks.append(t)
+        assert agree >= 14, (r, agree, got[r])
+
+
 def test_small_cache_preempts_and_still_gives_the_same_tokens(folders):
     from glint_b200 import LLM
     vocab = TINY["A"][0]["vocab_size"]
