@@ -645,6 +645,44 @@ def test_sampling_of_wide_rows_by_a_cluster(V):
         assert got[5] == int(torch.argmax(logits[5]))                      # top_k = 1
 
 
+@pytest.mark.parametrize("V", [16384, 100003, 256000])
+def test_sampling_of_wide_rows_at_the_edges(V):
+    """Rows that leave the usual paths of the cluster kernel: equal logits everywhere (every element is a
+    tie at the threshold; thousands of candidates in one bin), one finite logit, none, one dominant
+    logit, two equal maxima under top_k = 1, a tiny temperature, a large top-k."""
+    from glint_b200 import ops
+
+    def run(logits, temp=1.0, k=0, p=1.0, mp=0.0, u=0.5):
+        rows = logits.shape[0]
+        f32 = lambda v: torch.full((rows,), v, dtype=torch.float32, device=DEV)
+        out = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
+        ops.sample_rows(logits.to(DEV).contiguous(), torch.empty(rows, V, device=DEV), f32(temp),
+                        torch.full((rows,), k, dtype=torch.int32, device=DEV), f32(p), f32(mp), f32(u), out)
+        return out.tolist()
+
+    near = lambda want: (lambda g: abs(g - want) <= max(2, V // 2000))
+    flat = torch.zeros(2, V)
+    assert all(map(near(V // 2), run(flat, u=0.5)))
+    assert all(map(near(V // 4), run(flat, k=10, u=0.25)))                 # ties at the k-th value are all kept
+    assert all(map(near(V), run(flat, p=0.5, u=0.9999)))                   # and at the top-p boundary
+    one = torch.full((2, V), float("-inf"))
+    one[:, V - 3] = 1.0
+    assert run(one, k=5, p=0.9, u=0.7) == [V - 3, V - 3]
+    assert all(map(near(V // 2), run(torch.full((2, V), float("-inf")), u=0.5)))   # nothing finite: uniform
+    torch.manual_seed(V)
+    dom = torch.randn(2, V)
+    dom[:, 77] = 60.0
+    assert run(dom, temp=0.7, p=0.9, u=0.9999) == [77, 77]
+    two = torch.randn(2, V)
+    two[:, 5] = two[:, V - 9] = 30.0
+    assert run(two, k=1, u=0.4) == [5, 5] and run(two, k=1, u=0.6) == [V - 9, V - 9]
+    spread = torch.randn(2, V) * 3
+    assert run(spread, temp=1e-3, u=0.3) == spread.argmax(1).tolist()
+    kth = torch.topk(spread, 3000, dim=1).values[:, -1]
+    got = run(spread, k=3000, u=0.99999)
+    assert all(spread[r, g] >= kth[r] for r, g in enumerate(got)), got
+
+
 def test_repeat_penalty_kernel():
     from glint_b200 import ops
     V = 64
