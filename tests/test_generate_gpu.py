@@ -181,6 +181,19 @@ def test_small_cache_preempts_and_still_gives_the_same_tokens(folders):
         tight.generate([vocab + 5], max_tokens=3)
 
 
+def test_small_cache_with_sampling_and_repeat_penalty(folders):
+    """Requests that lose their pages and start over keep their generator and their token counts: the
+    sampled tokens are those of a roomy cache."""
+    from glint_b200 import LLM
+    vocab = TINY["A"][0]["vocab_size"]
+    prompts = [random_tokens(n, vocab, 60 + i) for i, n in enumerate([30, 28, 35, 20])]
+    opts = dict(max_tokens=20, stop_at_eos=False, temperature=0.8, top_k=8, repeat_penalty=1.4, seed=5)
+    want = LLM(folders["A"], dtype="float32", cache_tokens=1024, max_active=4).generate(prompts, **opts)
+    tight = LLM(folders["A"], dtype="float32", cache_tokens=96, max_active=4, max_step_tokens=48)
+    assert tight.generate(prompts, **opts) == want
+    assert tight.scheduler.counters["preemptions"] >= 1 or any(s["reuses"] > 0 for s in tight.cache_stats().values())
+
+
 def test_eos_stops_and_is_delivered(folders, tmp_path):
     from glint_b200 import LLM
     vocab = TINY["A"][0]["vocab_size"]
