@@ -28,24 +28,98 @@ import torch
 from ..errors import GlintError, PagePoolExhausted, SlotsExhausted
 
 
+class PagedNeed:
+    """What a mixer that keeps something per token declares.  The cache manager asks only this of
+    a declaration, so a mixer that caches something else than keys and values of one shape (one
+    latent vector per token, keys and values of different widths) brings a class of its own:
+
+    * ``paged`` is True; ``window`` is ``None`` (every position is kept) or the number of last
+      positions a later token can still reach (pages behind it are given back);
+    * ``group_key()``: hashable; layers with equal keys share one pool of pages and one block
+      table per request;
+    * ``allocate(layers, num_pages, page_size, dtype, device)``: the device storage of a group
+      with that many member layers, in whatever form ``view`` understands;
+    * ``view(storage, layer)``: what the mixer of member ``layer`` gets as its ``view`` (the
+      manager adds ``group``, ``page_size``, ``num_pages`` and ``writes`` to it);
+    * ``bytes_per_token(element_size)``: bytes one token takes in one layer;
+    * ``readable_by(other)``: whether a layer declaring ``other`` may read this layer's cache.
+    """
+    paged = True
+    window = None
+
+    def group_key(self):
+        raise NotImplementedError
+
+    def group_name(self):
+        return str(self.group_key())
+
+    def allocate(self, layers, num_pages, page_size, dtype, device):
+        raise NotImplementedError
+
+    def view(self, storage, layer):
+        raise NotImplementedError
+
+    def bytes_per_token(self, element_size):
+        raise NotImplementedError
+
+    def readable_by(self, other):
+        return self.group_key() == other.group_key()
+
+
+class LayerView:
+    """One member layer's part of a group's storage; the need's ``view`` fills in its tensors."""
+
+
 @dataclass(frozen=True)
-class PagedKVNeed:
-    """A mixer's declaration: keys and values of every position (``window`` None) or of the
-    last ``window`` positions, ``num_kv_heads`` x ``head_dim`` each."""
+class PagedKVNeed(PagedNeed):
+    """Keys and values of every position (``window`` None) or of the last ``window`` positions,
+    ``num_kv_heads`` x ``head_dim`` each, as ``[layers][pages][kv heads][page][head_dim]``."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+
+    def group_key(self):
+        return (self.num_kv_heads, self.head_dim, self.window)
 
     def group_name(self):
         w = "all" if self.window is None else f"window{self.window}"
         return f"kv{self.num_kv_heads}x{self.head_dim}/{w}"
 
+    def allocate(self, layers, num_pages, page_size, dtype, device):
+        shape = (layers, num_pages, self.num_kv_heads, page_size, self.head_dim)
+        return (torch.zeros(shape, dtype=dtype, device=device), torch.zeros(shape, dtype=dtype, device=device))
+
+    def view(self, storage, layer):
+        v = LayerView()
+        v.k, v.v = storage[0][layer], storage[1][layer]
+        return v
+
+    def bytes_per_token(self, element_size):
+        return 2 * self.num_kv_heads * self.head_dim * element_size
+
+    def readable_by(self, other):
+        return (getattr(other, "num_kv_heads", None), getattr(other, "head_dim", None)) == (self.num_kv_heads, self.head_dim)
+
 
 @dataclass(frozen=True)
 class SlotStateNeed:
-    """A mixer's declaration: one tensor of ``shape`` and ``dtype`` per request, zero at admission."""
+    """A mixer's declaration of a state of fixed size: one tensor of ``shape`` and ``dtype`` per
+    request, zero at admission.  ``allocate(num_slots, device)`` makes the rows of all slots."""
     shape: tuple
     dtype: torch.dtype = torch.float32
+    paged = False
+
+    def allocate(self, num_slots, device):
+        return torch.zeros((num_slots,) + tuple(self.shape), dtype=self.dtype, device=device)
+
+
+def is_paged(need):
+    return need is not None and bool(getattr(need, "paged", False))
+
+
+def cache_bytes_per_token(needs, cache_of, element_size):
+    """Bytes one token takes in all layers that keep pages of their own."""
+    return sum(n.bytes_per_token(element_size) for n, of in zip(needs, cache_of) if is_paged(n) and of is None)
 
 
 class PagePool:
@@ -104,15 +178,14 @@ class PagedGroup:
         self.num_pages = num_pages
         self.max_pages = (max_positions + page_size - 1) // page_size
         self.pool = PagePool(self.name, num_pages)
-        shape = (len(self.members), num_pages, need.num_kv_heads, page_size, need.head_dim)
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.element_size = torch.empty((), dtype=dtype).element_size()
+        self.storage = need.allocate(len(self.members), num_pages, page_size, dtype, device)
         self.table = np.full((num_slots, self.max_pages), -1, dtype=np.int32)
         self.first_live = np.zeros(num_slots, dtype=np.int64)   # first page index still held
         self.end_live = np.zeros(num_slots, dtype=np.int64)     # one past the last page held
 
     def bytes_per_token(self):
-        return 2 * len(self.members) * self.need.num_kv_heads * self.need.head_dim * self.k.element_size()
+        return len(self.members) * self.need.bytes_per_token(self.element_size)
 
     # pages that queries at positions >= start can still reach begin at this page index
     def _first_needed_page(self, start):
@@ -161,16 +234,16 @@ class PagedGroup:
         return [int(p) for p in self.table[slot] if p >= 0]
 
 
-class CacheView:
-    """What one run-order entry's mixer sees of a paged group: its own layer of the storage."""
-
-    def __init__(self, group, layer_in_group, writes):
-        self.group = group
-        self.k = group.k[layer_in_group]
-        self.v = group.v[layer_in_group]
-        self.page_size = group.page_size
-        self.num_pages = group.num_pages
-        self.writes = writes           # False when the entry reads another entry's cache
+def CacheView(group, layer_in_group, writes):
+    """What one run-order entry's mixer sees of a paged group: its own layer of the storage, as the
+    group's declaration lays it out, with the group, the page geometry and whether it writes."""
+    view = group.need.view(group.storage, layer_in_group)
+    view.group = group
+    view.layer_in_group = layer_in_group
+    view.page_size = group.page_size
+    view.num_pages = group.num_pages
+    view.writes = writes           # False when the entry reads another entry's cache
+    return view
 
 
 class CacheManager:
@@ -192,31 +265,43 @@ class CacheManager:
         self.groups = []
         self.views = [None] * len(needs)
         self.states = [None] * len(needs)
-        by_need = {}
+        by_key = {}
         for i, need in enumerate(needs):
-            if isinstance(need, PagedKVNeed) and cache_of[i] is None:
-                by_need.setdefault(need, []).append(i)
+            if is_paged(need) and cache_of[i] is None:
+                by_key.setdefault(need.group_key(), (need, []))[1].append(i)
         placed = {}
-        for need, members in by_need.items():
+        for need, members in by_key.values():
             g = PagedGroup(need, members, num_pages, num_slots, page_size, max_positions, dtype, device)
             self.groups.append(g)
             for j, i in enumerate(members):
                 placed[i] = (g, j)
                 self.views[i] = CacheView(g, j, writes=True)
         for i, need in enumerate(needs):
-            if isinstance(need, PagedKVNeed) and cache_of[i] is not None:
+            if is_paged(need) and cache_of[i] is not None:
                 src = cache_of[i]
                 if src not in placed:
                     raise GlintError(f"run-order entry {i} reads the cache of entry {src}, which owns none")
                 g, j = placed[src]
-                if (g.need.num_kv_heads, g.need.head_dim) != (need.num_kv_heads, need.head_dim):
+                if not g.need.readable_by(need):
                     raise GlintError(f"run-order entry {i} cannot read the cache of entry {src}: shapes differ")
                 self.views[i] = CacheView(g, j, writes=False)
-            elif isinstance(need, SlotStateNeed):
-                self.states[i] = torch.zeros((num_slots,) + tuple(need.shape), dtype=need.dtype, device=device)
+            elif need is not None and not is_paged(need):
+                self.states[i] = need.allocate(num_slots, device)
+        self.named_states = {}
         self._free_slots = list(range(num_slots - 1, -1, -1))
         self._slot_live = [False] * num_slots
         self.lengths = np.zeros(num_slots, dtype=np.int64)
+
+    def add_state(self, name, need):
+        """A fixed-size record per request slot for something beside the mixers (the sampler keeps the
+        request's options, generator state, position and count there): ``need`` is a ``SlotStateNeed``;
+        the rows are zero when a request takes its slot.  Returns the tensor [slots, *shape]."""
+        if name in self.named_states:
+            return self.named_states[name]
+        if any(self._slot_live):
+            raise GlintError(f"state '{name}' must be declared before requests are admitted")
+        st = self.named_states[name] = need.allocate(self.num_slots, self.device)
+        return st
 
     # ---- slots ----------------------------------------------------------------------------------
 
@@ -230,7 +315,7 @@ class CacheManager:
         slot = self._free_slots.pop()
         self._slot_live[slot] = True
         self.lengths[slot] = 0
-        for st in self.states:
+        for st in list(self.states) + list(self.named_states.values()):
             if st is not None:
                 st[slot].zero_()
         return slot

@@ -23,10 +23,13 @@ class PartSpec:
 
 @dataclass
 class BlockSpec:
-    """One layer: a mixer and a feed-forward, each between optional norms.
+    """One layer: a mixer, a feed-forward and up to four norms, arranged by the block class that
+    ``kind`` names in the ``"block"`` registry.
 
-    ``x = x + post_mixer_norm(mixer(pre_mixer_norm(x)))`` then the same shape for the
-    feed-forward; a norm that is ``None`` is the identity.
+    The package's kind ``"sandwich"`` computes ``x = x + post_mixer_norm(mixer(pre_mixer_norm(x)))``
+    and then the same shape for the feed-forward; a norm that is ``None`` is the identity.  Another
+    arrangement (a parallel residual, a shared norm) is another kind, which reads the same fields
+    and its own ``params``.
     """
     mixer: PartSpec
     feed_forward: PartSpec
@@ -34,6 +37,8 @@ class BlockSpec:
     post_mixer_norm: Optional[PartSpec] = None
     pre_ffn_norm: Optional[PartSpec] = None
     post_ffn_norm: Optional[PartSpec] = None
+    kind: str = "sandwich"
+    params: dict = field(default_factory=dict)
 
 
 @dataclass

@@ -260,7 +260,7 @@ using namespace glint;
 // Every pass of a warp over its steps costs one memory latency.  When the blocks fill the SMs at
 // most once, a block has 12 or 16 warps, whichever makes the passes fewest and leaves the fewest
 // step slots empty: more bytes in flight per SM.  With more blocks than that, small blocks (8
-// warps) pack the SMs better.  GLINT_SKINNY_WARPS in the environment overrides the choice.
+// warps) pack the SMs better.
 static int skinny_warps(int U, int n_steps, int n_blocks) {
   int device = 0, sms = 148;
   if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
@@ -274,12 +274,6 @@ static int skinny_warps(int U, int n_steps, int n_blocks) {
       }
     }
   }
-  static int forced = -1;
-  if (forced < 0) {
-    const char* e = getenv("GLINT_SKINNY_WARPS");
-    forced = e ? atoi(e) : 0;
-  }
-  if (forced >= 1 && forced <= SK_MAX_WARPS) warps = forced;
   return warps;
 }
 

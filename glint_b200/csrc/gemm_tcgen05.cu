@@ -9,13 +9,19 @@
 // feature, each column one token; a lane's K-loop order is fixed by K and the split factor
 // alone, never by which tokens share the launch.
 //
-// Roles in a block of 192 threads: warp 0 issues TMA loads into a ring of shared-memory
-// stages, warp 1 allocates tensor memory and issues the MMAs, warps 2..5 read the accumulator
-// back and write the result.  When a launch has too few tiles to fill the GPU the K range is
-// split over blockIdx.z; partial tiles go to a workspace and the block that arrives last at
-// the tile's counter adds them in split order (no spinning, deterministic) and resets the
-// counter.  Epilogues: soft cap (output head), or with two weight tiles per stage
-// (gate rows and up rows of the same features) act(gate) * up written as bfloat16.
+// Roles in a block: warp 0 issues TMA loads into a ring of shared-memory stages, warp 1 allocates
+// tensor memory and issues the MMAs, the other warps read the accumulator back and write the
+// result: four of them (192 threads) for token tiles narrower than 64 columns, eight (320
+// threads, two per quarter of the accumulator lanes on alternate groups of 16 columns) from 64
+// columns on.  When a launch has too few tiles to fill the GPU the K range is split over
+// blockIdx.z and partial tiles go to a workspace.  If every block of the launch is on an SM at
+// once, all blocks of a tile wait for one another at the tile's counter (a spin with a limit,
+// after which the status word is set) and each adds up a share of the tile's columns;
+// otherwise the block that arrives last adds up all of them.  Both add the splits in order, so
+// the result is deterministic.  Epilogues: soft cap (output head); with two weight tiles per
+// stage (gate rows and up rows of the same features) act(gate) * up written as bfloat16; two
+// plain tiles side by side for products with more 128-feature tiles than SMs; and, for the
+// q/k/v product, rotary encoding with the cache write.
 #include <stdlib.h>
 
 #include <mutex>
@@ -733,13 +739,7 @@ static int gemm_launch(const void* x, const void* w, void* out, int out_bf16, in
   if (rope) p.rope = *rope;
   else p.rope = RopeEpilogue{};
   p.M = M; p.N = N; p.K = K;
-  int bn_max = 256;
-  if (rope) bn_max = rope->bn;
-  else {
-    static int env_bn = -1;        // the environment is read once
-    if (env_bn < 0) { const char* ov = getenv("GLINT_GEMM_BN"); env_bn = ov ? atoi(ov) : 0; }
-    if (env_bn >= 16 && env_bn <= 256 && env_bn % 16 == 0) bn_max = env_bn;
-  }
+  const int bn_max = rope ? rope->bn : 256;
   const int m_tiles_256 = (M + bn_max - 1) / bn_max;
   int bn = ((M + m_tiles_256 - 1) / m_tiles_256 + 15) / 16 * 16;
   if (dual && bn > 256) bn = 256;
@@ -748,17 +748,16 @@ static int gemm_launch(const void* x, const void* w, void* out, int out_bf16, in
   int n_tiles = rope ? N / (2 * GEMM_BM) : (N + GEMM_BM - 1) / GEMM_BM;
   // A plain product whose 128-feature tiles would need more than one wave, and whose 256-feature
   // tiles still fill three quarters of the SMs, runs as the dual kernel with two plain tiles.
-  static int sms = 0, wide_on = -1;
+  static int sms = 0;
   if (sms == 0) {
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess ||
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
       sms = 148;
   }
-  if (wide_on < 0) { const char* ev = getenv("GLINT_GEMM_WIDE"); wide_on = ev ? atoi(ev) : 1; }
   const int n_tiles_wide = (N + 2 * GEMM_BM - 1) / (2 * GEMM_BM);
   p.wide = 0;
-  if (wide_on && !dual && !rope && force_splits <= 1 && bn == 256 && (long long)n_tiles * m_tiles > sms &&
+  if (!dual && !rope && force_splits <= 1 && bn == 256 && (long long)n_tiles * m_tiles > sms &&
       (long long)n_tiles_wide * m_tiles * 4 >= 3LL * sms) {
     p.wide = 1;
     dual = 1;
@@ -768,20 +767,15 @@ static int gemm_launch(const void* x, const void* w, void* out, int out_bf16, in
   const int stage_bytes = A_STAGE_BYTES * (dual ? 2 : 1) + bn * GEMM_BK * 2;
   int stages = (227 * 1024 - 1024 - (int)sizeof(GemmShared) - 256) / stage_bytes;
   if (stages > GEMM_MAX_STAGES) stages = GEMM_MAX_STAGES;
-  static int env_stages = -1;
-  if (env_stages < 0) { const char* ov = getenv("GLINT_GEMM_STAGES"); env_stages = ov ? atoi(ov) : 0; }
-  if (env_stages >= 2 && env_stages < stages) stages = env_stages;
   if (stages < 2) return GLINT_ERR_UNSUPPORTED_SIZE;
   p.stages = stages;
   p.total_kb = (K + GEMM_BK - 1) / GEMM_BK;
   const int tiles = m_tiles * n_tiles;
-  static int spread_on = -1;
-  if (spread_on < 0) { const char* ev = getenv("GLINT_GEMM_SPREAD"); spread_on = ev ? atoi(ev) : 1; }
   int splits = 1;
   if (force_splits > 0) {
     splits = force_splits;
-  } else if (tiles <= 74) {
-    // One wave of at most 148 blocks.  Estimated time (microseconds, fitted to measurements): the
+  } else if (2 * tiles <= sms) {
+    // At most half a wave of tiles: a split of K puts the other SMs to work.  Estimated time (microseconds, fitted to measurements): the
     // K blocks a block streams at ~0.3 each, plus for a split launch the reduction through the
     // workspace, which grows with the splits and the width of the token tile.
     const int width = bn * (dual ? 2 : 1);
@@ -789,7 +783,7 @@ static int gemm_launch(const void* x, const void* w, void* out, int out_bf16, in
     for (int cand = 1; cand <= 32 && tiles * cand <= sms && cand <= p.total_kb; ++cand) {
       const int per = (p.total_kb + cand - 1) / cand;
       // spread over the tile's blocks, the reduction costs the wait for the slowest block and one tile's worth of reads
-      const float reduce = spread_on ? 4.0f + 0.04f * width : 1.5f + 0.04f * width * cand;
+      const float reduce = 4.0f + 0.04f * width;
       const float kb_us = fmaxf(0.3f, 0.0015f * width);       // a K block: instruction-bound for narrow tiles, tensor-bound for wide ones
       const float est = kb_us * per + (cand > 1 ? reduce : 0.f);
       if (est < best) {
@@ -808,7 +802,7 @@ static int gemm_launch(const void* x, const void* w, void* out, int out_bf16, in
     p.kb_per_split = p.total_kb;
   }
   p.splits = splits;
-  p.spread = (spread_on && splits > 1 && (long long)tiles * splits <= sms && tiles <= GEMM_SPREAD_DEPARTED) ? 1 : 0;
+  p.spread = (splits > 1 && (long long)tiles * splits <= sms && tiles <= GEMM_SPREAD_DEPARTED) ? 1 : 0;
   p.dual_offset = dual_offset;
   p.act = act;
   p.cap = cap;
@@ -830,15 +824,11 @@ static int gemm_launch(const void* x, const void* w, void* out, int out_bf16, in
   CUtensorMap map_out = map_x;
   const int es = out_bf16 ? 2 : 4;
   p.tma_store = 0;
-  static int tma_store_on = -1;
-  if (tma_store_on < 0) { const char* ev = getenv("GLINT_GEMM_TMA_STORE"); tma_store_on = ev ? atoi(ev) : 1; }
-  if (tma_store_on && !p.wide && !rope && out_bf16 && splits == 1 && bn >= 64 && ((long long)N * es) % 16 == 0 && ((uintptr_t)out & 15) == 0 &&
+  if (!p.wide && !rope && out_bf16 && splits == 1 && bn >= 64 && ((long long)N * es) % 16 == 0 && ((uintptr_t)out & 15) == 0 &&
       (long long)bn * GEMM_BM * es <= (long long)stages * stage_bytes) {
     if (cached_map(&map_out, out, M, N, bn, GEMM_BM, out_bf16 ? 1 : 2) == GLINT_OK) p.tma_store = 1;
   }
-  static int wide_epilogue = -1;
-  if (wide_epilogue < 0) { const char* ev = getenv("GLINT_GEMM_EPILOGUE_WARPS"); wide_epilogue = ev ? (atoi(ev) >= 8) : 1; }
-  const int threads = (wide_epilogue && bn * (dual ? 2 : 1) >= 64) ? GEMM_THREADS_WIDE : GEMM_THREADS;
+  const int threads = bn * (dual ? 2 : 1) >= 64 ? GEMM_THREADS_WIDE : GEMM_THREADS;
   dim3 grid(n_tiles * m_tiles, 1, splits);
   cudaError_t e;
   // the shared-memory limit of each kernel is raised once, to the most a launch may ask for

@@ -791,6 +791,52 @@ sample_wide_kernel(const float* __restrict__ src, long long src_stride, int V, i
   cluster_sync();   // nobody leaves while its shared memory may still be read
 }
 
+// ---------------------------------------------------------------------------------------------
+// The per-request record of the sampler, one row of SAMPLER_RECORD 32-bit words per request slot:
+//   0 temperature  1 top-p  2 min-p  3 repeat penalty (floats)   4 top-k   5 1 if the request is not greedy
+//   6, 7 the low and high word of its xorshift64 generator's state
+//   8 the position of its newest token + 1   9 how many tokens have been chosen for it
+// Words 0 to 7 are written by the host when the request takes the slot; this kernel keeps 6 to 9 up to
+// date on the device.  For each row of a step that is about to be sampled it copies the row's options into
+// per-row arrays (the layout the sampling kernels read) and, for a row that is not greedy, advances the
+// generator (s ^= s << 13; s ^= s >> 7; s ^= s << 17; uniform from the upper 24 bits:
+// src/sampling/sampler.rs:35-70) and hands the draw over.  The reference keeps position and generator
+// with the session (src/session/mod.rs:86, src/sampling/sampler.rs:35-37).
+// row_opts: [7][stride] floats: temperature, uniform, top-p, min-p, penalty, not-greedy, top-k (int bits).
+// ---------------------------------------------------------------------------------------------
+constexpr int SAMPLER_RECORD = 10;
+
+__global__ void sample_prepare_kernel(int* __restrict__ records, const int* __restrict__ row_slots,
+                                      const int* __restrict__ positions, const int* __restrict__ logit_rows,
+                                      int rows, int num_slots, float* __restrict__ row_opts, int stride) {
+  pdl_wait();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const int slot = row_slots[r];
+  if (slot < 0 || slot >= num_slots) return;
+  int* rec = records + (size_t)slot * SAMPLER_RECORD;
+  const bool draws = rec[5] != 0;
+  float uniform = 0.f;
+  if (draws) {
+    unsigned long long x = (unsigned long long)(unsigned)rec[6] | ((unsigned long long)(unsigned)rec[7] << 32);
+    x ^= x << 13;
+    x ^= x >> 7;
+    x ^= x << 17;
+    rec[6] = (int)(unsigned)(x & 0xffffffffull);
+    rec[7] = (int)(unsigned)(x >> 32);
+    uniform = (float)(x >> 40) / 16777216.0f;
+  }
+  rec[8] = positions[logit_rows[r]] + 1;
+  rec[9] += 1;
+  row_opts[0 * stride + r] = draws ? __int_as_float(rec[0]) : 1.0f;
+  row_opts[1 * stride + r] = uniform;
+  row_opts[2 * stride + r] = __int_as_float(rec[1]);
+  row_opts[3 * stride + r] = __int_as_float(rec[2]);
+  row_opts[4 * stride + r] = __int_as_float(rec[3]);
+  row_opts[5 * stride + r] = draws ? 1.0f : 0.0f;
+  reinterpret_cast<int*>(row_opts)[6 * stride + r] = rec[4];
+}
+
 }  // namespace glint
 
 using namespace glint;
@@ -873,4 +919,17 @@ GLINT_API int glint_sample_rows(const float* logits, long long row_stride, float
   sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(src, stride, work, V, temperature, top_k, top_p, min_p, uniform,
                                                      out);
   return (int)cudaGetLastError();
+}
+
+GLINT_API int glint_sampler_record_words() { return SAMPLER_RECORD; }
+
+// Before the rows of a step are sampled: options from the slots' records into per-row arrays, the
+// generators of the rows that draw advanced by one, position and count brought up to date.
+GLINT_API int glint_sample_prepare(int* records, const int* row_slots, const int* positions, const int* logit_rows,
+                                   int rows, int num_slots, float* row_opts, int stride, cudaStream_t stream) {
+  if (rows <= 0) return GLINT_OK;
+  if (!records || !row_slots || !positions || !logit_rows || !row_opts || stride < rows) return GLINT_ERR_BAD_ARG;
+  const cudaError_t e = launch_kernel(sample_prepare_kernel, dim3((rows + 127) / 128), dim3(128), 0, stream, records,
+                                      row_slots, positions, logit_rows, rows, num_slots, row_opts, stride);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }

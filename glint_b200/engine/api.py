@@ -20,12 +20,9 @@ from .scheduler import Request, Scheduler
 def default_cache_tokens(model, max_active, fraction=0.5):
     """Room for ``max_active`` requests at full context, limited to ``fraction`` of the device memory
     that is free now, and never below four contexts."""
-    import torch
-    from ..cache import PagedKVNeed
+    from ..cache import cache_bytes_per_token
     needs, cache_of = model.cache_needs()
-    width = 2 if model.rt.dtype == torch.bfloat16 else 4
-    per_token = sum(2 * n.num_kv_heads * n.head_dim * width
-                    for n, of in zip(needs, cache_of) if isinstance(n, PagedKVNeed) and of is None)
+    per_token = cache_bytes_per_token(needs, cache_of, torch.empty((), dtype=model.rt.dtype).element_size())
     free, _ = torch.cuda.mem_get_info(model.rt.device)
     fit = int(fraction * free) // max(per_token, 1)
     contexts = model.spec.max_positions
@@ -54,7 +51,7 @@ class LLM:
         if cache_tokens is None:
             cache_tokens = default_cache_tokens(self.model, max_active)
         self.engine = build_engine(self.model, cache_tokens, num_slots=max_active, page_size=page_size)
-        self.sampler = DeviceSampler(self.model.rt, spec.vocab_size)
+        self.sampler = DeviceSampler(self.model.rt, spec.vocab_size, self.engine.cache)
         self.scheduler = Scheduler(self.engine, self.sampler, max_step_tokens=max_step_tokens,
                                    max_active=max_active, lookahead=lookahead)
         self.eos_token_id = spec.eos_token_id

@@ -7,7 +7,7 @@ embedding, the layers of the run order, final norm and output head at the wanted
 """
 from __future__ import annotations
 
-from ..parts import Block, build_part
+from ..parts import build_block, build_part
 
 
 class CausalLM:
@@ -16,7 +16,7 @@ class CausalLM:
         self.spec = spec
         self.rt = rt
         self.embedding = build_part("embedding", spec.embedding, rt)
-        self.blocks = [Block(rt, b) for b in spec.blocks]
+        self.blocks = [build_block(b, rt) for b in spec.blocks]
         self.final_norm = build_part("norm", spec.final_norm, rt)
         self.head = build_part("head", spec.head, rt)
         self.run_order = list(spec.run_order)
@@ -59,11 +59,32 @@ class CausalLM:
             total += sum(p.parameter_bytes() for p in self.blocks[call.layer].parts())
         return total
 
+    def flops(self, portions, logit_rows=1):
+        """Floating-point operations of one step that runs ``portions`` = [(start, n)] (``n`` tokens of
+        a request that has ``start`` tokens cached) and computes ``logit_rows`` rows of logits: the
+        parts' matrix products and their mixers' work over the cache."""
+        tokens = sum(n for _, n in portions)
+        total = self.head.flops(logit_rows)
+        for call in self.run_order:
+            for p in self.blocks[call.layer].parts():
+                total += p.flops(tokens)
+                total += sum(p.attention_flops(start, n) for start, n in portions)
+        return total
+
+    def decode_read_bytes(self, positions, element_size):
+        """Bytes a step of one token per request has to read: every weight once, and what each
+        request's mixers read of the cache (the tokens stand at ``positions``)."""
+        total = self.parameter_bytes()
+        for call in self.run_order:
+            for p in self.blocks[call.layer].parts():
+                total += sum(p.cache_read_bytes(pos, element_size) for pos in positions)
+        return total
+
     # ---- cache --------------------------------------------------------------------------------
 
     def cache_needs(self):
         """Per run-order entry: the mixer's declaration, and the entry whose cache it reads."""
-        needs = [self.blocks[c.layer].mixer.cache_need() for c in self.run_order]
+        needs = [self.blocks[c.layer].cache_need() for c in self.run_order]
         return needs, [c.cache_of for c in self.run_order]
 
     # ---- forward ------------------------------------------------------------------------------
@@ -77,9 +98,9 @@ class CausalLM:
         for i, call in enumerate(self.run_order):
             block = self.blocks[call.layer]
             last = i + 1 == n
-            next_norm = None if last else self.blocks[self.run_order[i + 1].layer].pre_mixer_norm
+            next_norm = None if last else self.blocks[self.run_order[i + 1].layer].entry_norm()
             normed = block.forward(x, normed, ctx, cache.views[i], cache.states[i], next_norm,
-                                   want_next=not last)
+                                   want_next=next_norm is not None)
         if ctx.num_logit_rows == 0:
             return None
         if self.final_norm is not None:

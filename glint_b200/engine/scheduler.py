@@ -47,7 +47,7 @@ class Request:
     slot: Optional[int] = None
     computed: int = 0            # tokens of prompt + output that are in the cache
     preemptions: int = 0
-    rng: Optional[Xorshift64] = None
+    rng_state: Optional[int] = None   # state of its xorshift64 generator when it takes a slot (the device advances it)
     order: int = 0
     unresolved: int = 0          # 1 while the newest token is still only on the device
     pending_index: int = 0       # its place among the tokens sampled by that step
@@ -87,8 +87,10 @@ class Request:
 
 
 class Scheduler:
-    """``engine`` offers ``open()``, ``close(slot)``, ``step(entries) -> logits`` and ``cache``;
-    ``sampler.sample(logits, params, rngs, histories) -> tokens``."""
+    """``engine`` offers ``open()``, ``close(slot)``, ``step(entries) -> logits``, ``cache`` and
+    ``last_ctx`` (the context of the step that ran last); ``sampler.sample(logits, ctx, params,
+    histories) -> tokens``.  A sampler that keeps per-request state in the slots also offers
+    ``admit(slot, params, rng_state, position, generated)`` and ``generator_state(slot)``."""
 
     def __init__(self, engine, sampler, max_step_tokens=2048, max_active=None, context_length=None,
                  lookahead=False):
@@ -96,7 +98,7 @@ class Scheduler:
         self.sampler = sampler
         # With ``lookahead`` the next step is launched with the sampled tokens still on the device,
         # and the host reads them one step late (EOS is then seen one step late: the extra row is
-        # discarded).  Needs a sampler with ``sample_device(logits, params, rngs, histories)``.
+        # discarded).  Needs a sampler with ``sample_device(logits, ctx, params, histories)``.
         self.lookahead = bool(lookahead) and hasattr(sampler, "sample_device")
         self._pending = None
         self._host_tokens = [None, None]
@@ -126,8 +128,8 @@ class Scheduler:
             request.finish_reason = FINISH_LENGTH
             self.finished.append(request)
             return
-        if request.rng is None:
-            request.rng = Xorshift64(request.params.seed)
+        if request.rng_state is None:
+            request.rng_state = Xorshift64(request.params.seed).state
         request.order = self._order
         self._order += 1
         self.waiting.append(request)
@@ -176,6 +178,8 @@ class Scheduler:
                 break
             self.waiting.popleft()
             self.running.append(r)
+            if hasattr(self.sampler, "admit"):       # options and generator state go into the slot, once
+                self.sampler.admit(r.slot, r.params, r.rng_state, r.computed, len(r.output))
             rows.append((r, n))
             budget -= n
         return rows
@@ -193,6 +197,8 @@ class Scheduler:
         victim = max(self.running, key=lambda r: r.order)
         alone = len(self.running) == 1
         self.running.remove(victim)
+        if hasattr(self.sampler, "generator_state"):   # its generator goes on from where it stands
+            victim.rng_state = self.sampler.generator_state(victim.slot)
         self.engine.close(victim.slot)
         victim.slot = None
         victim.computed = 0
@@ -248,7 +254,8 @@ class Scheduler:
         if sampled:
             histories = [r.token_counts() if (r.params.repeat_penalty != 1.0 and not r.params.greedy) else ()
                          for r in sampled]
-            tokens = self.sampler.sample(logits, [r.params for r in sampled], [r.rng for r in sampled], histories)
+            tokens = self.sampler.sample(logits, getattr(self.engine, "last_ctx", None), [r.params for r in sampled],
+                                         histories)
             for r, tok in zip(sampled, tokens):
                 r.output.append(int(tok))
                 # the reference's order of checks (src/server/engine.rs:548-578)
@@ -332,8 +339,7 @@ class Scheduler:
         if sampled:
             histories = [r.token_counts() if (r.params.repeat_penalty != 1.0 and not r.params.greedy) else ()
                          for r in sampled]
-            dev = self.sampler.sample_device(logits, [r.params for r in sampled], [r.rng for r in sampled],
-                                             histories)
+            dev = self.sampler.sample_device(logits, self.engine.last_ctx, [r.params for r in sampled], histories)
             k = self._host_flip
             self._host_flip ^= 1
             host = self._host_tokens[k]

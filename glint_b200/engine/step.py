@@ -39,7 +39,7 @@ class StepContext:
     token's request within this step, which is also its row in every block table.
     ``seq_slot``, ``seq_start`` (tokens cached before the step), ``cu_seqlens`` (token offsets,
     one more than requests) are per request; ``logit_rows`` are the token rows whose logits are
-    wanted.  ``leading_single`` counts the requests at the front of the step that bring a single
+    wanted and ``logit_slots`` the request slots of those rows.  ``leading_single`` counts the requests at the front of the step that bring a single
     token (a scheduler puts its decoding requests first), ``leading_single_context`` is the longest
     context among them.  The ``h_`` fields are host copies for
     planning launches.  ``memo`` is empty at the start of
@@ -63,12 +63,13 @@ class StepContext:
         self.leading_single = next((i for i, l in enumerate(lens) if l != 1), n)   # requests in front that bring one token
         self.max_context = max(s + l for s, l in zip(self.h_seq_start, lens))
         self.leading_single_context = max([s + 1 for s in self.h_seq_start[:self.leading_single]] or [0])
-        rows = []
+        rows, row_slots = [], []
         for i, e in enumerate(entries):
             for w in e.want:
                 if not 0 <= w < lens[i]:
                     raise RequestError(f"wanted place {w} lies outside the {lens[i]} tokens given")
                 rows.append(self.h_cu_seqlens[i] + w)
+                row_slots.append(e.slot)
         self.num_logit_rows = len(rows)
         self.is_decode = self.max_seq_len == 1
         self._groups = cache.groups
@@ -76,7 +77,7 @@ class StepContext:
         max_pages = [t.shape[1] for t in tables]
 
         # one packed int32 buffer -> one copy to the device
-        sizes = [T, T, T, n, n, n + 1, len(rows)] + [n * mp for mp in max_pages] + [len(x) for x in extra]
+        sizes = [T, T, T, n, n, n + 1, len(rows), len(rows)] + [n * mp for mp in max_pages] + [len(x) for x in extra]
         offs, total = [], 0
         for s in sizes:
             offs.append(total)
@@ -92,9 +93,10 @@ class StepContext:
         pack[offs[5]:offs[5] + n + 1] = self.h_cu_seqlens
         if rows:
             pack[offs[6]:offs[6] + len(rows)] = rows
+            pack[offs[7]:offs[7] + len(rows)] = row_slots
         for g, t in enumerate(tables):
-            pack[offs[7 + g]:offs[7 + g] + t.size] = t.reshape(-1)
-        first_extra = 7 + len(tables)
+            pack[offs[8 + g]:offs[8 + g] + t.size] = t.reshape(-1)
+        first_extra = 8 + len(tables)
         for k, x in enumerate(extra):
             if len(x):
                 pack[offs[first_extra + k]:offs[first_extra + k] + len(x)] = x
@@ -108,7 +110,8 @@ class StepContext:
         self.seq_start = cut(4, n)
         self.cu_seqlens = cut(5, n + 1)
         self.logit_rows = cut(6, len(rows))
-        self.block_tables = [cut(7 + g, n * mp).view(n, mp) for g, mp in enumerate(max_pages)]
+        self.logit_slots = cut(7, len(rows))
+        self.block_tables = [cut(8 + g, n * mp).view(n, mp) for g, mp in enumerate(max_pages)]
         self.extra = [cut(first_extra + k, len(x)) for k, x in enumerate(extra)]
 
     def block_table(self, group):
@@ -139,6 +142,7 @@ class Engine:
         self.steps = 0
         self.tokens_run = 0
         self.last_h2d_bytes = 0
+        self.last_ctx = None          # the context of the step that ran last (its device arrays stay valid until the next step)
 
     # ---- request slots ----------------------------------------------------------------------------
 
@@ -236,6 +240,7 @@ class Engine:
         self.steps += 1
         self.tokens_run += ctx.num_tokens
         self.last_h2d_bytes = ctx.h2d_bytes
+        self.last_ctx = ctx
         return logits
 
     # ---- CUDA graphs for decode steps -------------------------------------------------------------

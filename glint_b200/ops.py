@@ -59,6 +59,7 @@ _CORE_SIGNATURES = {
     "glint_apply_penalty": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
     "glint_sample": [_P, _L, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P],
     "glint_sample_rows": [_P, _L, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P],
+    "glint_sample_prepare": [_P, _P, _P, _P, _I, _I, _P, _I, _P],
 }
 
 _core = None
@@ -247,6 +248,29 @@ def sample(src, work, temperature, top_k, top_p, min_p, uniform, out):
     require(uniform, torch.float32, "uniform"); require(out, torch.int32, "out")
     check(core().glint_sample(ptr(src), src.stride(0), ptr(work), rows, V, ptr(temperature), ptr(top_k),
                               ptr(top_p), ptr(min_p), ptr(uniform), ptr(out), stream()), "sample")
+
+
+def sampler_record_words():
+    """32-bit words of the sampler's per-request record (see ``sample_prepare``)."""
+    lib = core().lib
+    lib.glint_sampler_record_words.restype = c_int
+    return int(lib.glint_sampler_record_words())
+
+
+def sample_prepare(records, row_slots, positions, logit_rows, row_opts):
+    """For the rows of a step that are about to be sampled: copy each row's options from its request
+    slot's record (``records`` int32 [slots, words]: temperature, top-p, min-p, penalty as float bits,
+    top-k, not-greedy, generator state low and high, position, count) into ``row_opts`` (float32
+    [7, stride]: temperature, uniform draw, top-p, min-p, penalty, not-greedy, top-k as int bits),
+    advance the generators of the rows that draw, and bring position and count up to date."""
+    rows = row_slots.shape[0]
+    require(records, torch.int32, "records"); require(row_slots, torch.int32, "row_slots")
+    require(positions, torch.int32, "positions"); require(logit_rows, torch.int32, "logit_rows")
+    require(row_opts, torch.float32, "row_opts")
+    if records.dim() != 2 or row_opts.dim() != 2 or row_opts.shape[0] != 7 or logit_rows.shape[0] != rows:
+        raise KernelError("sample_prepare: records [slots, words], row_opts [7, stride] and one logit row per row")
+    check(core().glint_sample_prepare(ptr(records), ptr(row_slots), ptr(positions), ptr(logit_rows), rows,
+                                      records.shape[0], ptr(row_opts), row_opts.shape[1], stream()), "sample_prepare")
 
 
 def sample_rows(logits, work, temperature, top_k, top_p, min_p, uniform, out, penalties=None):

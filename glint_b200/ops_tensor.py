@@ -188,12 +188,24 @@ def prefill_supported(nh, nkv, hd):
     return nkv > 0 and nh % nkv == 0 and nh // nkv <= 64 and hd % 16 == 0 and 16 <= hd <= 256
 
 
-def decode_splits(tokens, nkv, max_context):
-    """Blocks for about one wave (2 fit on each of the 148 SMs), each split with at least 128 keys;
+_sm_count = {}
+
+
+def sm_count(device=None):
+    """Streaming multiprocessors of the device (asked once)."""
+    device = torch.cuda.current_device() if device is None else device
+    n = _sm_count.get(device)
+    if n is None:
+        n = _sm_count[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return n
+
+
+def decode_splits(tokens, nkv, max_context, sms=None):
+    """Blocks for about one wave (2 fit on each SM), each split with at least 128 keys;
     the splits of a token are one thread-block cluster: a power of two up to 8 (measured: clusters
     of 9 to 16 blocks, or of 6, take 1.5 times as long when there are many of them), 16 only for
     one or two requests, where nothing else puts more SMs to work."""
-    want = 296 // max(1, tokens * nkv)
+    want = 2 * (sms or sm_count()) // max(1, tokens * nkv)
     limit = 16 if tokens * nkv <= 8 else 8
     splits = max(1, min(want, max_context // 128, limit))
     while splits & (splits - 1):          # a power of two: other cluster sizes are scheduled poorly

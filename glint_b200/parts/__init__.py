@@ -1,6 +1,6 @@
 """The parts a model is put together from, each registered under its kind."""
 from .base import Part, TensorNeed
-from .registry import register_part, part_class, build_part, CATEGORIES
+from .registry import register_part, part_class, build_part, build_block, CATEGORIES
 from .linear import linear
 from . import norms, positions, embedding, attention, feed_forward  # registration
 from .norms import RMSNorm
@@ -10,5 +10,5 @@ from .attention import Attention
 from .feed_forward import GatedFeedForward
 from .block import Block
 
-__all__ = ["Part", "TensorNeed", "register_part", "part_class", "build_part", "CATEGORIES", "linear",
+__all__ = ["Part", "TensorNeed", "register_part", "part_class", "build_part", "build_block", "CATEGORIES", "linear",
            "RMSNorm", "Rotary", "ScaledEmbedding", "LMHead", "Attention", "GatedFeedForward", "Block"]

@@ -84,5 +84,26 @@ class Attention(Part):
     def parameter_bytes(self):
         return (self.w_qkv.numel() + self.w_o.numel()) * self.w_o.element_size()
 
+    def flops(self, tokens):
+        return 2 * tokens * (self.w_qkv.numel() + self.w_o.numel())
+
+    def keys_read(self, start, n):
+        """Keys that ``n`` tokens at positions ``start``.. read in all: position p reads p + 1 of them,
+        or the last ``window``."""
+        total = n * start + n * (n + 1) // 2
+        if self.window is not None:
+            over = max(0, start + n - self.window)          # positions whose p + 1 exceeds the window
+            first = max(start, self.window)                 # the first such position
+            k = start + n - first                           # how many there are
+            if over > 0 and k > 0:
+                total -= k * (first + 1 - self.window) + k * (k - 1) // 2
+        return total
+
+    def attention_flops(self, start, n):
+        return 4 * self.num_heads * self.head_dim * self.keys_read(start, n)
+
+    def cache_read_bytes(self, position, element_size):
+        return self.keys_read(position, 1) * 2 * self.num_kv_heads * self.head_dim * element_size
+
 
 register_part("mixer", "attention", Attention)

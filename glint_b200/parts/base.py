@@ -41,6 +41,21 @@ class Part:
     def bind(self, tensors):
         """Receive the loaded tensors (by file name) once, on the device."""
 
+    # ---- accounting (rooflines): each part answers for itself, so that a measurement needs no
+    # knowledge of the architecture ----------------------------------------------------------------
+
     def parameter_bytes(self):
-        """Bytes of weights this part reads in one step (for roofline accounting)."""
+        """Bytes of weights this part reads in one step."""
+        return 0
+
+    def flops(self, tokens):
+        """Floating-point operations of this part's matrix products for ``tokens`` tokens."""
+        return 0
+
+    def attention_flops(self, start, n):
+        """Mixers: operations of scores and weighted values for ``n`` tokens at positions from ``start``."""
+        return 0
+
+    def cache_read_bytes(self, position, element_size):
+        """Mixers: bytes of cache a single token at ``position`` has to read."""
         return 0

@@ -15,7 +15,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .registry import build_part
+from .registry import build_part, register_part
 
 
 def _triple(norm):
@@ -27,8 +27,13 @@ def _fusable(*norms):
 
 
 class Block:
+    """The ``"sandwich"`` arrangement.  What the model asks of any block kind: ``parts()``,
+    ``cache_need()``, ``entry_norm()`` (the norm it applies to the residual first, or ``None``; the
+    block before it may hand its result in as ``normed``) and ``forward``."""
+
     def __init__(self, rt, spec):
         self.rt = rt
+        self.spec = spec
         self.mixer = build_part("mixer", spec.mixer, rt)
         self.feed_forward = build_part("feed_forward", spec.feed_forward, rt)
         self.pre_mixer_norm = build_part("norm", spec.pre_mixer_norm, rt)
@@ -40,6 +45,13 @@ class Block:
         return [p for p in (self.mixer, getattr(self.mixer, "position", None), self.feed_forward,
                             self.pre_mixer_norm, self.post_mixer_norm, self.pre_ffn_norm, self.post_ffn_norm)
                 if p is not None]
+
+    def cache_need(self):
+        """What the layer keeps per request between steps: its mixer's declaration."""
+        return self.mixer.cache_need()
+
+    def entry_norm(self):
+        return self.pre_mixer_norm
 
     def _enter(self, x, norm):
         if norm is not None:
@@ -66,3 +78,6 @@ class Block:
         n2 = self._add_then_norm(x, y, self.post_mixer_norm, self.pre_ffn_norm, True)
         d = self.feed_forward.forward(n2, ctx)
         return self._add_then_norm(x, d, self.post_ffn_norm, next_norm, want_next)
+
+
+register_part("block", "sandwich", Block)

@@ -62,6 +62,9 @@ class LMHead(Part):
     def parameter_bytes(self):
         return self.weight.numel() * self.weight.element_size()
 
+    def flops(self, rows):
+        return 2 * rows * self.weight.numel()
+
 
 register_part("embedding", "embedding", ScaledEmbedding)
 register_part("head", "lm_head", LMHead)

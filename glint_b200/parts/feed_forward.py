@@ -54,5 +54,8 @@ class GatedFeedForward(Part):
     def parameter_bytes(self):
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
+    def flops(self, tokens):
+        return 2 * tokens * (self.w_gate_up.numel() + self.w_down.numel())
+
 
 register_part("feed_forward", "gated", GatedFeedForward)

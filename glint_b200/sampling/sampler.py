@@ -4,7 +4,8 @@ Options and their meaning are the reference's ``SamplerConfig`` (src/sampling/sa
 temperature 0 is greedy (the argmax of the raw logits, before any penalty, :181-183); top_k 0,
 top_p 1.0, min_p 0.0 and repeat_penalty 1.0 switch their stage off; seed ``None`` seeds from the
 clock (:134-146).  The generator is xorshift64 with a uniform from its upper 24 bits (:35-70); its
-state is the request's own, kept with the request so that batching never changes what it draws.
+state is the request's own, kept in the request's slot on the device and advanced there, so that
+batching never changes what it draws.
 """
 from __future__ import annotations
 
@@ -124,46 +125,88 @@ def _counts_of(history):
 
 
 class DeviceSampler:
-    """Chooses one token per logits row with the CUDA kernels of ``csrc/sampling.cu``."""
+    """Chooses one token per logits row with the CUDA kernels of ``csrc/sampling.cu``.
 
-    def __init__(self, rt, vocab_size):
+    What a request needs for that lives in its slot, on the device: one record per request slot with
+    its options, the state of its generator, its position and how many tokens were chosen for it
+    (``attach`` declares the record to the cache manager, which zeroes it when a slot is taken;
+    ``admit`` writes options and generator state once, when the request takes the slot).  Before the
+    rows of a step are sampled one small kernel copies each row's options out of its slot's record,
+    advances the generators of the rows that draw and hands the draws over; nothing about a row goes
+    up from the host at every step except the repeat penalty's token counts.  The reference keeps
+    position and generator state with the session (src/session/mod.rs:86,
+    src/sampling/sampler.rs:35-37) and stores both in its snapshots (src/session/snapshot.rs:17-18).
+    """
+
+    HOST_WORDS = 8       # words of the record that the host writes at admission; the rest is the device's
+
+    def __init__(self, rt, vocab_size, cache=None):
         self.rt = rt
         self.vocab_size = vocab_size
         self._work = None
-        self._stage = [None] * 4          # pinned buffers for the per-row options
-        self._stage_next = 0
-        self._pen_stage = [None] * 4      # and for the repeat penalty's lists
+        self._row_opts = None
+        self._pen_stage = [None] * 4      # pinned buffers for the repeat penalty's lists
         self._pen_next = 0
+        self.records = None
+        self._host_records = None
+        if cache is not None:
+            self.attach(cache)
+
+    # ---- the per-request record ---------------------------------------------------------------------
+
+    def attach(self, cache):
+        """Declare the per-request record to the cache manager, which owns the slots."""
+        from ..cache import SlotStateNeed
+        words = ops.sampler_record_words()
+        self.records = cache.add_state("sampler", SlotStateNeed((words,), torch.int32))
+        # one pinned row per slot: a slot's row is written again only after its last request has finished
+        self._host_records = torch.zeros((cache.num_slots, words), dtype=torch.int32).pin_memory()
+        self._copied = [None] * cache.num_slots       # per slot: the event behind the last copy of its row
+        return self.records
+
+    def admit(self, slot, params, rng_state, position=0, generated=0):
+        """The request in ``slot`` samples with ``params`` and draws from a generator in ``rng_state``."""
+        if self._copied[slot] is not None:
+            self._copied[slot].synchronize()            # the row's previous copy has left the pinned buffer
+        row = self._host_records[slot].numpy()
+        row[:4].view(np.float32)[:] = (params.temperature, params.top_p, params.min_p, params.repeat_penalty)
+        row[4] = params.top_k
+        row[5] = 0 if params.greedy else 1
+        state = int(rng_state) & _MASK64
+        row[6:8].view(np.uint32)[:] = (state & 0xFFFFFFFF, state >> 32)
+        row[8] = position
+        row[9] = generated
+        self.records[slot].copy_(self._host_records[slot], non_blocking=True)
+        ev = self._copied[slot] or torch.cuda.Event()
+        ev.record()
+        self._copied[slot] = ev
+
+    def slot_record(self, slot):
+        """The record of ``slot`` read back from the device (waits for the GPU): a dictionary with the
+        generator's state, the position and the count."""
+        row = self.records[slot].cpu().numpy()
+        lo, hi = row[6:8].view(np.uint32)
+        return {"rng_state": int(lo) | (int(hi) << 32), "position": int(row[8]), "generated": int(row[9])}
+
+    def generator_state(self, slot):
+        return self.slot_record(slot)["rng_state"]
+
+    # ---- scratch ------------------------------------------------------------------------------------
 
     def _scratch(self, rows):
         if self._work is None or self._work.shape[0] < rows:
             self._work = torch.empty((max(rows, 8), self.vocab_size), dtype=torch.float32, device=self.rt.device)
         return self._work[:rows]
 
-    def _options(self, params, rngs, dev):
-        """Per-row options as one upload: rows temperature, uniform draw, top-p, min-p, repeat penalty,
-        not-greedy (float32) and top-k (int32 in the same buffer).  Uniform draws are taken from the rows'
-        generators now; a greedy row takes none.  The upload goes from one of four pinned buffers in turn
-        and does not wait for the GPU: a copy from pageable memory would hold the host until the step
-        before it on the stream has run, and with it the preparation of the next step."""
-        rows = len(params)
-        k = self._stage_next
-        self._stage_next = (k + 1) % len(self._stage)
-        host = self._stage[k]
-        if host is None or host.shape[1] < rows:
-            host = torch.empty((7, max(rows, 64)), dtype=torch.float32).pin_memory()
-            self._stage[k] = host
-        pack = host.numpy()
-        for i, (p, r) in enumerate(zip(params, rngs)):
-            g = p.greedy
-            pack[0, i] = 1.0 if g else p.temperature
-            pack[1, i] = 0.0 if g else float(r.next_f32())
-            pack[2, i] = p.top_p
-            pack[3, i] = p.min_p
-            pack[4, i] = p.repeat_penalty
-            pack[5, i] = 0.0 if g else 1.0
-        pack[6].view(np.int32)[:rows] = [p.top_k for p in params]
-        d = host.to(dev, non_blocking=True)[:, :rows]          # the whole small buffer: a contiguous copy
+    def _options(self, ctx, rows):
+        """Per-row options and draws [7, rows] for the rows of the step ``ctx``, made on the device from
+        the slots' records."""
+        if self.records is None:
+            raise RuntimeError("the sampler has no per-request records: call attach(cache) first")
+        if self._row_opts is None or self._row_opts.shape[1] < rows:
+            self._row_opts = torch.empty((7, max(rows, 64)), dtype=torch.float32, device=self.rt.device)
+        ops.sample_prepare(self.records, ctx.logit_slots, ctx.positions, ctx.logit_rows, self._row_opts)
+        d = self._row_opts[:, :rows]
         return d, d[6].view(torch.int32)
 
     def _penalties(self, params, histories, penalty_row, dev):
@@ -199,25 +242,27 @@ class DeviceSampler:
         d = host[:size].to(dev, non_blocking=True)
         return d[:rows + 1], d[rows + 1:rows + 1 + m], d[rows + 1 + m:rows + 1 + 2 * m], penalty_row
 
-    def sample_device(self, logits, params, rngs, histories=None):
+    def sample_device(self, logits, ctx, params, histories=None):
         """One token per row of ``logits`` (float32 [rows, vocab] on the device), left on the device
-        (int32 [rows]); nothing waits for the GPU.  Per row its ``SamplingParams``, its ``Xorshift64`` and,
-        for the repeat penalty, the tokens so far (a sequence, or a ``TokenCounts`` that the caller keeps
-        up to date)."""
+        (int32 [rows]); nothing waits for the GPU.  ``ctx`` is the context of the step that made the
+        logits (which slot and position each row belongs to); ``params`` are the rows' ``SamplingParams``
+        as admitted (the host only reads from them which kernels to launch); for the repeat penalty,
+        ``histories`` holds the tokens so far (a sequence, or a ``TokenCounts`` that the caller keeps up
+        to date)."""
         rows = logits.shape[0]
         dev = logits.device
+        opt, top_k = self._options(ctx, rows)
         some_greedy = any(p.greedy for p in params)
         if some_greedy:
             chosen = torch.empty(rows, dtype=torch.int32, device=dev)
             ops.argmax(logits, chosen)
             if all(p.greedy for p in params):
                 return chosen
-        opt, top_k = self._options(params, rngs, dev)
         penalties = self._penalties(params, histories, opt[4], dev)
         drawn = torch.empty(rows, dtype=torch.int32, device=dev)
         ops.sample_rows(logits, self._scratch(rows), opt[0], top_k, opt[2], opt[3], opt[1], drawn, penalties)
         return torch.where(opt[5] > 0, drawn, chosen) if some_greedy else drawn
 
-    def sample(self, logits, params, rngs, histories):
+    def sample(self, logits, ctx, params, histories=None):
         """The same with the tokens brought to the host: a list of ints."""
-        return [int(t) for t in self.sample_device(logits, params, rngs, histories).tolist()]
+        return [int(t) for t in self.sample_device(logits, ctx, params, histories).tolist()]

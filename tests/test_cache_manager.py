@@ -18,7 +18,7 @@ def test_groups_by_need():
     m = manager()
     assert sorted(g.name for g in m.groups) == ["kv1x8/all", "kv1x8/window8"]
     win = next(g for g in m.groups if g.need.window == 8)
-    assert win.members == [0, 2] and win.k.shape == (2, 12, 1, 16, 8)
+    assert win.members == [0, 2] and win.storage[0].shape == (2, 12, 1, 16, 8)
     assert m.views[0].k.data_ptr() != m.views[2].k.data_ptr()
     assert m.views[3] is None and m.states[3].shape == (4, 3) and m.states[4] is None
 

@@ -227,3 +227,46 @@ def test_command_line(folders, tmp_path):
     assert p.returncode == 0 and "Output:" in p.stdout and "tok/s)" in p.stdout, p.stderr
     p = run("run", "-f", str(tmp_path / "nowhere"), "-p", "1", "-m", "1")
     assert p.returncode == 1 and "error:" in p.stderr
+
+
+def test_slot_record_follows_the_plain_generator(folders):
+    """The request's record in its slot on the device: after N sampled tokens the generator's state is
+    the plain xorshift64's after N draws, the count is N and the position is the newest token's; a
+    greedy request draws nothing; a request that loses its slot goes on from the state it had."""
+    from glint_b200 import LLM
+    from glint_b200.engine.scheduler import Request
+    from glint_b200.sampling import SamplingParams
+    vocab = TINY["A"][0]["vocab_size"]
+    llm = LLM(folders["A"], dtype="float32", cache_tokens=512, max_active=3, max_step_tokens=16, lookahead=False)
+    sch = llm.scheduler
+    drawing = Request("d", random_tokens(21, vocab, 1), 40, SamplingParams(temperature=0.9, top_k=5, seed=11), None)
+    greedy = Request("g", random_tokens(9, vocab, 2), 40, SamplingParams(), None)
+    sch.add(drawing)
+    sch.add(greedy)
+    while len(drawing.output) < 13:
+        sch.step()
+    n = len(drawing.output)
+    rec = llm.sampler.slot_record(drawing.slot)
+    rng = psampler.Xorshift64(11)
+    for _ in range(n):
+        rng.next_u64()
+    assert rec["rng_state"] == rng.state and rec["generated"] == n
+    assert rec["position"] == len(drawing.prompt) + n - 1         # position of the newest token
+    grec = llm.sampler.slot_record(greedy.slot)
+    assert grec["rng_state"] == greedy.rng_state and grec["generated"] == len(greedy.output)   # drew nothing
+    # preemption by hand: the state is read back, the slot freed, and the request goes on in another slot
+    sch._preempt_or_finish()                                   # frees the request admitted last (the greedy one)
+    assert greedy.slot is None and greedy in sch.waiting
+    victim_state = drawing.rng_state
+    sch.running.remove(drawing)
+    drawing.rng_state = llm.sampler.generator_state(drawing.slot)
+    assert drawing.rng_state == rng.state and drawing.rng_state != victim_state
+    llm.engine.close(drawing.slot)
+    drawing.slot, drawing.computed = None, 0
+    sch.waiting.appendleft(drawing)
+    before = list(drawing.output)
+    sch.run()
+    # the same request in one go draws the same tokens
+    again = LLM(folders["A"], dtype="float32", cache_tokens=512, max_active=3, max_step_tokens=16, lookahead=False)
+    want = again.generate(drawing.prompt, max_tokens=40, temperature=0.9, top_k=5, seed=11, stop_at_eos=False)
+    assert drawing.output[:len(before)] == before and drawing.output == want

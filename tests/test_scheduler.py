@@ -48,7 +48,7 @@ class FakeEngine:
 
 
 class FakeSampler:
-    def sample(self, logits, params, rngs, histories):
+    def sample(self, logits, ctx, params, histories):
         return [int(np.argmax(row)) for row in logits]
 
 
