@@ -23,27 +23,10 @@ sys.path.insert(0, ROOT)
 
 METRIC = "Gemma-2-2B bf16 decode tok/s @ batch 8 (prefill tok/s @ 2048 and batch 1/64 alongside)"
 
-GEMMA2_2B = {
-    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
-    "num_hidden_layers": 26, "hidden_size": 2304, "num_attention_heads": 8, "num_key_value_heads": 4,
-    "head_dim": 256, "intermediate_size": 9216, "vocab_size": 256000, "rope_theta": 10000.0,
-    "sliding_window": 4096, "attn_logit_softcapping": 50.0, "final_logit_softcapping": 30.0,
-    "query_pre_attn_scalar": 256, "rms_norm_eps": 1e-6, "max_position_embeddings": 8192,
-    "tie_word_embeddings": True, "hidden_activation": "gelu_pytorch_tanh",
-}
 PROMPT_LEN = 2048
 PREFILL_TOKENS = 2048
 BATCH = 8
-
-
-def peaks():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.isfile(path):
-        with open(path) as f:
-            p = json.load(f)
-        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
-                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+REPEATS = 5
 
 
 class ClockSampler:
@@ -114,7 +97,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
-    ap.add_argument("--skip-points", action="store_true", help="skip batch 1 and 64, prefill and e2e (for profiling)")
+    ap.add_argument("--skip-points", action="store_true", help="only the headline decode (for profiling)")
+    ap.add_argument("--skip-large", action="store_true", help="leave out the 9B serving workload and the 27B decode")
     ap.add_argument("--batch", type=int, default=BATCH)
     args = ap.parse_args()
     if args.impl == "reference":
@@ -127,87 +111,130 @@ def main():
 
     import torch
     from glint_b200 import bench as B
-    from glint_b200 import ops
-    from glint_b200.config import config_from_dict
-    from glint_b200.engine.api import LLM
 
-    pk = peaks()
-    cfg = dict(GEMMA2_2B)
-    full_layers = cfg["num_hidden_layers"]
-    if args.layers:
-        cfg["num_hidden_layers"] = args.layers
-    c = config_from_dict(cfg)
-    L = c.num_hidden_layers
+    pk = B.peaks(ROOT)
+    full_layers = B.SHAPES["2b"]["num_hidden_layers"]
     max_batch = 64 if not args.skip_points else args.batch
-    cache_tokens = max_batch * (PROMPT_LEN + args.steps + args.warmup + 64)
-    llm = LLM.from_config(c, seed=2, std=0.02, norm_std=0.02, dtype="bfloat16", cache_tokens=cache_tokens,
-                          max_active=max_batch, max_step_tokens=4096)
+    cache_tokens = max_batch * (PROMPT_LEN + REPEATS * args.steps + args.warmup + 64)
+    llm = B.open_llm("2b", layers=args.layers, cache_tokens=cache_tokens, max_active=max_batch, max_step_tokens=4096)
     engine, model = llm.engine, llm.model
+    c = model.config
+    L = len(model.run_order)
     clocks = ClockSampler()
     clocks.start()
     spans = []
 
-    # ---- decode at the headline batch, device-timed ------------------------------------------------
-    launches0 = ops.launch_count
+    # ---- before anything is timed: the entry point's tokens against a plain step-by-step run ------------
+    check_prompts = [B.random_prompt(PROMPT_LEN, c.vocab_size, 70 + i) for i in range(args.batch)]
+    checked = B.check_generate(llm, check_prompts, new_tokens=6)
+
+    # ---- decode at the headline batch, device-timed: REPEATS regions of --steps steps, the median ------------
     t0 = clocks.mark()
-    ms, contexts = B.time_decode(engine, args.batch, PROMPT_LEN, args.steps, args.warmup, seed=10)
+    d = B.decode_point(engine, args.batch, PROMPT_LEN, args.steps, args.warmup, seed=10, repeats=REPEATS,
+                       hbm_gbs=pk["hbm_gbs"])
     spans.append((t0, clocks.mark()))
-    launches = (ops.launch_count - launches0) * args.steps // (args.steps + args.warmup + 1)
-    launches = getattr(engine, "timed_launches", None) or launches
-    value = args.batch * 1e3 / ms
-    step_bytes = B.decode_bytes(model, c, L, contexts, 2)
-    achieved = step_bytes / (ms * 1e-3) / 1e9
+    launches = d["launches_per_step"] * args.steps          # this package's kernels in one timed region
     out = {
-        "metric": METRIC, "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "metric": METRIC, "value": round(d["tok_per_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(d["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights N(0,0.02) seed 2, uniform-random token ids",
         "impl": "ours",
+        "spread": {"repeats": REPEATS, "ms_per_step_min": round(d["spread_ms"][0], 4),
+                   "ms_per_step_max": round(d["spread_ms"][1], 4)},
         "config": {"model": "gemma-2-2b shape", "layers": L, "layers_of_config": full_layers,
                    "hidden": c.hidden_size, "heads": c.num_attention_heads, "kv_heads": c.num_key_value_heads,
                    "head_dim": c.head_dim, "intermediate": c.intermediate_size, "vocab": c.vocab_size,
                    "sliding_window": c.sliding_window, "global_batch": args.batch, "seq_len": PROMPT_LEN,
                    "context_limit": c.max_position_embeddings, "page_size": engine.cache.page_size,
                    "parallelism": "single GPU", "l2": "weights 5.2 GB per step exceed the 126 MB L2; no flush",
-                   "peaks": pk["source"]},
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},
+                   "peaks": pk["source"], "repeats": REPEATS},
+        "roofline": {"bound": "hbm", "achieved": round(d["gb_per_s"], 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(d["frac"], 4), "bytes_per_step": d["bytes_per_step"]},
         "gpu_launches": int(launches),
+        "checked": {"what": "tokens of LLM.generate (graphs, launch-ahead) against a plain step-by-step run",
+                    "worst_gap_over_scale": round(checked, 5)},
     }
 
     if not args.skip_points:
+        points, detail = {}, {}
         # ---- decode at batch 1 and 64 --------------------------------------------------------------
-        points = {}
         for b, key in ((1, "decode_b1"), (64, "decode_b64")):
             t0 = clocks.mark()
-            ms_b, _ = B.time_decode(engine, b, PROMPT_LEN, max(16, args.steps // 2), args.warmup, seed=20 + b)
+            p = B.decode_point(engine, b, PROMPT_LEN, max(16, args.steps // 2), args.warmup, seed=20 + b, repeats=3,
+                               hbm_gbs=pk["hbm_gbs"])
             spans.append((t0, clocks.mark()))
-            points[key] = round(b * 1e3 / ms_b, 1)
-        out["points"] = points
+            points[key] = round(p["tok_per_s"], 1)
+            points[key + "_frac"] = round(p["frac"], 4)
+            detail[key] = {"ms_per_step": round(p["ms_per_step"], 4), "bytes_per_step": p["bytes_per_step"],
+                           "spread_ms": [round(x, 4) for x in p["spread_ms"]]}
         # ---- prefill of 2,048 tokens ---------------------------------------------------------------
         t0 = clocks.mark()
-        pms = B.time_prefill(engine, PREFILL_TOKENS, iters=5, warmup=3, seed=30)
+        pf = B.prefill_point(engine, PREFILL_TOKENS, iters=7, warmup=3, seed=30, pk=pk)
         spans.append((t0, clocks.mark()))
-        flops = B.prefill_flops(c, PREFILL_TOKENS, L)
-        out["prefill"] = {"value": round(PREFILL_TOKENS / pms * 1e3, 1), "tokens": PREFILL_TOKENS,
-                          "ms": round(pms, 3), "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
-                          "tflops": round(flops / (pms * 1e-3) / 1e12, 1)}
+        out["prefill"] = {"value": round(pf["tok_per_s"], 1), "tokens": PREFILL_TOKENS, "ms": round(pf["ms"], 3),
+                          "frac": round(pf["frac"], 4), "frac_sustained": round(pf["frac_sustained"], 4),
+                          "tflops": round(pf["tflops"], 1), "spread_ms": [round(x, 3) for x in pf["spread_ms"]]}
         # ---- end to end through LLM.generate -------------------------------------------------------
         prompts = [B.random_prompt(PROMPT_LEN, c.vocab_size, 40 + i) for i in range(args.batch)]
         llm.generate(prompts, max_tokens=4, stop_at_eos=False)          # warm-up of the whole path
         t0 = clocks.mark()
-        llm.generate(prompts, max_tokens=args.steps + 1, stop_at_eos=False)
+        llm.generate(prompts, max_tokens=args.steps + 8, stop_at_eos=False)
         spans.append((t0, clocks.mark()))
-        log = [s for s in llm.scheduler.step_log if s["prefill_tokens"] == 0 and s["decode_rows"] == args.batch]
-        log = log[-args.steps:]
-        e2e_s = sum(s["seconds"] for s in log)
-        out["e2e"] = {"value": round(sum(s["decode_rows"] for s in log) / e2e_s, 1), "unit": "tok/s",
-                      "h2d_bytes_per_step": int(sum(s["h2d_bytes"] for s in log) / len(log)),
-                      "d2h_bytes_per_step": int(sum(s["d2h_bytes"] for s in log) / len(log)),
-                      "steps": len(log)}
+        full = [i for i, s in enumerate(llm.scheduler.step_log) if s["prefill_tokens"] == 0 and s["decode_rows"] == args.batch]
+        log = list(llm.scheduler.step_log)
+        last = full[-1]
+        first = last - args.steps                   # the step before the first of the --steps timed ones
+        assert first >= 0 and all(i in full for i in range(first + 1, last + 1)), "too few full decode steps"
+        e2e_s = log[last]["t_end"] - log[first]["t_end"]
+        timed = log[first + 1:last + 1]
+        out["e2e"] = {"value": round(args.batch * args.steps / e2e_s, 1), "unit": "tok/s",
+                      "h2d_bytes_per_step": int(sum(s["h2d_bytes"] for s in timed) / len(timed)),
+                      "d2h_bytes_per_step": int(sum(s["d2h_bytes"] for s in timed) / len(timed)),
+                      "steps": len(timed)}
+        out["points"] = points
+        out["detail"] = detail
+        if not args.skip_large:
+            del engine, model
+            B.release(llm)
+            del llm
+            large(B, args, pk, clocks, spans, points, detail)
     clocks.stop()
     out["clocks"] = clocks.summary(spans)
     print(json.dumps(out))
     return 0
+
+
+def large(B, args, pk, clocks, spans, points, detail):
+    """The serving workload at the 9B layer sizes (64 requests at t = 0 through the scheduler) and decode at
+    the 27B layer sizes (batch 1 and 16, prompts of 4,096 tokens: past the window)."""
+    import gc
+    import torch
+    gc.collect()
+    torch.cuda.empty_cache()
+    ranges = ((128, 4096), (64, 512))
+    llm = B.open_llm("9b", cache_tokens=B.serve_cache_tokens(64, *ranges), max_active=64, max_step_tokens=2048)
+    B.serve(llm, 8, (128, 1024), (8, 16), seed=1)                 # warm-up of the path: kernels, buffers, graphs
+    t0 = clocks.mark()
+    s = B.serve(llm, 64, *ranges, seed=3)
+    spans.append((t0, clocks.mark()))
+    points["serve_9b"] = round(s["tok_per_s"], 1)
+    points["serve_9b_ttft_ms"] = round(s["ttft_ms_mean"], 1)
+    points["serve_9b_tpot_ms"] = round(s["tpot_ms_mean"], 2)
+    detail["serve_9b"] = {k: (round(v, 3) if isinstance(v, float) else v) for k, v in s.items()}
+    B.release(llm)
+    del llm
+    gc.collect()
+    torch.cuda.empty_cache()
+    llm = B.open_llm("27b", cache_tokens=16 * (4096 + 256), max_active=16, max_step_tokens=4096)
+    for b in (1, 16):
+        t0 = clocks.mark()
+        p = B.decode_point(llm.engine, b, 4096, 24, 4, seed=60 + b, repeats=3, hbm_gbs=pk["hbm_gbs"])
+        spans.append((t0, clocks.mark()))
+        points[f"decode_27b_b{b}"] = round(p["tok_per_s"], 1)
+        points[f"decode_27b_b{b}_frac"] = round(p["frac"], 4)
+        detail[f"decode_27b_b{b}"] = {"ms_per_step": round(p["ms_per_step"], 4), "bytes_per_step": p["bytes_per_step"],
+                                      "context": p["context"], "layers": len(llm.model.run_order)}
+    B.release(llm)
 
 
 if __name__ == "__main__":

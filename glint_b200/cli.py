@@ -55,11 +55,17 @@ def build_parser():
     p.add_argument("-m", "--max-tokens", type=int, default=20)
     _add_engine_options(p)
 
-    p = sub.add_parser("bench", help="Measure prefill and decode throughput.")
-    p.add_argument("-f", "--file", required=True)
-    p.add_argument("--mode", default="all", choices=["all", "prefill", "decode", "concurrency"])
+    p = sub.add_parser("bench", help="Measure prefill, decode and serving throughput with roofline fractions.")
+    p.add_argument("-f", "--file", default=None, help="model folder (the same as --shape <folder>)")
+    p.add_argument("--shape", default=None, help="2b, 9b, 27b (random weights made on the device) or a model folder")
+    p.add_argument("--mode", default="all", choices=["all", "prefill", "decode", "concurrency", "serve"],
+                   help="concurrency: decode at the batch sizes 1, 2, 4 .. --max-concurrent")
+    p.add_argument("--batch", default=None, help="decode batch sizes, e.g. 1,8,64 (default: 1, 2, 4 .. --max-concurrent)")
     p.add_argument("--prompt-len", type=int, default=512)
     p.add_argument("--decode-tokens", type=int, default=128)
+    p.add_argument("--context", type=int, default=None, help="context limit of a named shape (default 8192)")
+    p.add_argument("--layers", type=int, default=None, help="run fewer layers of a named shape")
+    p.add_argument("--requests", type=int, default=64, help="requests of the serve workload")
     p.add_argument("--max-concurrent", type=int, default=8)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--iters", type=int, default=10)

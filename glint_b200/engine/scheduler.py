@@ -53,6 +53,9 @@ class Request:
     pending_index: int = 0       # its place among the tokens sampled by that step
     counts: Optional[TokenCounts] = None   # token counts for the repeat penalty, made at first use
     draining: bool = False       # reached its budget by count; finishes when its last token arrives
+    t_submit: float = 0.0        # time.perf_counter() when it was queued, when its first token reached the host,
+    t_first: float = 0.0         # and when it finished (time to first token, time per output token)
+    t_finish: float = 0.0
 
     @property
     def tokens(self):
@@ -131,6 +134,7 @@ class Scheduler:
         if request.rng_state is None:
             request.rng_state = Xorshift64(request.params.seed).state
         request.order = self._order
+        request.t_submit = time.perf_counter()
         self._order += 1
         self.waiting.append(request)
 
@@ -211,6 +215,7 @@ class Scheduler:
 
     def _finish(self, r, reason):
         r.finish_reason = reason
+        r.t_finish = time.perf_counter()
         if r.slot is not None:
             self.engine.close(r.slot)
             r.slot = None
@@ -258,6 +263,8 @@ class Scheduler:
                                          histories)
             for r, tok in zip(sampled, tokens):
                 r.output.append(int(tok))
+                if r.t_first == 0.0:
+                    r.t_first = time.perf_counter()
                 # the reference's order of checks (src/server/engine.rs:548-578)
                 if r.eos_token_id is not None and tok == r.eos_token_id:
                     self._finish(r, FINISH_STOP)
@@ -265,10 +272,11 @@ class Scheduler:
                     self._finish(r, FINISH_LENGTH)
                 elif r.num_tokens >= self.context_length:
                     self._finish(r, FINISH_LENGTH)
-        self.step_log.append({"seconds": time.perf_counter() - t_start, "decode_rows": n_decode,
+        t_end = time.perf_counter()
+        self.step_log.append({"seconds": t_end - t_start, "t_end": t_end, "decode_rows": n_decode,
                               "prefill_tokens": n_prefill,
                               "h2d_bytes": getattr(self.engine, "last_h2d_bytes", 0),
-                              "d2h_bytes": 4 * len(sampled) * (1 if all(r.params.greedy for r in sampled) else 2)})
+                              "d2h_bytes": 4 * len(sampled)})
         return self.finished[done_before:]
 
     # ---- one step with the sampled tokens left on the device ------------------------------------------
@@ -288,6 +296,8 @@ class Scheduler:
                 continue                       # met EOS a step ago; this token is the discarded one
             r.output.append(int(tok))
             r.unresolved = 0
+            if r.t_first == 0.0:
+                r.t_first = time.perf_counter()
             if r.eos_token_id is not None and tok == r.eos_token_id:
                 self._finish(r, FINISH_STOP)
             elif r.draining:
@@ -359,7 +369,8 @@ class Scheduler:
                 r.draining = True              # no further rows; it finishes when this token arrives
                 self.running.remove(r)
         self._pending = new_pending
-        self.step_log.append({"seconds": time.perf_counter() - t_start, "decode_rows": n_decode,
+        t_end = time.perf_counter()
+        self.step_log.append({"seconds": t_end - t_start, "t_end": t_end, "decode_rows": n_decode,
                               "prefill_tokens": n_prefill,
                               "h2d_bytes": getattr(self.engine, "last_h2d_bytes", 0),
                               "d2h_bytes": 4 * len(sampled)})

@@ -378,3 +378,180 @@ def test_runtime_buffers_are_kept_per_role():
     big.zero_()
     assert float(a.float().sum()) == 3.0 * 8 * 64
     assert rt.buffer("test.a", (8, 64)).data_ptr() == big.data_ptr()
+
+
+# ---- another arrangement of a layer and a mixer that caches one latent vector per token, defined here ----------
+
+
+def _register_parallel_latent_toy():
+    from glint_b200.cache import LayerView, PagedNeed
+    from glint_b200.config import BlockSpec, LayerCall, ModelSpec, PartSpec, register_architecture
+    from glint_b200.parts import Part, TensorNeed, build_part, register_part
+
+    class LatentNeed(PagedNeed):
+        """One vector of ``width`` per token and layer, in pages: neither keys nor values."""
+
+        def __init__(self, width):
+            self.width = width
+
+        def group_key(self):
+            return ("latent", self.width)
+
+        def allocate(self, layers, num_pages, page_size, dtype, device):
+            return torch.zeros((layers, num_pages, page_size, self.width), dtype=torch.float32, device=device)
+
+        def view(self, storage, layer):
+            v = LayerView()
+            v.latent = storage[layer]
+            return v
+
+        def bytes_per_token(self, element_size):
+            return 4 * self.width
+
+    class LatentMixer(Part):
+        """c_t = Wc x_t is cached; y_t = Wo mean(c_0 .. c_t): every token reads every page of its request."""
+
+        def __init__(self, rt, params, tensors):
+            super().__init__(rt, params, tensors)
+            self.size, self.width = int(params["size"]), int(params["width"])
+
+        def cache_need(self):
+            return LatentNeed(self.width)
+
+        def needs(self):
+            return [TensorNeed(self.names["c"], (self.width, self.size)), TensorNeed(self.names["o"], (self.size, self.width))]
+
+        def bind(self, tensors):
+            self.wc, self.wo = tensors[self.names["c"]].float(), tensors[self.names["o"]].float()
+
+        def forward(self, normed, ctx, view, state):
+            T, ps = normed.shape[0], view.page_size
+            table = ctx.block_table(view.group).long()
+            pos, seq = ctx.positions[:T].long(), ctx.token_seq[:T].long()
+            view.latent[table[seq, pos // ps], pos % ps] = normed.float() @ self.wc.T
+            out = torch.empty((T, self.size), dtype=torch.float32, device=normed.device)
+            for i in range(ctx.num_seqs):
+                lo, hi = ctx.h_cu_seqlens[i], ctx.h_cu_seqlens[i + 1]
+                upto = ctx.h_seq_start[i] + hi - lo
+                at = torch.arange(upto, device=normed.device)
+                latents = view.latent[table[i, at // ps], at % ps]                    # [upto, width] through the pages
+                means = latents.cumsum(0) / (at + 1)[:, None]
+                out[lo:hi] = means[ctx.h_seq_start[i]:] @ self.wo.T
+            return out
+
+    class ParallelBlock:
+        """x = x + mixer(norm(x)) + scale * feed_forward(norm(x)): one norm, both parts read it."""
+
+        def __init__(self, rt, spec):
+            self.rt = rt
+            self.mixer = build_part("mixer", spec.mixer, rt)
+            self.feed_forward = build_part("feed_forward", spec.feed_forward, rt)
+            self.norm = build_part("norm", spec.pre_mixer_norm, rt)
+            self.scale = float(spec.params.get("ffn_scale", 1.0))
+
+        def parts(self):
+            return [p for p in (self.mixer, getattr(self.mixer, "position", None), self.feed_forward, self.norm) if p is not None]
+
+        def cache_need(self):
+            return self.mixer.cache_need()
+
+        def entry_norm(self):
+            return self.norm
+
+        def forward(self, x, normed, ctx, view, state, next_norm=None, want_next=False):
+            if normed is None:
+                normed = self.norm.forward(x)
+            y = self.mixer.forward(normed, ctx, view, state)
+            d = self.feed_forward.forward(normed, ctx)
+            x.add_(y + self.scale * d)
+            return next_norm.forward(x) if want_next else None
+
+    class ParallelToyConfig:
+        def __init__(self, obj):
+            self.obj = obj
+
+        @classmethod
+        def from_dict(cls, obj):
+            return cls(obj)
+
+        def to_dict(self):
+            return dict(self.obj)
+
+        def model_spec(self):
+            o = self.obj
+            H, V = o["hidden_size"], o["vocab_size"]
+            norm = lambda name: PartSpec("rmsnorm", {"size": H, "eps": 1e-5, "unit_offset": False}, {"weight": name})
+            ffn = lambda p, act: PartSpec("gated", {"hidden_size": H, "intermediate_size": 56, "activation": act},
+                                          {"gate": p + "gate", "up": p + "up", "down": p + "down"})
+            latent = PartSpec("latent_toy", {"size": H, "width": o["latent_width"]}, {"c": "l0.c", "o": "l0.o"})
+            attn = PartSpec("attention", {"hidden_size": H, "num_heads": 2, "num_kv_heads": 2, "head_dim": 16,
+                                          "score_multiplier": 0.25, "softcap": 30.0, "window": 8,
+                                          "position": PartSpec("rope", {"head_dim": 16, "theta": 10000.0})},
+                            {"q": "l1.q", "k": "l1.k", "v": "l1.v", "o": "l1.o"})
+            blocks = [BlockSpec(latent, ffn("l0.", "silu"), pre_mixer_norm=norm("l0.n"), kind="parallel_toy",
+                                params={"ffn_scale": 0.5}),
+                      BlockSpec(attn, ffn("l1.", "gelu_tanh"), pre_mixer_norm=norm("l1.n1"), pre_ffn_norm=norm("l1.n2"))]
+            return ModelSpec("ParallelToyForCausalLM", V, H, o["max_position_embeddings"],
+                             PartSpec("embedding", {"vocab_size": V, "hidden_size": H, "scale": 1.0}, {"table": "embed"}),
+                             blocks, [LayerCall(0), LayerCall(1), LayerCall(0)], norm("final_norm"),
+                             PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "softcap": None, "tie": True},
+                                      {"weight": "head", "tied_to": "embed"}))
+
+    register_part("mixer", "latent_toy", LatentMixer)
+    register_part("block", "parallel_toy", ParallelBlock)
+    register_architecture("ParallelToyForCausalLM", ParallelToyConfig)
+    return ParallelToyConfig
+
+
+def test_toy_block_kind_and_toy_latent_cache(tmp_path):
+    """A layer with a parallel residual and a mixer whose cache is one latent vector per token (pages of its
+    own shape, declared by a need class of its own): registered from this file, built, and stepped under cuts
+    with a cache so small that pages are used again."""
+    import json
+    from glint_b200.cache import cache_bytes_per_token
+    from glint_b200.engine.loading import build_engine, load_model
+    from glint_b200.engine.step import StepEntry
+    from glint_b200.weights import model_needs, random_tensors, write_safetensors
+    Config = _register_parallel_latent_toy()
+    obj = {"architectures": ["ParallelToyForCausalLM"], "hidden_size": 40, "vocab_size": 113, "latent_width": 12,
+           "max_position_embeddings": 128}
+    folder = str(tmp_path / "parallel")
+    os.makedirs(folder)
+    json.dump(obj, open(os.path.join(folder, "config.json"), "w"))
+    tensors = random_tensors(model_needs(Config(obj)), seed=9, std=0.2, norm_std=1.0, dtype=torch.float32)
+    for k in list(tensors):
+        if k.endswith(".n") or k.endswith("n1") or k.endswith("n2") or k == "final_norm":
+            tensors[k] = tensors[k].abs() + 0.5
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
+
+    model = load_model(folder, "float32")
+    assert type(model.blocks[0]).__name__ == "ParallelBlock" and type(model.blocks[1]).__name__ == "Block"
+    engine = build_engine(model, 96, num_slots=3, use_graphs=False)       # 6 pages per group
+    needs, cache_of = model.cache_needs()
+    assert [type(n).__name__ for n in needs] == ["LatentNeed", "PagedKVNeed", "LatentNeed"]
+    names = sorted(g.name for g in engine.cache.groups)
+    assert len(names) == 2 and any("latent" in n for n in names)
+    latent_group = next(g for g in engine.cache.groups if "latent" in g.name)
+    assert latent_group.members == [0, 2] and latent_group.storage.shape == (2, 6, 16, 12)
+    assert cache_bytes_per_token(needs, cache_of, 4) == 2 * 4 * 12 + 2 * 2 * 16 * 4
+
+    toks_a, toks_b = random_tokens(37, 113, 1), random_tokens(26, 113, 2)
+    whole = {}
+    for name, toks in (("a", toks_a), ("b", toks_b)):
+        s = engine.open()
+        whole[name] = engine.step([StepEntry(s, toks, list(range(len(toks))))]).cpu()
+        engine.close(s)
+    sa, sb = engine.open(), engine.open()
+    got_a, got_b = [], []
+    got_a.append(engine.step([StepEntry(sa, toks_a[:13], list(range(13)))]).cpu())
+    out = engine.step([StepEntry(sb, toks_b[:2], [0, 1]), StepEntry(sa, toks_a[13:14], [0])]).cpu()
+    got_b.append(out[:2]); got_a.append(out[2:])
+    out = engine.step([StepEntry(sa, toks_a[14:], list(range(23))), StepEntry(sb, toks_b[2:25], list(range(23)))]).cpu()
+    got_a.append(out[:23]); got_b.append(out[23:])
+    got_b.append(engine.step([StepEntry(sb, toks_b[25:], [0])]).cpu())
+    assert (torch.cat(got_a) - whole["a"]).abs().max().item() < 1e-4
+    assert (torch.cat(got_b) - whole["b"]).abs().max().item() < 1e-4
+    assert latent_group.pool.reuses > 0
+    engine.close(sa); engine.close(sb)
+    engine.cache.check_consistency()
+    model.rt.check_status()
