@@ -114,9 +114,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     tc::tma_prefetch_desc(&map_k);
     tc::tma_prefetch_desc(&map_v);
   }
-  pdl_launch_dependents();
   __syncthreads();
-  pdl_wait();                                   // the keys of this step and q come from earlier kernels
+  pdl_wait_release();                           // the keys of this step and q come from earlier kernels
   volatile int* abort_flag = &sh->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 

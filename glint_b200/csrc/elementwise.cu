@@ -186,8 +186,7 @@ __global__ void __launch_bounds__(ROW_THREADS)
 rmsnorm_fast_kernel(const float* __restrict__ x, const int* __restrict__ row_index, const float* __restrict__ w,
                     S* __restrict__ out, int H, float eps, float offset) {
   __shared__ float scratch[33];
-  pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_release();
   const int r = blockIdx.x;
   const int H4 = H >> 2;
   const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(row_index ? row_index[r] : r) * H);
@@ -220,8 +219,7 @@ add_rmsnorm_fast_kernel(float* __restrict__ x, const float* __restrict__ y, cons
                         float eps_a, float offset_a, S* __restrict__ out, const float* __restrict__ w_b,
                         float eps_b, float offset_b, int H) {
   __shared__ float scratch[33];
-  pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_release();
   const int r = blockIdx.x;
   const int H4 = H >> 2;
   float4* xr = reinterpret_cast<float4*>(x + (size_t)r * H);
@@ -285,8 +283,7 @@ add_rmsnorm_fast_kernel(float* __restrict__ x, const float* __restrict__ y, cons
 __global__ void __launch_bounds__(128)
 rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, float factor,
                   float2* __restrict__ out, int half) {
-  pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_release();
   const int t = blockIdx.x;
   const float ps = (float)positions[t] / factor;
   for (int j = threadIdx.x; j < half; j += blockDim.x) {
@@ -306,8 +303,7 @@ rope_kv_write_fast_kernel(const float* __restrict__ qkv, const int* __restrict__
                           S* __restrict__ k_pool, S* __restrict__ v_pool, int nh, int nkv, int hd, int page_size,
                           int num_pages, int* __restrict__ status) {
   extern __shared__ float trig[];   // cos[half], sin[half]
-  pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_release();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half = hd >> 1;
@@ -380,8 +376,7 @@ rope_kv_write_fast_kernel(const float* __restrict__ qkv, const int* __restrict__
 __global__ void embed_scale_fast_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
                                         float* __restrict__ x, int H, float scale, int vocab,
                                         int* __restrict__ status) {
-  pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_release();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool bad = id < 0 || id >= vocab;
@@ -421,8 +416,7 @@ __global__ void gated_act_kernel(const float* __restrict__ gu, S* __restrict__ o
 // ids[dst_rows[i]] = src[src_idx[i]]: tokens sampled by the previous step, which never left the device
 __global__ void place_tokens_kernel(int* __restrict__ ids, const int* __restrict__ dst_rows,
                                     const int* __restrict__ src, const int* __restrict__ src_idx, int n) {
-  pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_release();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) ids[dst_rows[i]] = src[src_idx[i]];
 }

@@ -78,7 +78,6 @@ __global__ void __launch_bounds__(SK_MAX_WARPS * 32) gemm_skinny_kernel(const Sk
   constexpr bool GATED = MODE == SK_GATED;
   constexpr int SETS = GATED ? 2 : 1;
   __shared__ float red[SK_MAX_WARPS][SETS][SK_ROWS][8 * NT + 1];
-  pdl_launch_dependents();     // the next kernel may start as soon as there is room for it
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_warps = blockDim.x >> 5;
   const int g = lane >> 2, tq = lane & 3;
@@ -140,7 +139,7 @@ __global__ void __launch_bounds__(SK_MAX_WARPS * 32) gemm_skinny_kernel(const Sk
       }
     }
     if (!waited) {       // x comes from the kernel before this one; the weights above did not have to wait
-      pdl_wait();
+      pdl_wait_release();
       waited = true;
     }
 #pragma unroll
@@ -174,7 +173,7 @@ __global__ void __launch_bounds__(SK_MAX_WARPS * 32) gemm_skinny_kernel(const Sk
       }
     }
   }
-  if (!waited) pdl_wait();
+  if (!waited) pdl_wait_release();
 
   // ---- the warps' partial sums, added in warp order ---------------------------------------------------
 #pragma unroll

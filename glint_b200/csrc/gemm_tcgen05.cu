@@ -148,7 +148,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const int stage_bytes = A_STAGE_BYTES * (DUAL ? 2 : 1) + b_stage_bytes;
   GemmShared* sh = reinterpret_cast<GemmShared*>(smem + (size_t)p.stages * stage_bytes);
 
-  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // blockIdx.x walks the token tiles of one feature tile first: the blocks that run at the same
   // time then share their weight tiles, which come from HBM once and from L2 for the other token
@@ -202,7 +201,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         tc::tma_load_2d(stage, &map_w, &sh->full[i], k, n0);
         if (DUAL) tc::tma_load_2d(stage + A_STAGE_BYTES, &map_w, &sh->full[i], k, n0 + p.dual_offset);
       }
-      pdl_wait();
+      pdl_wait_release();
       for (int i = 0; i < pre; ++i)
         tc::tma_load_2d(smem + (size_t)i * stage_bytes + A_STAGE_BYTES * (DUAL ? 2 : 1), &map_x, &sh->full[i],
                         (kb_begin + i) * GEMM_BK, m0);
@@ -225,11 +224,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
       }
     } else {
-      pdl_wait();
+      pdl_wait_release();
     }
   } else if (warp == 1) {
     // ---- MMA issuer ----------------------------------------------------------------------------
-    pdl_wait();
+    pdl_wait_release();
     if (tc::elect_one()) {
       // One thread issues everything, so its instruction count per K block is what bounds a
       // launch with few tokens: stage index and phase are counters (no division), and the
@@ -267,7 +266,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // ---- epilogue: each warp owns the 32 accumulator lanes of its quarter; with eight warps two share
     // a quarter and take alternate groups of 16 columns (one warp per scheduler leaves the tensor
     // memory loads, the activation and the stores of a wide tile waiting on each other) -------------
-    pdl_wait();
+    pdl_wait_release();
     const int q = warp & 3;
     const int ep_threads = (int)blockDim.x - 64;
     const int eg = (warp - 2) >> 2, c_first = eg * 16, c_step = ep_threads >> 3;   // 16 or 32 columns

@@ -58,8 +58,7 @@ __device__ __forceinline__ ArgBest block_argmax(ArgBest best, ArgBest* scratch) 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, long long row_stride, int V, int* __restrict__ out) {
   __shared__ ArgBest scratch[33];
-  pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_release();
   const float* row = logits + (size_t)blockIdx.x * row_stride;
   ArgBest best{-INFINITY, -1};
   if ((V & 3) == 0 && ((uintptr_t)row & 15) == 0) {
@@ -102,8 +101,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_wide_kernel(const float* __restrict__ logits, long long row_stride, int V, int chunk,
                    unsigned long long* __restrict__ keys, int* __restrict__ counters, int* __restrict__ out) {
   __shared__ ArgBest scratch[33];
-  pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_release();
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * row_stride;
   const int begin = blockIdx.y * chunk, end = min(V, begin + chunk);     // chunk is a multiple of 4
@@ -809,7 +807,7 @@ constexpr int SAMPLER_RECORD = 10;
 __global__ void sample_prepare_kernel(int* __restrict__ records, const int* __restrict__ row_slots,
                                       const int* __restrict__ positions, const int* __restrict__ logit_rows,
                                       int rows, int num_slots, float* __restrict__ row_opts, int stride) {
-  pdl_wait();
+  pdl_wait_release();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   const int slot = row_slots[r];

@@ -140,6 +140,7 @@ class Engine:
         self._staging_events = []
         self._staging_next = 0
         self.steps = 0
+        self.graph_counts = {"eager": 0, "first_sight": 0, "captured": 0, "replayed": 0}
         self.tokens_run = 0
         self.last_h2d_bytes = 0
         self.last_ctx = None          # the context of the step that ran last (its device arrays stay valid until the next step)
@@ -233,6 +234,7 @@ class Engine:
                 ctx.token_ids.copy_(device_tokens, non_blocking=True)
             key = self._graph_key(entries, ctx)
             if key is None:
+                self.graph_counts["eager"] += 1
                 logits = self.model.forward(ctx, self.cache)
             else:
                 logits = self._run_graphed(key, ctx)
@@ -264,6 +266,7 @@ class Engine:
         entry = self._graphs.get(key)
         if entry is None:                 # first sight: run eagerly (also warms lazy set-up)
             self._graphs[key] = "seen"
+            self.graph_counts["first_sight"] += 1
             return self.model.forward(ctx, self.cache)
         if entry == "seen":
             from .. import ops
@@ -276,9 +279,11 @@ class Engine:
                 self._graph_pool = graph.pool()
             entry = (graph, logits, ops.launch_count - before, self._meta_dev.data_ptr())
             self._graphs[key] = entry
+            self.graph_counts["captured"] += 1
         graph, logits, launches, meta_ptr = entry
         assert meta_ptr == self._meta_dev.data_ptr()
         graph.replay()
+        self.graph_counts["replayed"] += 1
         from .. import ops
         ops.launch_count += launches
         return logits
