@@ -198,15 +198,18 @@ def block(x, lw, c, layer_idx):
     return a + d
 
 
-def forward(c, w, tokens):
-    """Logits [T, vocab] of one whole sequence from position 0.
+def forward(c, w, tokens, positions=None):
+    """Logits [T, vocab] of one whole sequence from position 0, or only the rows at ``positions``.
 
     Final norm, the tied (or separate) output matrix and the final cap
-    (src/transformer/forward.rs:516-520, src/transformer/weights.rs:315-319).
+    (src/transformer/forward.rs:516-520, src/transformer/weights.rs:315-319); the reference also
+    computes the head for the positions it keeps only (:1045-1064).
     """
     x = embed(w["model.embed_tokens.weight"], tokens, c["hidden"])
     for i in range(c["layers"]):
         x = block(x, layer_weights(w, i), c, i)
+    if positions is not None:
+        x = x[torch.as_tensor(list(positions), dtype=torch.long)]
     y = rms_norm(x, w["model.norm.weight"], c["eps"])
     head = w["model.embed_tokens.weight"] if (c["tie"] or "lm_head.weight" not in w) else w["lm_head.weight"]
     return softcap(y @ head.T, c["final_cap"])
