@@ -115,7 +115,7 @@ def time_decode(engine, batch, prompt_len, steps, warmup, seed=0, repeats=1):
         for _ in range(warmup):
             one()
         regions = []
-        launches = ops.launch_count
+        launches = ops.launches()
         for r in range(repeats):
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
@@ -125,7 +125,7 @@ def time_decode(engine, batch, prompt_len, steps, warmup, seed=0, repeats=1):
             stop.record()
             torch.cuda.synchronize()
             regions.append((start.elapsed_time(stop) / steps, prompt_len + warmup + r * steps + steps // 2))
-        launches = (ops.launch_count - launches) / (repeats * steps)
+        launches = (ops.launches() - launches) / (repeats * steps)
         engine.rt.check_status()
         order = sorted(regions)
         ms, mid = order[len(order) // 2]

@@ -29,10 +29,10 @@ NVCC_FLAGS = ARCH_FLAGS + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPI
 NVCC_FLAGS += os.environ.get("GLINT_NVCC_EXTRA", "").split()
 
 LIBRARIES = {
-    "core": ["elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu", "sample_noalloc.cu"],
+    "core": ["elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu", "sample_noalloc.cu", "runtime.cu"],
     "tensor": ["gemm_tcgen05.cu", "gemm_skinny.cu", "attention_decode.cu", "attention_prefill.cu", "attention_tcgen05.cu"],
 }
-HEADERS = ["common.cuh", "tcgen05.cuh", "noalloc.h"]
+HEADERS = ["common.cuh", "tcgen05.cuh", "noalloc.h", "runtime.h"]
 
 _loaded = {}
 _lock = threading.Lock()

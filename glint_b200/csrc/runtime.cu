@@ -1,0 +1,283 @@
+// Routed operations and the program executor (see runtime.h).  Host code only: every kernel is
+// launched through the entry point of the file that holds it.
+#include "runtime.h"
+
+#include <vector>
+
+#include "common.cuh"
+
+extern "C" {
+int glint_embed_scale(const void* table, int dtype, const int* ids, float* x, int T, int H, float scale, int vocab,
+                      int* status, cudaStream_t stream);
+int glint_rmsnorm(const float* x, const int* row_index, const float* w, void* out, int dtype, int rows, int H,
+                  float eps, float offset, cudaStream_t stream);
+int glint_add_rmsnorm(float* x, const float* y, const float* w_a, float eps_a, float offset_a, void* out, int dtype,
+                      const float* w_b, float eps_b, float offset_b, int rows, int H, cudaStream_t stream);
+int glint_rope_table(const int* positions, const float* inv_freq, float factor, float* out, int T, int half,
+                     cudaStream_t stream);
+int glint_rope_kv_write(const float* qkv, const int* positions, const int* token_slot, const int* block_table,
+                        int max_pages, const float* inv_freq, float factor, int rot, void* q_out, void* k_pool,
+                        void* v_pool, int dtype, int T, int nh, int nkv, int hd, int page_size, int num_pages,
+                        int* status, cudaStream_t stream);
+int glint_gated_act(const float* gu, void* out, int dtype, int T, int I, int act, cudaStream_t stream);
+int glint_gemm_plain(const void* A, const void* W, int dtype, float* out, int M, int N, int K, float cap,
+                     cudaStream_t stream);
+int glint_attention_plain(const void* q, const void* k_pool, const void* v_pool, int dtype, const int* positions,
+                          const int* token_slot, const int* block_table, int max_pages, void* out, int T, int nh,
+                          int nkv, int hd, int page_size, int num_pages, float multiplier, float cap, int window,
+                          int* status, cudaStream_t stream);
+}
+
+namespace {
+
+long long g_launches = 0;     // kernels launched through the routed operations (one host thread drives a model)
+inline int counted(int rc) {
+  ++g_launches;
+  return rc;
+}
+
+// ---- which product kernel ------------------------------------------------------------------------------
+constexpr int SKINNY_MAX_TOKENS = 16;
+constexpr long long SKINNY_MAX_FEATURES = 65536;     // beyond this the tiled kernel streams at the memory's speed anyway
+constexpr long long SKINNY_WIDE_LIMIT = 12ll << 20;  // 9 to 16 tokens: only products whose launch cost outweighs their stream
+
+bool tiled_supported(int M, int N, int K) { return M > 0 && N > 0 && K > 0 && K % 8 == 0; }
+bool skinny_supported(int M, int N, int K) { return M >= 1 && M <= 16 && N >= 1 && K >= 64 && K % 64 == 0; }
+// Few tokens go to the weight-streaming kernel: up to 8 always, 9 to 16 when the matrix is small.
+bool takes_skinny(int M, long long N, int K) {
+  if (M > SKINNY_MAX_TOKENS || N > SKINNY_MAX_FEATURES || !skinny_supported(M, (int)N, K)) return false;
+  return M <= 8 || N * K <= SKINNY_WIDE_LIMIT;
+}
+
+// ---- which attention kernel -----------------------------------------------------------------------------
+bool decode_supported(int nh, int nkv, int hd, int page) {
+  return nkv > 0 && nh % nkv == 0 && hd % 16 == 0 && hd >= 16 && hd <= 256 && page % 16 == 0 && page >= 16 && page <= 256;
+}
+bool prefill_supported(int nh, int nkv, int hd) {
+  return nkv > 0 && nh % nkv == 0 && nh / nkv <= 64 && hd % 16 == 0 && hd >= 16 && hd <= 256;
+}
+bool tiled_attention_supported(int nh, int nkv, int hd, int page) {
+  return nkv > 0 && nh % nkv == 0 && nh / nkv <= 128 && hd % 16 == 0 && hd >= 16 && hd <= 256 &&
+         (page == 16 || page == 32 || page == 64);
+}
+constexpr int SPLIT_SINGLES_FROM = 4096;   // context from which single tokens in front of portions leave the tiled kernel
+constexpr int SPLIT_SINGLES_UP_TO = 8;     // so few of them leave it at any context
+
+}  // namespace
+
+// Blocks for about one wave (2 fit on each SM), each split with at least 128 keys; the splits of a token
+// are one thread-block cluster: a power of two up to 8 (measured: clusters of 9 to 16 blocks, or of 6,
+// take 1.5 times as long when there are many of them), 16 only for one or two requests, where nothing
+// else puts more SMs to work.
+extern "C" int glint_decode_splits(int tokens, int nkv, int max_context, int sms) {
+  const int rows = tokens * nkv > 1 ? tokens * nkv : 1;
+  const int want = 2 * sms / rows;
+  const int limit = tokens * nkv <= 8 ? 16 : 8;
+  int splits = want < max_context / 128 ? want : max_context / 128;
+  if (splits > limit) splits = limit;
+  if (splits < 1) splits = 1;
+  while (splits & (splits - 1)) splits &= splits - 1;
+  return splits;
+}
+
+extern "C" int glint_route_linear(const GlintRuntime* rt, int M, int N, int K) {
+  if (!rt->tensor_cores || rt->dtype != GLINT_DTYPE_BF16 || !tiled_supported(M, N, K)) return 0;
+  return takes_skinny(M, N, K) ? 1 : 2;
+}
+
+extern "C" int glint_op_linear(const GlintRuntime* rt, const void* a, const void* w, void* out, int out_bf16, int M,
+                               int N, int K, float cap, int gated, int act, float* tmp, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return GLINT_OK;
+  const int route = glint_route_linear(rt, M, N, K);
+  if (route == 1)
+    return counted(rt->tensor.gemm_skinny(a, w, out, gated ? 1 : out_bf16, M, N, K, gated ? 0.f : cap, gated, gated ? N : 0,
+                                  act, stream));
+  if (route == 2)
+    return counted(rt->tensor.gemm_tcgen05(a, w, out, gated ? 1 : out_bf16, M, N, K, gated ? 2ll * N : (long long)N,
+                                   gated ? 0.f : cap, gated, gated ? N : 0, act, rt->workspace, rt->counters,
+                                   rt->status, 0, stream));
+  // CUDA cores: float32 results; a gated product goes through `tmp` [M, 2N]
+  if (out_bf16 && !gated) return GLINT_ERR_BAD_ARG;
+  if (!gated) return counted(glint_gemm_plain(a, w, rt->dtype, (float*)out, M, N, K, cap, stream));
+  if (!tmp) return GLINT_ERR_BAD_ARG;
+  const int rc = counted(glint_gemm_plain(a, w, rt->dtype, tmp, M, 2 * N, K, 0.f, stream));
+  if (rc != GLINT_OK) return rc;
+  return counted(glint_gated_act(tmp, out, rt->dtype, M, N, act, stream));
+}
+
+extern "C" int glint_op_rope_store(const GlintRuntime* rt, const GlintStep* step, const float* qkv, void* q_out,
+                                   const GlintView* view, int nh, int nkv, int hd, const float* inv_freq,
+                                   float factor, int rotary_dim, cudaStream_t stream) {
+  return counted(glint_rope_kv_write(qkv, step->positions, step->token_seq, step->block_table[view->group],
+                             step->max_pages[view->group], inv_freq, factor, rotary_dim, q_out,
+                             view->writes ? view->k : nullptr, view->writes ? view->v : nullptr, rt->dtype,
+                             step->num_tokens, nh, nkv, hd, view->page_size, view->num_pages, rt->status, stream));
+}
+
+extern "C" int glint_op_qkv_rope(const GlintRuntime* rt, const GlintStep* step, const void* x, const void* w,
+                                 void* q_out, float* qkv_tmp, const GlintView* view, int nh, int nkv, int hd, int K,
+                                 const float* inv_freq, float factor, int rotary_dim, GlintTrigTable* trig,
+                                 cudaStream_t stream) {
+  const int M = step->num_tokens;
+  if (M <= 0) return GLINT_OK;
+  const int g = view->group;
+  void* k = view->writes ? view->k : nullptr;
+  void* v = view->writes ? view->v : nullptr;
+  if (rt->tensor_cores && rt->dtype == GLINT_DTYPE_BF16) {
+    // one kernel for a few single tokens: the weight-streaming product with the rotation in its epilogue
+    if (M <= SKINNY_MAX_TOKENS && K >= 64 && K % 64 == 0 && hd % 16 == 0 && hd >= 16 && rotary_dim == hd)
+      return counted(rt->tensor.gemm_skinny_rope(x, w, M, K, step->positions, step->token_seq, step->block_table[g],
+                                         step->max_pages[g], inv_freq, factor, q_out, k, v, nh, nkv, hd,
+                                         view->page_size, view->num_pages, rt->status, stream));
+    // one kernel for portions: the tiled product with the rotation in its epilogue.  Its grid is heads x
+    // token tiles with K unsplit, so it wants tiles for half of the SMs; head sizes in steps of 256.
+    const int heads = view->writes ? nh + 2 * nkv : nh;
+    const int min_blocks = rt->sms / 2;
+    if (trig && K % 8 == 0 && hd >= 256 && hd % 256 == 0 && rotary_dim == hd &&
+        (long long)heads * (hd / 256) * ((M + 127) / 128) >= min_blocks) {
+      if (trig->filled_step != step->id) {       // the angles of this step's tokens, once for all layers
+        const int rc = counted(glint_rope_table(step->positions, inv_freq, factor, trig->table, M, rotary_dim / 2, stream));
+        if (rc != GLINT_OK) return rc;
+        trig->filled_step = step->id;
+      }
+      return counted(rt->tensor.gemm_tcgen05_rope(x, w, M, K, trig->table, step->positions, step->token_seq,
+                                          step->block_table[g], step->max_pages[g], q_out, k, v, nh, nkv, hd,
+                                          view->page_size, view->num_pages, min_blocks, rt->status, stream));
+    }
+  }
+  if (!qkv_tmp) return GLINT_ERR_BAD_ARG;
+  const int rc = glint_op_linear(rt, x, w, qkv_tmp, 0, M, (nh + 2 * nkv) * hd, K, 0.f, 0, 0, nullptr, stream);
+  if (rc != GLINT_OK) return rc;
+  return glint_op_rope_store(rt, step, qkv_tmp, q_out, view, nh, nkv, hd, inv_freq, factor, rotary_dim, stream);
+}
+
+extern "C" int glint_op_attention(const GlintRuntime* rt, const GlintStep* step, const void* q, const GlintView* view,
+                                  void* out, int nh, int nkv, int hd, float multiplier, float cap, int window,
+                                  cudaStream_t stream) {
+  const int T = step->num_tokens;
+  if (T <= 0) return GLINT_OK;
+  const int g = view->group;
+  const int* table = step->block_table[g];
+  const int max_pages = step->max_pages[g];
+  const int page = view->page_size;
+  const bool dec = decode_supported(nh, nkv, hd, page), pre = prefill_supported(nh, nkv, hd);
+  if (!(rt->tensor_cores && rt->dtype == GLINT_DTYPE_BF16 && (dec || pre)))
+    return counted(glint_attention_plain(q, view->k, view->v, rt->dtype, step->positions, step->token_seq, table, max_pages,
+                                 out, T, nh, nkv, hd, page, view->num_pages, multiplier, cap, window, rt->status,
+                                 stream));
+  const GlintTensorEntries& t = rt->tensor;
+  if (step->max_seq_len > 1 && tiled_attention_supported(nh, nkv, hd, page)) {
+    const int lead = step->leading_single;
+    if (lead > 0 && (lead <= SPLIT_SINGLES_UP_TO || step->leading_single_context >= SPLIT_SINGLES_FROM) && dec) {
+      // Decoding requests in front of the prompt portions: in the tiled kernel one block walks all keys of
+      // such a row (8192 keys: 150 us, and the step waits for it); the split kernel shares them among a
+      // cluster.  Many requests with short contexts stay: their walks hide behind the portions' tiles.
+      // The portions keep their absolute token offsets.
+      int rc = counted(t.attention_decode(q, view->k, view->v, step->positions, step->token_seq, table, max_pages, out, lead,
+                                  nh, nkv, hd, page, view->num_pages, multiplier, cap, window,
+                                  glint_decode_splits(lead, nkv, step->max_context, rt->sms), rt->status, stream));
+      if (rc != GLINT_OK) return rc;
+      return counted(t.attention_tcgen05(q, view->k, view->v, step->cu_seqlens + lead, step->seq_start + lead,
+                                 table + (size_t)lead * max_pages, max_pages, out, T, step->num_seqs - lead,
+                                 step->max_seq_len, nh, nkv, hd, page, view->num_pages, multiplier, cap, window,
+                                 rt->status, stream));
+    }
+    return counted(t.attention_tcgen05(q, view->k, view->v, step->cu_seqlens, step->seq_start, table, max_pages, out, T,
+                               step->num_seqs, step->max_seq_len, nh, nkv, hd, page, view->num_pages, multiplier, cap,
+                               window, rt->status, stream));
+  }
+  if ((step->max_seq_len > 1 || !dec) && pre)
+    return counted(t.attention_prefill(q, view->k, view->v, step->cu_seqlens, step->seq_start, table, max_pages, out,
+                               step->num_seqs, step->max_seq_len, nh, nkv, hd, page, view->num_pages, multiplier, cap,
+                               window, rt->status, stream));
+  return counted(t.attention_decode(q, view->k, view->v, step->positions, step->token_seq, table, max_pages, out, T, nh, nkv,
+                            hd, page, view->num_pages, multiplier, cap, window,
+                            glint_decode_splits(T, nkv, step->max_context, rt->sms), rt->status, stream));
+}
+
+// ---- programs ---------------------------------------------------------------------------------------------
+struct GlintProgram {
+  const GlintRuntime* rt;
+  std::vector<GlintOp> ops;
+};
+
+extern "C" GlintProgram* glint_program_create(const GlintRuntime* rt) {
+  GlintProgram* p = new GlintProgram();
+  p->rt = rt;
+  return p;
+}
+
+extern "C" void glint_program_destroy(GlintProgram* prog) { delete prog; }
+
+extern "C" int glint_program_add(GlintProgram* prog, const GlintOp* op) {
+  if (!prog || !op || op->kind < GLINT_OP_EMBED || op->kind > GLINT_OP_HOST) return GLINT_ERR_BAD_ARG;
+  prog->ops.push_back(*op);
+  return (int)prog->ops.size() - 1;
+}
+
+// Kernels launched so far through the routed operations and programs of this process.
+extern "C" long long glint_native_launches() { return g_launches; }
+
+extern "C" int glint_program_size(const GlintProgram* prog) { return prog ? (int)prog->ops.size() : 0; }
+
+// Per kind, what the fields of an operation hold:
+//   EMBED        p: table, out            i: table dtype, H, vocab                    f: scale
+//   RMSNORM      p: x, weight, out        i: out dtype, H                             f: eps, offset
+//   ADD_RMSNORM  p: x, y, w_a, out, w_b   i: out dtype, H                             f: eps_a, offset_a, eps_b, offset_b
+//   LINEAR       p: a, w, out, tmp        i: out bf16, N, K, gated, activation        f: cap
+//   QKV_ROPE     p: x, w, q_out, tmp, view, inv_freq, trig   i: nh, nkv, hd, K, rotary dim    f: factor
+//   ROPE_STORE   p: qkv, q_out, view, inv_freq               i: nh, nkv, hd, rotary dim       f: factor
+//   ATTENTION    p: q, view, out          i: nh, nkv, hd, window                      f: multiplier, cap
+//   HOST         nothing: the place of a step that the host language runs between two native stretches
+// rows = 1: the operation runs on the wanted logit rows (RMSNORM gathers them from x, LINEAR takes that many).
+extern "C" int glint_program_run(GlintProgram* prog, const GlintStep* step, int first, int last, int* failed,
+                                 cudaStream_t stream) {
+  if (!prog || !step || first < 0 || last > (int)prog->ops.size()) return GLINT_ERR_BAD_ARG;
+  const GlintRuntime* rt = prog->rt;
+  const int T = step->num_tokens;
+  for (int n = first; n < last; ++n) {
+    const GlintOp& op = prog->ops[n];
+    const int rows = op.rows ? step->num_logit_rows : T;
+    int rc = GLINT_OK;
+    switch (op.kind) {
+      case GLINT_OP_EMBED:
+        rc = counted(glint_embed_scale(op.p[0], (int)op.i[0], step->token_ids, (float*)op.p[1], T, (int)op.i[1], op.f[0],
+                               (int)op.i[2], rt->status, stream));
+        break;
+      case GLINT_OP_RMSNORM:
+        rc = counted(glint_rmsnorm((const float*)op.p[0], op.rows ? step->logit_rows : nullptr, (const float*)op.p[1], op.p[2],
+                           (int)op.i[0], rows, (int)op.i[1], op.f[0], op.f[1], stream));
+        break;
+      case GLINT_OP_ADD_RMSNORM:
+        rc = counted(glint_add_rmsnorm((float*)op.p[0], (const float*)op.p[1], (const float*)op.p[2], op.f[0], op.f[1], op.p[3],
+                               (int)op.i[0], (const float*)op.p[4], op.f[2], op.f[3], rows, (int)op.i[1], stream));
+        break;
+      case GLINT_OP_LINEAR:
+        rc = glint_op_linear(rt, op.p[0], op.p[1], op.p[2], (int)op.i[0], rows, (int)op.i[1], (int)op.i[2], op.f[0],
+                             (int)op.i[3], (int)op.i[4], (float*)op.p[3], stream);
+        break;
+      case GLINT_OP_QKV_ROPE:
+        rc = glint_op_qkv_rope(rt, step, op.p[0], op.p[1], op.p[2], (float*)op.p[3], (const GlintView*)op.p[4],
+                               (int)op.i[0], (int)op.i[1], (int)op.i[2], (int)op.i[3], (const float*)op.p[5], op.f[0],
+                               (int)op.i[4], (GlintTrigTable*)op.p[6], stream);
+        break;
+      case GLINT_OP_ROPE_STORE:
+        rc = glint_op_rope_store(rt, step, (const float*)op.p[0], op.p[1], (const GlintView*)op.p[2], (int)op.i[0],
+                                 (int)op.i[1], (int)op.i[2], (const float*)op.p[3], op.f[0], (int)op.i[3], stream);
+        break;
+      case GLINT_OP_ATTENTION:
+        rc = glint_op_attention(rt, step, op.p[0], (const GlintView*)op.p[1], op.p[2], (int)op.i[0], (int)op.i[1],
+                                (int)op.i[2], op.f[0], op.f[1], (int)op.i[3], stream);
+        break;
+      case GLINT_OP_HOST:
+        break;
+      default:
+        rc = GLINT_ERR_BAD_ARG;
+    }
+    if (rc != GLINT_OK) {
+      if (failed) *failed = n;
+      return rc;
+    }
+  }
+  return GLINT_OK;
+}

@@ -20,6 +20,7 @@ class CausalLM:
         self.final_norm = build_part("norm", spec.final_norm, rt)
         self.head = build_part("head", spec.head, rt)
         self.run_order = list(spec.run_order)
+        self._programs = {}           # per cache manager: (program, logits tensor, the cache)
 
     # ---- weights ------------------------------------------------------------------------------
 
@@ -89,22 +90,89 @@ class CausalLM:
 
     # ---- forward ------------------------------------------------------------------------------
 
-    def forward(self, ctx, cache):
-        """Run the step's tokens; return float32 logits [len(ctx.logit_rows), vocab], or ``None``
-        when no row is wanted."""
-        x = self.embedding.forward(ctx.token_ids, ctx)
+    def lower(self, prog, cache, logit_capacity):
+        """The whole forward pass as operations of ``prog``: embedding, the layers of the run order with
+        the cache views and state tensors of ``cache``, final norm and output head at the wanted rows.
+        A part or a block kind that offers no ``lower`` runs through its ``forward`` between the native
+        operations.  Returns the logits as a [logit_capacity, vocab] float32 tensor."""
+        import torch
+        from ..native import Value
+        rt = self.rt
+        H = self.spec.hidden_size
+        if hasattr(self.embedding, "lower"):
+            x = self.embedding.lower(prog)
+        else:
+            x = prog.value("embedding.x", H, torch.float32)
+            emb = self.embedding
+            prog.host(lambda ctx: x.rows(ctx.num_tokens).copy_(emb.forward(ctx.token_ids, ctx)))
         normed = None
         n = len(self.run_order)
         for i, call in enumerate(self.run_order):
             block = self.blocks[call.layer]
-            last = i + 1 == n
-            next_norm = None if last else self.blocks[self.run_order[i + 1].layer].entry_norm()
-            normed = block.forward(x, normed, ctx, cache.views[i], cache.states[i], next_norm,
-                                   want_next=next_norm is not None)
+            next_norm = None if i + 1 == n else self.blocks[self.run_order[i + 1].layer].entry_norm()
+            view, state = cache.views[i], cache.states[i]
+            if hasattr(block, "lower"):
+                normed = block.lower(prog, x, normed, view, state, next_norm, next_norm is not None)
+            else:
+                normed = self._host_block(prog, block, x, normed, view, state, next_norm)
+        rows = Value(rt.buffer("head.rows", (logit_capacity, H)))
+        if self.final_norm is not None and hasattr(self.final_norm, "lower"):
+            self.final_norm.lower(prog, x, rows, logit_rows=True)
+        else:
+            norm = self.final_norm
+
+            def gather(ctx):
+                r = rows.rows(ctx.num_logit_rows)
+                if norm is not None:
+                    norm.forward(x.rows(ctx.num_tokens), out=r, row_index=ctx.logit_rows)
+                else:
+                    r.copy_(x.rows(ctx.num_tokens).index_select(0, ctx.logit_rows.long()))
+            prog.host(gather)
+        logits = Value(rt.buffer("head.logits", (logit_capacity, self.spec.vocab_size), torch.float32))
+        if hasattr(self.head, "lower"):
+            self.head.lower(prog, rows, logits)
+        else:
+            head = self.head
+            prog.host(lambda ctx: logits.rows(ctx.num_logit_rows).copy_(head.forward(rows.rows(ctx.num_logit_rows), ctx)))
+        return logits.tensor
+
+    @staticmethod
+    def _host_block(prog, block, x, normed, view, state, next_norm):
+        """A block kind without ``lower``: its ``forward`` between the native operations."""
+        want_next = next_norm is not None
+        out = prog.value("block.normed", x.width) if want_next else None
+        given = normed
+
+        def run(ctx):
+            T = ctx.num_tokens
+            got = block.forward(x.rows(T), None if given is None else given.rows(T), ctx, view, state, next_norm, want_next)
+            if want_next:
+                out.rows(T).copy_(got)
+        prog.host(run)
+        return out
+
+    def program(self, cache, tokens, logit_rows):
+        """The lowered program for ``cache`` with room for a step of ``tokens`` tokens and ``logit_rows``
+        wanted rows: (program, logits tensor, whether it was built anew, in which case launches captured
+        earlier point into memory that is no longer used)."""
+        from ..native import Program
+        entry = self._programs.get(id(cache))
+        fresh = False
+        if entry is None or entry[0].capacity < tokens or entry[1].shape[0] < logit_rows:
+            capacity = max(tokens, 2 * entry[0].capacity if entry is not None and entry[0].capacity < tokens else 0,
+                           entry[0].capacity if entry is not None else 0, 64)
+            rows_cap = max(logit_rows, entry[1].shape[0] if entry is not None else 0, min(64, capacity))
+            prog = Program(self.rt, capacity, cache.groups)
+            logits = self.lower(prog, cache, rows_cap)
+            entry = self._programs[id(cache)] = (prog, logits, cache)
+            fresh = True
+        return entry[0], entry[1], fresh
+
+    def forward(self, ctx, cache):
+        """Run the step's tokens; return float32 logits [len(ctx.logit_rows), vocab], or ``None``
+        when no row is wanted."""
+        prog, logits, _ = self.program(cache, ctx.num_tokens, ctx.num_logit_rows)
+        prog.run(ctx)
         if ctx.num_logit_rows == 0:
             return None
-        if self.final_norm is not None:
-            rows = self.final_norm.forward(x, row_index=ctx.logit_rows)
-        else:
-            rows = x.index_select(0, ctx.logit_rows.long()).to(self.rt.dtype)
-        return self.head.forward(rows, ctx)
+        return logits[:ctx.num_logit_rows]

@@ -114,6 +114,11 @@ class StepContext:
         self.block_tables = [cut(8 + g, n * mp).view(n, mp) for g, mp in enumerate(max_pages)]
         self.extra = [cut(first_extra + k, len(x)) for k, x in enumerate(extra)]
 
+    @property
+    def groups(self):
+        """The cache manager's paged groups, in the order of ``block_tables``."""
+        return self._groups
+
     def block_table(self, group):
         """Device block table [requests of this step, max pages] of a cache group."""
         for g, t in zip(self._groups, self.block_tables):
@@ -232,6 +237,8 @@ class Engine:
                     ops.place_tokens(ctx.token_ids, ctx.extra[1], device_tokens[0], ctx.extra[0])
             elif device_tokens is not None:
                 ctx.token_ids.copy_(device_tokens, non_blocking=True)
+            if self.model.program(self.cache, ctx.num_tokens, ctx.num_logit_rows)[2]:
+                self._graphs.clear()      # the values moved: captured launches point into the old ones
             key = self._graph_key(entries, ctx)
             if key is None:
                 self.graph_counts["eager"] += 1
@@ -272,12 +279,12 @@ class Engine:
             from .. import ops
             graph = torch.cuda.CUDAGraph()
             torch.cuda.synchronize()
-            before = ops.launch_count
+            before = ops.launches()
             with torch.cuda.graph(graph, pool=self._graph_pool):
                 logits = self.model.forward(ctx, self.cache)
             if self._graph_pool is None:
                 self._graph_pool = graph.pool()
-            entry = (graph, logits, ops.launch_count - before, self._meta_dev.data_ptr())
+            entry = (graph, logits, ops.launches() - before, self._meta_dev.data_ptr())
             self._graphs[key] = entry
             self.graph_counts["captured"] += 1
         graph, logits, launches, meta_ptr = entry

@@ -21,6 +21,14 @@ ACTIVATIONS = {"gelu_tanh": 0, "silu": 1}
 launch_count = 0  # kernels launched through this module since import (graph replays add their own)
 
 
+def launches():
+    """Kernels of this package launched so far in this process: through this module's calls, through the
+    native runtime's routed operations and programs, and by replayed graphs."""
+    lib = core().lib
+    lib.glint_native_launches.restype = c_longlong
+    return launch_count + int(lib.glint_native_launches())
+
+
 def dtype_code(dtype):
     try:
         return _DTYPE_CODE[dtype]
@@ -295,3 +303,31 @@ def sample_rows(logits, work, temperature, top_k, top_p, min_p, uniform, out, pe
     check(core().glint_sample_rows(ptr(logits), logits.stride(0), ptr(work), rows, V, ptr(temperature), ptr(top_k),
                                    ptr(top_p), ptr(min_p), ptr(uniform), ptr(offsets), ptr(tokens), ptr(counts),
                                    ptr(penalty), ptr(out), stream()), "sample_rows")
+
+
+# ---- routed operations: the native runtime chooses the kernel (csrc/runtime.h) -------------------------------
+
+
+def _routed():
+    lib = core().lib
+    if not getattr(lib, "_glint_routed", False):
+        lib.glint_op_linear.argtypes = [_P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P]
+        lib.glint_op_linear.restype = c_int
+        lib._glint_routed = True
+    return lib
+
+
+def op_linear(rt, a, w, out, cap=0.0, gated=None, tmp=None):
+    """out [M, N] = a [M, K] w[N, K]^T with the kernel the runtime chooses for these sizes (CUDA cores for
+    float32, the weight-streaming or the tiled tensor-core product for bfloat16); ``gated`` (an activation
+    name): w is [2N, K] and out = act(a w[:N]^T) * (a w[N:]^T) in the activation dtype."""
+    M, K = a.shape
+    N = w.shape[0] // 2 if gated else w.shape[0]
+    require(a, w.dtype, "a"); require(w, None, "w"); require(out, None, "out"); require(tmp, torch.float32, "tmp")
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"linear shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    rc = _routed().glint_op_linear(ctypes.addressof(rt.native), ptr(a), ptr(w), ptr(out), int(out.dtype == torch.bfloat16),
+                                   M, N, K, cap or 0.0, 1 if gated else 0, ACTIVATIONS[gated] if gated else 0, ptr(tmp),
+                                   stream())
+    if rc != 0:
+        raise KernelError(f"linear: {error_string(rc)} (code {rc})")

@@ -1,7 +1,10 @@
-"""Python face of the tensor-core kernels (bfloat16 only): tcgen05 matrix products."""
+"""Python face of the tensor-core kernels (bfloat16 only), one function per kernel: the tcgen05 and the
+weight-streaming products, their variants with the rotary epilogue, and the attention kernels.  Which of
+them a model's operation takes is decided by the native runtime (csrc/runtime.cu); these functions are
+for kernel tests and measurements."""
 from __future__ import annotations
 
-import os
+import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -45,13 +48,18 @@ def scratch(device):
     return entry
 
 
-def gemm_supported(M, N, K):
-    return M > 0 and N > 0 and K > 0 and K % 8 == 0
+_route_rt = None
 
 
-SKINNY_MAX_TOKENS = int(os.environ.get("GLINT_SKINNY_MAX_TOKENS", "16"))   # 0 switches the kernel off
-SKINNY_MAX_FEATURES = 65536      # beyond this the tiled kernel streams at the memory's speed anyway
-SKINNY_WIDE_LIMIT = 12 << 20     # 9 to 16 tokens: only products whose launch cost outweighs their stream
+def route_linear(M, N, K):
+    """The runtime's choice for a bfloat16 product of these sizes: 1 the weight-streaming kernel, 2 the
+    tiled tcgen05 kernel (0: neither takes them)."""
+    global _route_rt
+    from . import native
+    if _route_rt is None:
+        _route_rt = native.RuntimeStruct()
+        _route_rt.tensor_cores, _route_rt.dtype = 1, ops.BF16
+    return native.lib().glint_route_linear(ctypes.addressof(_route_rt), M, N, K)
 
 
 def skinny_supported(M, N, K):
@@ -59,16 +67,14 @@ def skinny_supported(M, N, K):
 
 
 def takes_skinny(M, N, K, force_splits, path):
-    """Few tokens go to the weight-streaming kernel; ``path`` ("skinny", "tcgen05") overrides."""
+    """``path`` ("skinny", "tcgen05") names the kernel; without it the runtime's choice."""
     if path == "tcgen05" or force_splits:
         return False
     if path == "skinny":
         if not skinny_supported(M, N, K):
             raise KernelError(f"the weight-streaming product takes up to 16 tokens and K in steps of 64, not M={M} K={K}")
         return True
-    if M > SKINNY_MAX_TOKENS or N > SKINNY_MAX_FEATURES or not skinny_supported(M, N, K):
-        return False
-    return M <= 8 or N * K <= SKINNY_WIDE_LIMIT
+    return route_linear(M, N, K) == 1
 
 
 def gemm(a, w, out, cap=0.0, status=None, force_splits=0, path=None):
@@ -88,15 +94,6 @@ def gemm(a, w, out, cap=0.0, status=None, force_splits=0, path=None):
     ops.check(lib().glint_gemm_tcgen05(ops.ptr(a), ops.ptr(w), ops.ptr(out), int(out.dtype == torch.bfloat16), M, N,
                                        K, N, cap or 0.0, 0, 0, 0, ops.ptr(ws), ops.ptr(counters), ops.ptr(st),
                                        force_splits, ops.stream()), "gemm_tcgen05")
-
-
-FUSED_ROPE = os.environ.get("GLINT_FUSED_ROPE", "1") != "0"
-
-
-def qkv_rope_supported(M, K, hd, rotary_dim):
-    """The fused q/k/v product takes up to 16 tokens, K in steps of 64 and whole-head rotation."""
-    return (FUSED_ROPE and 1 <= M <= min(16, SKINNY_MAX_TOKENS) and K >= 64 and K % 64 == 0 and hd % 16 == 0 and hd >= 16
-            and rotary_dim == hd)
 
 
 def qkv_rope(a, w_qkv, positions, token_slot, block_table, inv_freq, factor, q_out, k_pool, v_pool, nh, nkv, hd,
@@ -119,16 +116,13 @@ def qkv_rope(a, w_qkv, positions, token_slot, block_table, inv_freq, factor, q_o
                                            num_pages, ops.ptr(status), ops.stream()), "gemm_skinny_rope")
 
 
-ROPE_TILED_MIN_BLOCKS = int(os.environ.get("GLINT_ROPE_TILED_MIN_BLOCKS", "74"))
-
-
 def qkv_rope_tiled_supported(M, K, hd, rotary_dim, heads, min_blocks=None):
     """The tiled q/k/v product with the rotary epilogue: head sizes in steps of 256 (a thread holds
     features j and j + hd/2 of a head), whole-head rotation, K in steps of 8, and, as its grid is heads x
-    token tiles with K unsplit, enough tokens for ``min_blocks`` blocks (default: half of a B200's SMs)."""
-    if not (FUSED_ROPE and M >= 1 and K % 8 == 0 and hd >= 256 and hd % 256 == 0 and rotary_dim == hd):
+    token tiles with K unsplit, enough tokens for ``min_blocks`` blocks (default: half of the SMs)."""
+    if not (M >= 1 and K % 8 == 0 and hd >= 256 and hd % 256 == 0 and rotary_dim == hd):
         return False
-    mb = ROPE_TILED_MIN_BLOCKS if min_blocks is None else min_blocks
+    mb = sm_count() // 2 if min_blocks is None else min_blocks
     head_tiles = heads * (hd // 256)
     return head_tiles * -(-M // 128) >= mb          # the kernel takes tiles of 256 tokens if they suffice, else of 128
 
@@ -150,7 +144,7 @@ def qkv_rope_tiled(a, w_qkv, trig, positions, token_seq, block_table, q_out, k_p
     ops.check(lib().glint_gemm_tcgen05_rope(ops.ptr(a), ops.ptr(w_qkv), M, K, ops.ptr(trig), ops.ptr(positions),
                                             ops.ptr(token_seq), ops.ptr(block_table), block_table.shape[1],
                                             ops.ptr(q_out), ops.ptr(k_pool), ops.ptr(v_pool), nh, nkv, hd, page_size,
-                                            num_pages, ROPE_TILED_MIN_BLOCKS if min_blocks is None else min_blocks,
+                                            num_pages, sm_count() // 2 if min_blocks is None else min_blocks,
                                             ops.ptr(status), ops.stream()), "gemm_tcgen05_rope")
 
 
@@ -171,12 +165,6 @@ def gemm_gated(a, w_gate_up, out, activation, status=None, force_splits=0, path=
     ops.check(lib().glint_gemm_tcgen05(ops.ptr(a), ops.ptr(w_gate_up), ops.ptr(out), 1, M, I, K, 2 * I, 0.0, 1, I,
                                        ops.ACTIVATIONS[activation], ops.ptr(ws), ops.ptr(counters), ops.ptr(st),
                                        force_splits, ops.stream()), "gemm_tcgen05 (gated)")
-
-
-def attention_supported(nh, nkv, hd, page_size):
-    """The bfloat16 attention kernels take head sizes in steps of 8 up to 512 (single tokens) and
-    in steps of 16 up to 256 with at most 64 query heads per kv head (prompt portions)."""
-    return decode_supported(nh, nkv, hd, page_size) or prefill_supported(nh, nkv, hd)
 
 
 def decode_supported(nh, nkv, hd, page_size):
@@ -201,16 +189,9 @@ def sm_count(device=None):
 
 
 def decode_splits(tokens, nkv, max_context, sms=None):
-    """Blocks for about one wave (2 fit on each SM), each split with at least 128 keys;
-    the splits of a token are one thread-block cluster: a power of two up to 8 (measured: clusters
-    of 9 to 16 blocks, or of 6, take 1.5 times as long when there are many of them), 16 only for
-    one or two requests, where nothing else puts more SMs to work."""
-    want = 2 * (sms or sm_count()) // max(1, tokens * nkv)
-    limit = 16 if tokens * nkv <= 8 else 8
-    splits = max(1, min(want, max_context // 128, limit))
-    while splits & (splits - 1):          # a power of two: other cluster sizes are scheduled poorly
-        splits &= splits - 1
-    return splits
+    """How many blocks share the keys of one token in the split attention kernel (the runtime's choice)."""
+    from . import native
+    return native.lib().glint_decode_splits(tokens, nkv, max_context, sms or sm_count())
 
 
 def attention_decode(q, k_pool, v_pool, positions, token_seq, block_table, out, nh, nkv, hd, page_size, num_pages,
@@ -254,44 +235,3 @@ def attention_tcgen05(q, k_pool, v_pool, cu_seqlens, seq_start, block_table, out
                                             ops.ptr(out), q.shape[0], n_seqs, max_q_len, nh, nkv, hd, page_size,
                                             num_pages, multiplier, cap or 0.0, window or 0, ops.ptr(status),
                                             ops.stream()), "attention_tcgen05")
-
-
-SPLIT_SINGLES_FROM = int(os.environ.get("GLINT_SPLIT_SINGLES_FROM", "4096"))   # context from which single tokens leave the tiled kernel
-SPLIT_SINGLES_UP_TO = 8            # so few of them leave it at any context
-
-
-def attention(q, view, ctx, out, nh, nkv, hd, multiplier, cap, window, status):
-    """Route a step's attention: single tokens to the split kernel, portions to the tiled one."""
-    table = ctx.block_table(view.group)
-    if ctx.max_seq_len > 1 and tcgen05_attention_supported(nh, nkv, hd, view.page_size):
-        lead = getattr(ctx, "leading_single", 0)
-        if (lead > 0 and (lead <= SPLIT_SINGLES_UP_TO or getattr(ctx, "leading_single_context", 0) >= SPLIT_SINGLES_FROM)
-                and decode_supported(nh, nkv, hd, view.page_size)):
-            # Decoding requests in front of the prompt portions: in the tiled kernel one block walks all
-            # keys of such a row (8192 keys: 150 us, and the step waits for it); the split kernel shares
-            # them among a cluster (two requests at 7000 keys beside a portion of 1024 tokens: 9.2 -> 7.3
-            # ms a step).  Many requests with short contexts stay: their walks (2048 keys: 38 us) hide
-            # behind the portions' tiles, and the split kernel's time for 32 of them does not.  The
-            # portions keep their absolute token offsets.
-            attention_decode(q, view.k, view.v, ctx.positions, ctx.token_seq, table, out, nh, nkv, hd, view.page_size,
-                             view.num_pages, multiplier, cap, window, status,
-                             decode_splits(lead, nkv, ctx.max_context), tokens=lead)
-            key = ("portions behind single tokens", id(view.group), lead)
-            rest = ctx.memo.get(key)
-            if rest is None:
-                rest = ctx.memo[key] = (ctx.cu_seqlens[lead:], ctx.seq_start[lead:], table[lead:])
-            attention_tcgen05(q, view.k, view.v, rest[0], rest[1], rest[2], out, ctx.num_seqs - lead,
-                              ctx.max_seq_len, nh, nkv, hd, view.page_size, view.num_pages, multiplier, cap, window,
-                              status)
-            return
-        attention_tcgen05(q, view.k, view.v, ctx.cu_seqlens, ctx.seq_start, table, out, ctx.num_seqs,
-                          ctx.max_seq_len, nh, nkv, hd, view.page_size, view.num_pages, multiplier, cap, window,
-                          status)
-    elif (ctx.max_seq_len > 1 or not decode_supported(nh, nkv, hd, view.page_size)) and prefill_supported(nh, nkv, hd):
-        attention_prefill(q, view.k, view.v, ctx.cu_seqlens, ctx.seq_start, table, out, ctx.num_seqs,
-                          ctx.max_seq_len, nh, nkv, hd, view.page_size, view.num_pages, multiplier, cap, window,
-                          status)
-    else:
-        splits = decode_splits(ctx.num_tokens, nkv, ctx.max_context)
-        attention_decode(q, view.k, view.v, ctx.positions, ctx.token_seq, table, out, nh, nkv, hd, view.page_size,
-                         view.num_pages, multiplier, cap, window, status, splits)

@@ -11,10 +11,8 @@ from __future__ import annotations
 
 import torch
 
-from .. import ops
 from ..cache import PagedKVNeed
-from .base import Part, TensorNeed
-from .linear import linear
+from .base import Part, TensorNeed, run_lowered
 from .registry import build_part, register_part
 
 
@@ -56,30 +54,28 @@ class Attention(Part):
         self.w_qkv = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
         self.w_o = tensors[n["o"]]
 
-    def forward(self, normed, ctx, view, state=None):
-        rt = self.rt
-        T = normed.shape[0]
-        q = rt.buffer("mixer.q", (T, self.q_size))
-        fused = getattr(self.position, "project_encode_store", None)
-        if fused is None or not fused(normed, self.w_qkv, ctx, q, view, self.num_heads, self.num_kv_heads,
-                                      self.head_dim):
-            qkv = linear(rt, normed, self.w_qkv, out=rt.buffer("mixer.qkv", (T, self.w_qkv.shape[0]), torch.float32))
-            self.position.encode_and_store(qkv, ctx, q, view, self.num_heads, self.num_kv_heads, self.head_dim)
-        out = rt.buffer("mixer.out", (T, self.q_size))
-        self.attend(q, ctx, view, out)
-        return linear(rt, out, self.w_o, out=rt.buffer("mixer.y", (T, self.w_o.shape[0]), torch.float32))
+    def lower(self, prog, normed, view, state=None):
+        """q/k/v product with the position encoding and the cache write, attention over the pages of
+        ``view``, output product.  Returns the value float32 [tokens, hidden].  A position encoding
+        that offers no ``lower`` runs through its ``encode_and_store`` between the native operations."""
+        nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        q = prog.value("mixer.q", self.q_size)
+        if hasattr(self.position, "lower"):
+            self.position.lower(prog, normed, self.w_qkv, q, view, nh, nkv, hd)
+        else:
+            qkv = prog.value("mixer.qkv", self.w_qkv.shape[0], torch.float32)
+            prog.linear(normed, self.w_qkv, qkv)
+            position = self.position
+            prog.host(lambda ctx: position.encode_and_store(qkv.rows(ctx.num_tokens), ctx, q.rows(ctx.num_tokens), view,
+                                                            nh, nkv, hd))
+        out = prog.value("mixer.out", self.q_size)
+        prog.attention(q, view, out, nh, nkv, hd, self.multiplier, self.softcap, self.window)
+        y = prog.value("mixer.y", self.w_o.shape[0], torch.float32)
+        prog.linear(out, self.w_o, y)
+        return y
 
-    def attend(self, q, ctx, view, out):
-        rt = self.rt
-        if rt.tensor_cores:
-            from .. import ops_tensor
-            if ops_tensor.attention_supported(self.num_heads, self.num_kv_heads, self.head_dim, view.page_size):
-                ops_tensor.attention(q, view, ctx, out, self.num_heads, self.num_kv_heads, self.head_dim,
-                                     self.multiplier, self.softcap, self.window, rt.status)
-                return
-        ops.attention_plain(q, view.k, view.v, ctx.positions, ctx.token_seq, ctx.block_table(view.group), out,
-                            self.num_heads, self.num_kv_heads, self.head_dim, view.page_size, view.num_pages,
-                            self.multiplier, self.softcap, self.window, rt.status)
+    def forward(self, normed, ctx, view, state=None):
+        return run_lowered(self.rt, ctx, normed.shape[0], lambda prog: self.lower(prog, prog.bind(normed), view, state))
 
     def parameter_bytes(self):
         return (self.w_qkv.numel() + self.w_o.numel()) * self.w_o.element_size()

@@ -6,11 +6,17 @@ Interfaces (``ctx`` is the step's ``StepContext``; activations are [tokens, size
 * norm:          ``forward(x_f32, out=None, row_index=None) -> normalized (activation dtype)``;
                  ``triple()`` -> (weight, eps, offset) for fused add+norm kernels, or ``None``
 * position:      ``encode_and_store(qkv_f32, ctx, q_out, view, nh, nkv, hd)``
-* mixer:         ``cache_need() -> PagedKVNeed | SlotStateNeed | None``;
+* mixer:         ``cache_need() -> a cache declaration or None``;
                  ``forward(normed, ctx, view, state) -> float32 [tokens, hidden]``
 * feed-forward:  ``forward(normed, ctx) -> float32 [tokens, hidden]``
 * embedding:     ``forward(token_ids, ctx) -> float32 [tokens, hidden]``
 * head:          ``forward(normed_rows, ctx) -> float32 logits [rows, vocab]``
+
+``forward`` runs at once on tensors.  A part may also offer ``lower(prog, ...)``, which describes the same
+work as operations of a ``glint_b200.native.Program`` on its ``Value`` objects; a model whose parts all
+offer it runs a whole step with one call into the native executor, and a part without it runs through
+``forward`` between two native stretches.  The package's parts implement ``forward`` by lowering
+themselves into a short program and running it (``run_lowered``): one description of the work serves both.
 """
 from __future__ import annotations
 
@@ -59,3 +65,13 @@ class Part:
     def cache_read_bytes(self, position, element_size):
         """Mixers: bytes of cache a single token at ``position`` has to read."""
         return 0
+
+
+def run_lowered(rt, ctx, rows, lower):
+    """Run ``lower(prog) -> Value`` at once for the step ``ctx``: a short program for ``rows`` tokens, run on
+    the current stream; returns the first ``rows`` rows of the value it produced."""
+    from ..native import Program
+    prog = Program(rt, rows, ctx.groups)
+    out = lower(prog)
+    prog.run(ctx)
+    return out.rows(rows)

@@ -25,6 +25,12 @@ class ScaledEmbedding(Part):
     def bind(self, tensors):
         self.table = tensors[self.names["table"]]
 
+    def lower(self, prog):
+        """The residual stream of the step's tokens, float32 [tokens, hidden]."""
+        out = prog.value("embedding.x", self.hidden_size, torch.float32)
+        prog.embed(self.table, out, self.scale, self.vocab_size)
+        return out
+
     def forward(self, token_ids, ctx):
         out = torch.empty((token_ids.shape[0], self.hidden_size), dtype=torch.float32, device=token_ids.device)
         ops.embed_scale(self.table, token_ids, out, self.scale, self.rt.status)
@@ -55,6 +61,11 @@ class LMHead(Part):
     def bind(self, tensors):
         own = tensors.get(self.names["weight"])
         self.weight = tensors[self.names["tied_to"]] if (self.tie or own is None) else own
+
+    def lower(self, prog, rows, out):
+        """Logits of the normalized ``rows`` (the step's wanted rows) into ``out`` [rows, vocab] float32."""
+        prog.linear(rows, self.weight, out, cap=self.softcap, logit_rows=True)
+        return out
 
     def forward(self, normed_rows, ctx):
         return linear(self.rt, normed_rows, self.weight, cap=self.softcap)

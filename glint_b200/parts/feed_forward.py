@@ -9,8 +9,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import Part, TensorNeed
-from .linear import linear
+from .base import Part, TensorNeed, run_lowered
 from .registry import register_part
 
 
@@ -36,20 +35,21 @@ class GatedFeedForward(Part):
         self.w_gate_up = torch.cat([tensors[n["gate"]], tensors[n["up"]]], dim=0).contiguous()
         self.w_down = tensors[n["down"]]
 
+    def lower(self, prog, normed):
+        """Two operations: the gated product (one kernel with the activation in its epilogue where the
+        runtime has one, else the product and the activation), and the down product.  Returns the value
+        float32 [tokens, hidden]."""
+        act = prog.value("ffn.act", self.intermediate_size)
+        # the two-kernel path keeps gate and up in 32-bit between the kernels
+        fused = self.rt.tensor_cores and self.w_gate_up.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
+        tmp = None if fused else prog.value("ffn.gate_up", 2 * self.intermediate_size, torch.float32)
+        prog.linear(normed, self.w_gate_up, act, gated=self.activation, tmp=tmp)
+        y = prog.value("ffn.y", self.hidden_size, torch.float32)
+        prog.linear(act, self.w_down, y)
+        return y
+
     def forward(self, normed, ctx):
-        rt = self.rt
-        T = normed.shape[0]
-        act = rt.buffer("ffn.act", (T, self.intermediate_size))
-        fused = False
-        if rt.tensor_cores:
-            from .. import ops_tensor
-            if ops_tensor.gemm_supported(T, self.intermediate_size, self.hidden_size):
-                ops_tensor.gemm_gated(normed, self.w_gate_up, act, self.activation, rt.status)
-                fused = True
-        if not fused:
-            gu = linear(rt, normed, self.w_gate_up, out=rt.buffer("ffn.gate_up", (T, 2 * self.intermediate_size), torch.float32))
-            ops.gated_act(gu, act, self.activation)
-        return linear(rt, act, self.w_down, out=rt.buffer("ffn.y", (T, self.hidden_size), torch.float32))
+        return run_lowered(self.rt, ctx, normed.shape[0], lambda prog: self.lower(prog, prog.bind(normed)))
 
     def parameter_bytes(self):
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()

@@ -29,6 +29,11 @@ class RMSNorm(Part):
     def triple(self):
         return (self.weight, self.eps, self.offset)
 
+    def lower(self, prog, x, out, logit_rows=False):
+        """out = norm(x) as an operation of ``prog``; with ``logit_rows`` of the step's wanted rows only."""
+        prog.rmsnorm(x, self.weight, self.eps, self.offset, out, logit_rows)
+        return out
+
     def forward(self, x, out=None, row_index=None):
         rows = x.shape[0] if row_index is None else row_index.shape[0]
         if out is None:

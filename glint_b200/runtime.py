@@ -42,6 +42,9 @@ class Runtime:
             raise KernelError("no CUDA device is available: the engine has no CPU path")
         ops.core()  # build or load the kernels now, loudly
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.shared = {}          # what several parts of a model share (a table of rotation angles), by key
+        from . import native
+        self.native = native.make_runtime_struct(self)     # the C++ side's view of this runtime
         self._backing = {}        # (role, dtype) -> flat tensor
         self._views = {}          # (role, shape, dtype) -> view of the backing tensor
         self._retired = []        # outgrown backing tensors: captured launches may still point into them

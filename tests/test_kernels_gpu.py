@@ -693,3 +693,18 @@ def test_repeat_penalty_kernel():
                       torch.tensor([2.0, 1.5], device=DEV))
     assert work[0, 5].item() == 0.25 and work[0, 9].item() == 1.0 and work[0, 0].item() == 2.0
     assert work[1, 7].item() == pytest.approx(-2.25) and work[1, 5].item() == -1.0
+
+
+def test_runtime_routes_products_by_size():
+    """Which product kernel the native runtime takes: the weight-streaming one up to 8 tokens, and from 9 to
+    16 for small matrices; the tiled one beyond; neither when K is no multiple of 8 (CUDA cores then)."""
+    from glint_b200 import ops_tensor
+    assert ops_tensor.route_linear(1, 4096, 2304) == 1 and ops_tensor.route_linear(8, 36864, 4608) == 1
+    assert ops_tensor.route_linear(16, 2304, 2048) == 1            # 9 to 16 tokens, a small matrix
+    assert ops_tensor.route_linear(16, 9216, 2304) == 2            # 9 to 16 tokens, a large one
+    assert ops_tensor.route_linear(17, 2304, 2048) == 2 and ops_tensor.route_linear(2048, 4096, 2304) == 2
+    assert ops_tensor.route_linear(4, 256000, 2304) == 2           # the output head streams on the tiled kernel
+    assert ops_tensor.route_linear(4, 4096, 2296) == 2             # K in steps of 8 but not of 64
+    assert ops_tensor.route_linear(4, 4096, 2300) == 0
+    assert ops_tensor.decode_splits(1, 4, 8192, 148) == 16 and ops_tensor.decode_splits(8, 4, 2304, 148) == 8
+    assert ops_tensor.decode_splits(64, 4, 2304, 148) == 1 and ops_tensor.decode_splits(8, 4, 200, 148) == 1

@@ -80,17 +80,14 @@ def test_replay_child_process(folders, expected, tmp_path, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "C"])
-def test_single_tokens_in_front_of_portions(folders, expected, name, dtype, monkeypatch):
+def test_single_tokens_in_front_of_portions(folders, expected, name, dtype):
     """A step with decoding requests first and prompt portions behind them (a scheduler's order) sends
     the single tokens to the split attention kernel and the portions to the tiled one; the same step
     with the portions first takes the tiled kernel for all.  Both must give the plain logits."""
-    from glint_b200 import ops_tensor
     from glint_b200.engine.step import StepEntry
     reqs, want = expected[name]
     ids = sorted(reqs)
     engine = _engine(folders[name], dtype, 512)
-    monkeypatch.setattr(ops_tensor, "SPLIT_SINGLES_FROM", 1)         # contexts of any length
-    monkeypatch.setattr(ops_tensor, "SPLIT_SINGLES_UP_TO", 0)
     for portions_first in (False, True):
         slots = {rid: engine.open() for rid in ids}
         singles, portions = ids[2:], ids[:2]                     # the two longest requests decode
