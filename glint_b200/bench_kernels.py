@@ -44,13 +44,13 @@ def _copies(nbytes):
     return max(2, int(math.ceil(2.5 * L2_BYTES / max(nbytes, 1))))
 
 
-def bench_gemm(M, N, K, gated=False, splits=0, iters=20, path=None, resident=False):
+def bench_gemm(M, N, K, gated=False, splits=0, iters=20, path=None):
+    """A product at the given sizes with the kernel the runtime would take (``path`` names one instead:
+    "skinny" or "tcgen05")."""
     from . import ops_tensor
     rows = 2 * N if gated else N
     n = min(_copies(rows * K * 2), 64)
-    ws = [torch.randn(rows, K, device=DEV).to(torch.bfloat16) * 0.05 for _ in range(1 if resident else n)]
-    if resident:
-        ws = ws * n                                           # the same weights every launch: they stay in L2
+    ws = [torch.randn(rows, K, device=DEV).to(torch.bfloat16) * 0.05 for _ in range(n)]
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16 if gated else torch.float32)
     if gated:
@@ -131,17 +131,8 @@ def prefill_step(tokens, layers, iters):
     last step runs between cudaProfilerStart and cudaProfilerStop, so that a profiler started with
     ``--profile-from-start off`` lists the launches of exactly one step."""
     from . import bench as B
-    from .config import config_from_dict
-    from .engine.api import LLM
-    cfg = {"architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2", "num_hidden_layers": layers,
-           "hidden_size": 2304, "num_attention_heads": 8, "num_key_value_heads": 4, "head_dim": 256,
-           "intermediate_size": 9216, "vocab_size": 256000, "rope_theta": 10000.0, "sliding_window": 4096,
-           "attn_logit_softcapping": 50.0, "final_logit_softcapping": 30.0, "query_pre_attn_scalar": 256,
-           "rms_norm_eps": 1e-6, "max_position_embeddings": 8192, "tie_word_embeddings": True,
-           "hidden_activation": "gelu_pytorch_tanh"}
-    llm = LLM.from_config(config_from_dict(cfg), seed=2, std=0.02, norm_std=0.02, dtype="bfloat16",
-                          cache_tokens=2 * tokens + 256, max_active=2, max_step_tokens=max(tokens, 16))
-    ms = B.time_prefill(llm.engine, tokens, iters=iters, warmup=3, seed=30)
+    llm = B.open_llm("2b", layers=layers, cache_tokens=2 * tokens + 256, max_active=2, max_step_tokens=max(tokens, 16))
+    ms = B.time_prefill(llm.engine, tokens, iters=iters, warmup=3, seed=30)[0]
     torch.cuda.synchronize()
     torch.cuda.profiler.start()
     B.time_prefill(llm.engine, tokens, iters=1, warmup=0, seed=31)
@@ -182,7 +173,7 @@ def main():
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=2304)
-    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--splits", type=int, default=0, help="attention-decode: blocks per token (default: the runtime's choice)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2176)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -190,18 +181,15 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--layers", type=int, default=2, help="prefill-step: layers of the engine")
-    ap.add_argument("--resident", action="store_true", help="products: reuse one set of weights (they stay in L2)")
-    ap.add_argument("--path", choices=["tcgen05", "skinny"], default=None,
-                    help="which product kernel (default: the one the engine would take)")
     a = ap.parse_args()
     out = []
     if a.what == "gemm":
-        out.append(bench_gemm(a.m, a.n, a.k, False, a.splits, a.iters, a.path))
+        out.append(bench_gemm(a.m, a.n, a.k, False, 0, a.iters))
     elif a.what == "gated":
-        out.append(bench_gemm(a.m, a.n, a.k, True, a.splits, a.iters, a.path))
+        out.append(bench_gemm(a.m, a.n, a.k, True, 0, a.iters))
     elif a.what == "decode-shapes":
         for name, M, N, K, gated in gemma2_2b_decode_cases(a.batch):
-            out.append(dict(bench_gemm(M, N, K, gated, 0, a.iters, a.path, a.resident), name=name))
+            out.append(dict(bench_gemm(M, N, K, gated, 0, a.iters), name=name))
         out.append(bench_attention_decode(a.batch, a.context, iters=a.iters))
         out.extend(bench_rows(a.batch))
     elif a.what == "prefill-shapes":
