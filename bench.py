@@ -212,7 +212,7 @@ def large(B, args, pk, clocks, spans, points, detail):
     gc.collect()
     torch.cuda.empty_cache()
     ranges = ((128, 4096), (64, 512))
-    llm = B.open_llm("9b", cache_tokens=B.serve_cache_tokens(64, *ranges), max_active=64, max_step_tokens=2048)
+    llm = B.open_llm("9b", cache_tokens=B.serve_cache_tokens(64, *ranges), max_active=64, max_step_tokens=4096)
     B.serve(llm, 8, (128, 1024), (8, 16), seed=1)                 # warm-up of the path: kernels, buffers, graphs
     t0 = clocks.mark()
     s = B.serve(llm, 64, *ranges, seed=3)
@@ -221,6 +221,7 @@ def large(B, args, pk, clocks, spans, points, detail):
     points["serve_9b_ttft_ms"] = round(s["ttft_ms_mean"], 1)
     points["serve_9b_tpot_ms"] = round(s["tpot_ms_mean"], 2)
     detail["serve_9b"] = {k: (round(v, 3) if isinstance(v, float) else v) for k, v in s.items()}
+    detail["serve_9b"]["max_step_tokens"] = 4096
     B.release(llm)
     del llm
     gc.collect()

@@ -141,6 +141,62 @@ def prefill_step(tokens, layers, iters):
     return {"kernel": "prefill step", "tokens": tokens, "layers": layers, "ms": round(ms, 4)}
 
 
+def engine_step(shape, layers, batch, context, tokens, timeline=False):
+    """One step of an engine of a named shape with ``layers`` layers: ``batch`` requests with ``context``
+    tokens cached bring one token each and, with ``tokens`` > 0, one more request brings a portion of that
+    many tokens.  The last step runs between cudaProfilerStart and cudaProfilerStop (for a profiler started
+    with ``--profile-from-start off``).  ``timeline``: a step of single tokens is replayed from its CUDA graph
+    under the PyTorch profiler and every kernel's start, end and duration in microseconds are printed, which
+    shows what runs under what (a launch list shows each kernel alone)."""
+    from . import bench as B
+    from . import ops
+    from .engine.step import StepEntry
+    llm = B.open_llm(shape, layers=layers, cache_tokens=(batch + 2) * (context + 64) + 2 * tokens + 64,
+                     max_active=batch + 2, max_step_tokens=max(4096, tokens))
+    eng = llm.engine
+    V = eng.vocab_size
+    slots = [eng.open() for _ in range(batch)]
+    B.fill_cache(eng, slots, [B.random_prompt(context, V, 100 + i) for i in range(batch)])
+    out = torch.ones(max(batch, 1), dtype=torch.int32, device=DEV)
+
+    def step():
+        entries = [StepEntry(s, [5], [0]) for s in slots]
+        if tokens:
+            extra = eng.open()
+            entries.append(StepEntry(extra, B.random_prompt(tokens, V, 7), [tokens - 1]))
+        logits = eng.step(entries)
+        ops.argmax(logits, out[:logits.shape[0]]) if logits.shape[0] <= out.shape[0] else None
+        if tokens:
+            eng.close(extra)
+
+    for _ in range(4):
+        step()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    step()
+    b.record()
+    torch.cuda.synchronize()
+    res = [{"kernel": "engine step", "shape": shape, "layers": layers, "batch": batch, "context": context,
+            "portion": tokens, "ms": round(a.elapsed_time(b), 4), "graphs": dict(eng.graph_counts)}]
+    if timeline:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step()
+            torch.cuda.synchronize()
+        evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                     key=lambda e: e.time_range.start)
+        t0 = evs[0].time_range.start if evs else 0
+        for e in evs:
+            res.append({"start_us": round(e.time_range.start - t0, 1), "end_us": round(e.time_range.end - t0, 1),
+                        "us": round(e.time_range.end - e.time_range.start, 1), "kernel": e.name[:60]})
+    torch.cuda.profiler.start()
+    step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    return res
+
+
 def bench_sampling(rows, V, iters=20):
     """The sampling kernel on random logits: temperature alone, with top-k, and with every stage."""
     from . import ops
@@ -169,7 +225,10 @@ def gemma2_2b_decode_cases(batch):
 def main():
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("what", choices=["gemm", "gated", "decode-shapes", "prefill-shapes", "attention-decode",
-                                     "attention-prefill", "rows", "prefill-step", "sampling"])
+                                     "attention-prefill", "rows", "prefill-step", "sampling", "step"])
+    ap.add_argument("--shape", default="2b", help="step: 2b, 9b, 27b or a model folder")
+    ap.add_argument("--portion", type=int, default=0, help="step: tokens of a prompt portion beside the single tokens")
+    ap.add_argument("--timeline", action="store_true", help="step: kernel starts and ends inside a graph replay")
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=2304)
@@ -207,6 +266,8 @@ def main():
         out.extend(bench_rows(a.batch))
     elif a.what == "sampling":
         out.extend(bench_sampling(a.batch, a.n if a.n != 4096 else 256000, a.iters))
+    elif a.what == "step":
+        out.extend(engine_step(a.shape, a.layers, a.batch, a.context, a.portion, a.timeline))
     elif a.what == "prefill-step":
         out.append(prefill_step(a.tokens, a.layers, a.iters))
     for row in out:

@@ -132,6 +132,7 @@ class PagePool:
         self._owned = [False] * self.capacity
         self.peak_live = 0
         self.reuses = 0
+        self.hidden = 0          # pages held for the engine's own use: not counted in the statistics
         self._ever_used = [False] * self.capacity
 
     @property
@@ -163,8 +164,8 @@ class PagePool:
             self._free.append(p)
 
     def stats(self):
-        return {"capacity": self.capacity, "live": self.live, "peak_live": self.peak_live,
-                "pooled": self.available, "reuses": self.reuses}
+        return {"capacity": self.capacity - self.hidden, "live": self.live - self.hidden,
+                "peak_live": self.peak_live - self.hidden, "pooled": self.available, "reuses": self.reuses}
 
 
 class PagedGroup:
@@ -295,11 +296,9 @@ class CacheManager:
     def add_state(self, name, need):
         """A fixed-size record per request slot for something beside the mixers (the sampler keeps the
         request's options, generator state, position and count there): ``need`` is a ``SlotStateNeed``;
-        the rows are zero when a request takes its slot.  Returns the tensor [slots, *shape]."""
+        the rows are zero now and again whenever a request takes its slot.  Returns the tensor [slots, *shape]."""
         if name in self.named_states:
             return self.named_states[name]
-        if any(self._slot_live):
-            raise GlintError(f"state '{name}' must be declared before requests are admitted")
         st = self.named_states[name] = need.allocate(self.num_slots, self.device)
         return st
 

@@ -107,7 +107,7 @@ class Scheduler:
         self._host_tokens = [None, None]
         self._host_flip = 0
         self.max_step_tokens = int(max_step_tokens)
-        self.max_active = int(max_active or engine.cache.num_slots)
+        self.max_active = int(max_active or getattr(engine, "num_slots", engine.cache.num_slots))
         self.context_length = int(context_length or engine.cache.max_positions)
         self.waiting = deque()
         self.running = []

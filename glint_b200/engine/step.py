@@ -32,6 +32,19 @@ def _align4(n):
     return (n + 3) & ~3
 
 
+def padded_size(n):
+    """The batch size whose graph a step of ``n`` single tokens replays: itself up to 8, then the next
+    multiple of 4 up to 32, of 8 up to 64, of 16 beyond.  A serving run whose batch shrinks request by request
+    then captures a dozen graphs instead of one per size (each capture holds the GPU idle for milliseconds)."""
+    if n <= 8:
+        return n
+    if n <= 32:
+        return (n + 3) & ~3
+    if n <= 64:
+        return (n + 7) & ~7
+    return (n + 15) & ~15
+
+
 class StepContext:
     """Everything about one step that parts may read.  Device tensors are int32.
 
@@ -137,8 +150,19 @@ class Engine:
         self._graph_pool = None
         self.rt = model.rt
         needs, cache_of = model.cache_needs()
-        self.cache = CacheManager(needs, cache_of, num_slots, num_pages, page_size, model.spec.max_positions,
-                                  self.rt.dtype, self.rt.device)
+        # With graphs, steps of single tokens are padded to a few batch sizes (see padded_size): the rows
+        # that fill a step up belong to a slot and a page of their own, beyond what the caller asked for.
+        spare = 1 if use_graphs else 0
+        self.cache = CacheManager(needs, cache_of, num_slots + spare, num_pages + spare, page_size,
+                                  model.spec.max_positions, self.rt.dtype, self.rt.device)
+        self.num_slots = num_slots
+        self._pad_entry = None
+        if use_graphs:
+            slot = self.cache.alloc_slot()
+            self.cache.reserve([(slot, 1)])             # one page in every group, position 0, never advanced
+            for g in self.cache.groups:
+                g.pool.hidden = 1
+            self._pad_entry = StepEntry(slot, [0], [0])
         self.vocab_size = model.spec.vocab_size
         self._meta_dev = None
         self._staging = []
@@ -227,6 +251,12 @@ class Engine:
         self.validate(entries)
         rows = [(e.slot, len(e.tokens)) for e in entries]
         self.cache.reserve(rows)
+        n_real = len(entries)
+        real_tokens = sum(n for _, n in rows)
+        if self._graphable(entries):
+            # a step of single tokens replays a graph captured for its padded size: the rows behind the
+            # caller's are one token at position 0 of the spare slot, and their logits are dropped
+            entries = list(entries) + [self._pad_entry] * (padded_size(n_real) - n_real)
         with torch.cuda.device(self.rt.device):
             placed = isinstance(device_tokens, tuple)      # (source tensor, source indices, token rows)
             extra = (device_tokens[1], device_tokens[2]) if placed else ()
@@ -236,7 +266,7 @@ class Engine:
                 if len(device_tokens[1]):
                     ops.place_tokens(ctx.token_ids, ctx.extra[1], device_tokens[0], ctx.extra[0])
             elif device_tokens is not None:
-                ctx.token_ids.copy_(device_tokens, non_blocking=True)
+                ctx.token_ids[:real_tokens].copy_(device_tokens, non_blocking=True)
             if self.model.program(self.cache, ctx.num_tokens, ctx.num_logit_rows)[2]:
                 self._graphs.clear()      # the values moved: captured launches point into the old ones
             key = self._graph_key(entries, ctx)
@@ -245,14 +275,19 @@ class Engine:
                 logits = self.model.forward(ctx, self.cache)
             else:
                 logits = self._run_graphed(key, ctx)
+                if len(entries) > n_real:
+                    logits = logits[:n_real]
         self.cache.advance(rows)
         self.steps += 1
-        self.tokens_run += ctx.num_tokens
+        self.tokens_run += real_tokens
         self.last_h2d_bytes = ctx.h2d_bytes
         self.last_ctx = ctx
         return logits
 
     # ---- CUDA graphs for decode steps -------------------------------------------------------------
+
+    def _graphable(self, entries):
+        return self.use_graphs and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries)
 
     def _graph_key(self, entries, ctx):
         """Steps of single tokens with logits wanted for each are launch-bound: they replay a

@@ -205,7 +205,8 @@ class DeviceSampler:
             raise RuntimeError("the sampler has no per-request records: call attach(cache) first")
         if self._row_opts is None or self._row_opts.shape[1] < rows:
             self._row_opts = torch.empty((7, max(rows, 64)), dtype=torch.float32, device=self.rt.device)
-        ops.sample_prepare(self.records, ctx.logit_slots, ctx.positions, ctx.logit_rows, self._row_opts)
+        # the first ``rows`` wanted rows of the step (rows that only fill a step up to a graph's size follow them)
+        ops.sample_prepare(self.records, ctx.logit_slots[:rows], ctx.positions, ctx.logit_rows[:rows], self._row_opts)
         d = self._row_opts[:, :rows]
         return d, d[6].view(torch.int32)
 

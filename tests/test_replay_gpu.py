@@ -111,3 +111,40 @@ def test_single_tokens_in_front_of_portions(folders, expected, name, dtype):
         for s_ in slots.values():
             engine.close(s_)
         engine.rt.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_padded_to_a_graph_size(folders, dtype):
+    """Steps of 11 and then 9 single tokens replay the graph captured for 12 (the rows that fill the step
+    up belong to the engine's spare slot): the logits are the plain ones at every step, a request that ends
+    changes nothing for the others, and the spare slot's page is not counted among the caller's."""
+    from glint_b200.engine.loading import build_engine, load_model
+    from glint_b200.engine.step import StepEntry, padded_size
+    assert [padded_size(n) for n in (1, 8, 9, 12, 13, 33, 64, 65)] == [1, 8, 12, 12, 16, 40, 64, 80]
+    name = "C"
+    vocab = TINY[name][0]["vocab_size"]
+    reqs = [random_tokens(14 + 3 * i, vocab, 700 + i) for i in range(11)]
+    want = [plain_logits(folders[name], r) for r in reqs]
+    engine = build_engine(load_model(folders[name], dtype), 11 * 64, num_slots=11)
+    slots = [engine.open() for _ in reqs]
+    tail = 6
+    for s, r in zip(slots, reqs):
+        engine.step([StepEntry(s, r[:-tail], [])])
+    live = list(range(11))
+    for t in range(tail):
+        if t == 4:                                              # two requests end: 9 rows, the same graph
+            for i in (3, 7):
+                engine.close(slots[i])
+                live.remove(i)
+        got = engine.step([StepEntry(slots[i], [reqs[i][len(reqs[i]) - tail + t]], [0]) for i in live])
+        got = got.float().cpu().numpy()
+        assert got.shape[0] == len(live)
+        for row, i in enumerate(live):
+            ref = want[i][len(reqs[i]) - tail + t]
+            assert np.abs(got[row] - ref).max() <= tolerance(dtype, want[i]), (dtype, t, i)
+    assert engine.graph_counts["replayed"] >= 4 and engine.graph_counts["captured"] == 1
+    for i in live:
+        engine.close(slots[i])
+    assert all(s["live"] == 0 for s in engine.cache.stats().values())
+    engine.cache.check_consistency()
+    engine.rt.check_status()
