@@ -9,7 +9,7 @@ knows which architecture it serves.  The reference has one forward pass with
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Optional
+from typing import Optional
 
 
 @dataclass

@@ -31,6 +31,7 @@ int glint_attention_plain(const void* q, const void* k_pool, const void* v_pool,
 namespace {
 
 long long g_launches = 0;     // kernels launched through the routed operations (one host thread drives a model)
+long long g_fallbacks = 0;    // operations of a tensor-core runtime that took a CUDA-core kernel (sizes no other takes)
 inline int counted(int rc) {
   ++g_launches;
   return rc;
@@ -97,6 +98,7 @@ extern "C" int glint_op_linear(const GlintRuntime* rt, const void* a, const void
                                    gated ? 0.f : cap, gated, gated ? N : 0, act, rt->workspace, rt->counters,
                                    rt->status, 0, stream));
   // CUDA cores: float32 results; a gated product goes through `tmp` [M, 2N]
+  if (rt->tensor_cores) ++g_fallbacks;
   if (out_bf16 && !gated) return GLINT_ERR_BAD_ARG;
   if (!gated) return counted(glint_gemm_plain(a, w, rt->dtype, (float*)out, M, N, K, cap, stream));
   if (!tmp) return GLINT_ERR_BAD_ARG;
@@ -161,6 +163,7 @@ extern "C" int glint_op_attention(const GlintRuntime* rt, const GlintStep* step,
   const int max_pages = step->max_pages[g];
   const int page = view->page_size;
   const bool dec = decode_supported(nh, nkv, hd, page), pre = prefill_supported(nh, nkv, hd);
+  if (rt->tensor_cores && !(dec || pre)) ++g_fallbacks;
   if (!(rt->tensor_cores && rt->dtype == GLINT_DTYPE_BF16 && (dec || pre)))
     return counted(glint_attention_plain(q, view->k, view->v, rt->dtype, step->positions, step->token_seq, table, max_pages,
                                  out, T, nh, nkv, hd, page, view->num_pages, multiplier, cap, window, rt->status,
@@ -217,6 +220,9 @@ extern "C" int glint_program_add(GlintProgram* prog, const GlintOp* op) {
 
 // Kernels launched so far through the routed operations and programs of this process.
 extern "C" long long glint_native_launches() { return g_launches; }
+// Operations that a runtime with tensor-core kernels ran on CUDA cores because of their sizes (K not a
+// multiple of 8, a head size above 256 or not a multiple of 16): right, but far slower.
+extern "C" long long glint_native_fallbacks() { return g_fallbacks; }
 
 extern "C" int glint_program_size(const GlintProgram* prog) { return prog ? (int)prog->ops.size() : 0; }
 

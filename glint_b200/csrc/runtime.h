@@ -97,6 +97,8 @@ int glint_route_linear(const GlintRuntime* rt, int M, int N, int K);
 
 // Kernels launched so far through the routed operations and programs of this process.
 long long glint_native_launches();
+// Operations that a tensor-core runtime ran on CUDA cores because no tensor-core kernel takes their sizes.
+long long glint_native_fallbacks();
 int glint_decode_splits(int tokens, int nkv, int max_context, int sms);
 
 // ---- programs ------------------------------------------------------------------------------------------

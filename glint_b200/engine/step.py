@@ -156,6 +156,8 @@ class Engine:
         self.cache = CacheManager(needs, cache_of, num_slots + spare, num_pages + spare, page_size,
                                   model.spec.max_positions, self.rt.dtype, self.rt.device)
         self.num_slots = num_slots
+        from .. import ops
+        self._fallbacks_before = ops.fallbacks()
         self._pad_entry = None
         if use_graphs:
             slot = self.cache.alloc_slot()
@@ -279,10 +281,22 @@ class Engine:
                     logits = logits[:n_real]
         self.cache.advance(rows)
         self.steps += 1
+        if self.steps == 1 and self.rt.tensor_cores:
+            self._note_fallbacks()
         self.tokens_run += real_tokens
         self.last_h2d_bytes = ctx.h2d_bytes
         self.last_ctx = ctx
         return logits
+
+    def _note_fallbacks(self):
+        """Say once, after the first step, if sizes of this model kept operations off the tensor cores."""
+        import sys
+        from .. import ops
+        n = ops.fallbacks() - self._fallbacks_before
+        if n > 0:
+            print(f"[glint_b200] note: {n} operations of the first step ran on CUDA-core kernels although the engine "
+                  f"is bfloat16: no tensor-core kernel takes their sizes (products want K in steps of 8, attention "
+                  f"head sizes in steps of 16 up to 256); results are right, speed is not", file=sys.stderr, flush=True)
 
     # ---- CUDA graphs for decode steps -------------------------------------------------------------
 

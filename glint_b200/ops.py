@@ -106,6 +106,13 @@ def stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+def fallbacks():
+    """Operations that a tensor-core runtime ran on CUDA cores so far because of their sizes."""
+    lib = core().lib
+    lib.glint_native_fallbacks.restype = c_longlong
+    return int(lib.glint_native_fallbacks())
+
+
 def ptr(t):
     return 0 if t is None else t.data_ptr()
 
