@@ -115,7 +115,7 @@ def main():
     pk = B.peaks(ROOT)
     full_layers = B.SHAPES["2b"]["num_hidden_layers"]
     max_batch = 64 if not args.skip_points else args.batch
-    cache_tokens = max_batch * (PROMPT_LEN + REPEATS * args.steps + args.warmup + 64)
+    cache_tokens = max_batch * (PROMPT_LEN + REPEATS * args.steps + args.warmup + 128)
     llm = B.open_llm("2b", layers=args.layers, cache_tokens=cache_tokens, max_active=max_batch, max_step_tokens=4096)
     engine, model = llm.engine, llm.model
     c = model.config
@@ -175,22 +175,30 @@ def main():
                           "frac": round(pf["frac"], 4), "frac_sustained": round(pf["frac_sustained"], 4),
                           "tflops": round(pf["tflops"], 1), "spread_ms": [round(x, 3) for x in pf["spread_ms"]]}
         # ---- end to end through LLM.generate -------------------------------------------------------
-        prompts = [B.random_prompt(PROMPT_LEN, c.vocab_size, 40 + i) for i in range(args.batch)]
-        llm.generate(prompts, max_tokens=4, stop_at_eos=False)          # warm-up of the whole path
-        t0 = clocks.mark()
-        llm.generate(prompts, max_tokens=args.steps + 8, stop_at_eos=False)
-        spans.append((t0, clocks.mark()))
-        full = [i for i, s in enumerate(llm.scheduler.step_log) if s["prefill_tokens"] == 0 and s["decode_rows"] == args.batch]
-        log = list(llm.scheduler.step_log)
-        last = full[-1]
-        first = last - args.steps                   # the step before the first of the --steps timed ones
-        assert first >= 0 and all(i in full for i in range(first + 1, last + 1)), "too few full decode steps"
-        e2e_s = log[last]["t_end"] - log[first]["t_end"]
-        timed = log[first + 1:last + 1]
-        out["e2e"] = {"value": round(args.batch * args.steps / e2e_s, 1), "unit": "tok/s",
-                      "h2d_bytes_per_step": int(sum(s["h2d_bytes"] for s in timed) / len(timed)),
-                      "d2h_bytes_per_step": int(sum(s["d2h_bytes"] for s in timed) / len(timed)),
-                      "steps": len(timed)}
+        def end_to_end(batch, seed):
+            """--steps full decode steps of ``batch`` requests through the entry point, by the wall clock between
+            the ends of the steps (host token ids in, sampled tokens read back every step)."""
+            prompts = [B.random_prompt(PROMPT_LEN, c.vocab_size, seed + i) for i in range(batch)]
+            llm.generate(prompts, max_tokens=4, stop_at_eos=False)          # warm-up of the whole path
+            ahead = batch * PROMPT_LEN // 4096 + 8           # tokens the first request is ahead when the last joins
+            t0 = clocks.mark()
+            llm.generate(prompts, max_tokens=args.steps + ahead, stop_at_eos=False)
+            spans.append((t0, clocks.mark()))
+            log = list(llm.scheduler.step_log)
+            full = [i for i, s in enumerate(log) if s["prefill_tokens"] == 0 and s["decode_rows"] == batch]
+            last = full[-1]
+            first = last - args.steps                   # the step before the first of the --steps timed ones
+            assert first >= 0 and all(i in full for i in range(first + 1, last + 1)), "too few full decode steps"
+            seconds = log[last]["t_end"] - log[first]["t_end"]
+            timed = log[first + 1:last + 1]
+            return {"value": round(batch * args.steps / seconds, 1), "unit": "tok/s",
+                    "h2d_bytes_per_step": int(sum(s["h2d_bytes"] for s in timed) / len(timed)),
+                    "d2h_bytes_per_step": int(sum(s["d2h_bytes"] for s in timed) / len(timed)),
+                    "steps": len(timed)}
+
+        out["e2e"] = end_to_end(args.batch, 40)
+        for b, key in ((1, "e2e_b1"), (64, "e2e_b64")):
+            points[key] = end_to_end(b, 200 + b)["value"]
         out["points"] = points
         out["detail"] = detail
         if not args.skip_large:
