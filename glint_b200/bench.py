@@ -304,7 +304,16 @@ def run_cli_bench(args):
     else:
         batches = [n for n in (1, 2, 4, 8, 16, 32, 64) if n <= args.max_concurrent]
     modes = ("prefill", "decode", "serve") if args.mode == "all" else (("decode",) if args.mode == "concurrency" else (args.mode,))
-    serve_ranges = ((128, min(4096, args.context // 2 if args.context else 4096)), (64, 512))
+    if shape in SHAPES:
+        context = shape_config(shape, args.layers, args.context)["max_position_embeddings"]
+    else:
+        from .config import load_config
+        context = load_config(shape).model_spec().max_positions
+    # the workload's lengths, cut down for a model with a short context
+    serve_ranges = ((min(128, max(1, context // 8)), min(4096, context // 2)), (min(64, max(1, context // 16)), min(512, context // 4)))
+    if args.prompt_len + args.decode_tokens + args.warmup + 1 > context:
+        raise ValueError(f"--prompt-len {args.prompt_len} and --decode-tokens {args.decode_tokens} exceed the model's "
+                         f"context of {context} tokens")
     need = max(batches) * (args.prompt_len + args.decode_tokens + args.warmup + 64) if ("decode" in modes or "prefill" in modes) else 0
     if "serve" in modes:
         need = max(need, serve_cache_tokens(args.requests, *serve_ranges))

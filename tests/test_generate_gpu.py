@@ -227,6 +227,12 @@ def test_command_line(folders, tmp_path):
     assert p.returncode == 0 and "Output:" in p.stdout and "tok/s)" in p.stdout, p.stderr
     p = run("run", "-f", str(tmp_path / "nowhere"), "-p", "1", "-m", "1")
     assert p.returncode == 1 and "error:" in p.stderr
+    p = run("bench", "-f", out_dir, "--mode", "all", "--prompt-len", "24", "--decode-tokens", "6", "--batch", "1,3",
+            "--requests", "5", "--iters", "2", "--output", "json", "--dtype", "float32")
+    assert p.returncode == 0, p.stderr
+    rows = json.loads(p.stdout.strip().splitlines()[-1])["rows"]
+    assert [r["mode"] for r in rows] == ["prefill", "decode", "decode", "serve"]
+    assert all(r["tok_per_s"] > 0 for r in rows) and "frac_of_hbm_peak" in rows[1] and rows[3]["requests"] == 5
 
 
 def test_slot_record_follows_the_plain_generator(folders):
