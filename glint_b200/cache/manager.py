@@ -15,17 +15,23 @@ slot.  The slot also carries the request's length; the sampler's generator state
 the request in the scheduler.
 
 All bookkeeping is host-side and exact: a page is either free or owned by one slot of one
-group; taking is all-or-nothing; giving back a page that is not owned raises.
+group; taking is all-or-nothing; giving back a page that is not owned raises.  The bookkeeping
+itself (pools, block tables, slots, lengths) is C++ (``csrc/host/cache_core.cpp``); the classes
+here own the device storage, turn the core's codes into exceptions, and show its tables as
+numpy arrays.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
 from typing import Optional
 
+import ctypes
+
 import numpy as np
 import torch
 
 from ..errors import GlintError, PagePoolExhausted, SlotsExhausted
+from . import core
 
 
 class PagedNeed:
@@ -123,113 +129,95 @@ def cache_bytes_per_token(needs, cache_of, element_size):
 
 
 class PagePool:
-    """Free list of page ids 0..capacity-1 of one group (LIFO, so pages are reused soon)."""
+    """Free list of page ids 0..capacity-1 of one group (last in, first out, so pages are reused soon).
+    The list itself is kept by the C++ core; this class is its face."""
 
-    def __init__(self, name, capacity):
+    def __init__(self, name, capacity, handle=None):
         self.name = name
         self.capacity = int(capacity)
-        self._free = list(range(self.capacity - 1, -1, -1))
-        self._owned = [False] * self.capacity
-        self.peak_live = 0
-        self.reuses = 0
+        self._lib = core.lib()
+        self._own = handle is None
+        self._h = self._lib.glint_pool_create(self.capacity) if handle is None else handle
         self.hidden = 0          # pages held for the engine's own use: not counted in the statistics
-        self._ever_used = [False] * self.capacity
+
+    def __del__(self):
+        try:
+            if self._own and self._h:
+                self._lib.glint_pool_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+    def _stats(self):
+        out = (ctypes.c_longlong * 5)()
+        self._lib.glint_pool_stats(self._h, out)
+        return list(out)
 
     @property
     def available(self):
-        return len(self._free)
+        return self._stats()[3]
 
     @property
     def live(self):
-        return self.capacity - len(self._free)
+        return self._stats()[1]
+
+    @property
+    def peak_live(self):
+        return self._stats()[2]
+
+    @property
+    def reuses(self):
+        return self._stats()[4]
+
+    @property
+    def _free(self):
+        out = (ctypes.c_int * max(self.capacity, 1))()
+        n = self._lib.glint_pool_free_list(self._h, out, self.capacity)
+        return list(out[:n])
 
     def take(self, n):
-        if n > len(self._free):
-            raise PagePoolExhausted(self.name, n, len(self._free), self.capacity)
-        pages = [self._free.pop() for _ in range(n)]
-        for p in pages:
-            assert not self._owned[p], f"page {p} of {self.name} handed out twice"
-            self._owned[p] = True
-            if self._ever_used[p]:
-                self.reuses += 1
-            self._ever_used[p] = True
-        self.peak_live = max(self.peak_live, self.live)
-        return pages
+        out = (ctypes.c_int * max(n, 1))()
+        rc = self._lib.glint_pool_take(self._h, n, out)
+        if rc == core.EXHAUSTED:
+            raise PagePoolExhausted(self.name, n, self.available, self.capacity)
+        if rc != core.OK:
+            raise GlintError(f"page pool '{self.name}': bad request for {n} pages")
+        return list(out[:n])
 
     def give(self, pages):
-        for p in pages:
-            if not (0 <= p < self.capacity) or not self._owned[p]:
-                raise GlintError(f"page {p} of group '{self.name}' given back but not owned")
-            self._owned[p] = False
-            self._free.append(p)
+        arr, n = core.int_array([int(p) for p in pages])
+        bad = ctypes.c_int(-1)
+        if self._lib.glint_pool_give(self._h, arr, n, ctypes.byref(bad)) != core.OK:
+            raise GlintError(f"page {bad.value} of group '{self.name}' given back but not owned")
 
     def stats(self):
-        return {"capacity": self.capacity - self.hidden, "live": self.live - self.hidden,
-                "peak_live": self.peak_live - self.hidden, "pooled": self.available, "reuses": self.reuses}
+        _, live, peak, free, reuses = self._stats()
+        return {"capacity": self.capacity - self.hidden, "live": live - self.hidden,
+                "peak_live": peak - self.hidden, "pooled": free, "reuses": reuses}
 
 
 class PagedGroup:
-    """One pool, its device storage for all member layers, and the block tables of all slots."""
+    """One pool, its device storage for all member layers, and the block tables of all slots.  Pool and
+    tables live in the C++ core (``index`` is the group's place there); ``table``, ``first_live`` and
+    ``end_live`` are views of its memory."""
 
-    def __init__(self, need, members, num_pages, num_slots, page_size, max_positions, dtype, device):
+    def __init__(self, need, members, handle, index, num_pages, num_slots, page_size, max_positions, dtype, device):
+        lib = core.lib()
         self.need = need
         self.name = need.group_name()
         self.members = list(members)          # run-order indices that own a layer of storage here
         self.page_size = page_size
         self.num_pages = num_pages
         self.max_pages = (max_positions + page_size - 1) // page_size
-        self.pool = PagePool(self.name, num_pages)
+        self.pool = PagePool(self.name, num_pages, handle=lib.glint_cache_pool(handle, index))
         self.element_size = torch.empty((), dtype=dtype).element_size()
         self.storage = need.allocate(len(self.members), num_pages, page_size, dtype, device)
-        self.table = np.full((num_slots, self.max_pages), -1, dtype=np.int32)
-        self.first_live = np.zeros(num_slots, dtype=np.int64)   # first page index still held
-        self.end_live = np.zeros(num_slots, dtype=np.int64)     # one past the last page held
+        self.table = core.as_array(lib.glint_cache_table(handle, index), (num_slots, self.max_pages))
+        self.first_live = core.as_array(lib.glint_cache_first_live(handle, index), (num_slots,))   # first page index still held
+        self.end_live = core.as_array(lib.glint_cache_end_live(handle, index), (num_slots,))       # one past the last page held
 
     def bytes_per_token(self):
         return len(self.members) * self.need.bytes_per_token(self.element_size)
-
-    # pages that queries at positions >= start can still reach begin at this page index
-    def _first_needed_page(self, start):
-        if self.need.window is None:
-            return 0
-        return max(0, start - self.need.window + 1) // self.page_size
-
-    def release_behind(self, slot, start):
-        """Give back pages that no query at position >= ``start`` can reach."""
-        first = min(self._first_needed_page(start), int(self.end_live[slot]))
-        lo = int(self.first_live[slot])
-        if first > lo:
-            pages = [int(p) for p in self.table[slot, lo:first] if p >= 0]
-            self.pool.give(pages)
-            self.table[slot, lo:first] = -1
-            self.first_live[slot] = first
-        return max(0, first - lo)
-
-    def pages_needed(self, slot, start, n):
-        """How many new pages the tokens [start, start+n) need beyond those already held."""
-        end_page = (start + n + self.page_size - 1) // self.page_size
-        begin = max(int(self.end_live[slot]), self._first_needed_page(start))
-        return max(0, end_page - begin)
-
-    def extend(self, slot, start, n):
-        end_page = (start + n + self.page_size - 1) // self.page_size
-        begin = max(int(self.end_live[slot]), self._first_needed_page(start))
-        if end_page > self.max_pages:
-            raise GlintError(f"positions up to {start + n} exceed the block table of {self.max_pages} pages")
-        if end_page > begin:
-            pages = self.pool.take(end_page - begin)
-            self.table[slot, begin:end_page] = pages
-            if int(self.end_live[slot]) == int(self.first_live[slot]):
-                self.first_live[slot] = begin     # nothing was held: the held range starts here
-            self.end_live[slot] = end_page
-
-    def release_all(self, slot):
-        lo, hi = int(self.first_live[slot]), int(self.end_live[slot])
-        pages = [int(p) for p in self.table[slot, lo:hi] if p >= 0]
-        self.pool.give(pages)
-        self.table[slot, :] = -1
-        self.first_live[slot] = 0
-        self.end_live[slot] = 0
 
     def owned_pages(self, slot):
         return [int(p) for p in self.table[slot] if p >= 0]
@@ -270,9 +258,15 @@ class CacheManager:
         for i, need in enumerate(needs):
             if is_paged(need) and cache_of[i] is None:
                 by_key.setdefault(need.group_key(), (need, []))[1].append(i)
+        # pools, block tables, slots and lengths are kept by the C++ core, one group per distinct need
+        self._lib = core.lib()
+        windows, n_groups = core.int_array([-1 if need.window is None else int(need.window) for need, _ in by_key.values()])
+        self._h = self._lib.glint_cache_create(n_groups, windows, num_slots, num_pages, page_size, max_positions)
+        if not self._h:
+            raise GlintError("the cache core refused these sizes")
         placed = {}
-        for need, members in by_key.values():
-            g = PagedGroup(need, members, num_pages, num_slots, page_size, max_positions, dtype, device)
+        for index, (need, members) in enumerate(by_key.values()):
+            g = PagedGroup(need, members, self._h, index, num_pages, num_slots, page_size, max_positions, dtype, device)
             self.groups.append(g)
             for j, i in enumerate(members):
                 placed[i] = (g, j)
@@ -289,9 +283,16 @@ class CacheManager:
             elif need is not None and not is_paged(need):
                 self.states[i] = need.allocate(num_slots, device)
         self.named_states = {}
-        self._free_slots = list(range(num_slots - 1, -1, -1))
-        self._slot_live = [False] * num_slots
-        self.lengths = np.zeros(num_slots, dtype=np.int64)
+        self.lengths = core.as_array(self._lib.glint_cache_lengths(self._h), (num_slots,))
+
+    def __del__(self):
+        try:
+            if self._h:
+                self.groups.clear()                     # their views point into the core's memory
+                self._lib.glint_cache_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
 
     def add_state(self, name, need):
         """A fixed-size record per request slot for something beside the mixers (the sampler keeps the
@@ -306,46 +307,47 @@ class CacheManager:
 
     @property
     def free_slots(self):
-        return len(self._free_slots)
+        return self._lib.glint_cache_free_slots(self._h)
+
+    def slot_live(self, slot):
+        return bool(self._lib.glint_cache_slot_live(self._h, int(slot)))
 
     def alloc_slot(self):
-        if not self._free_slots:
+        slot = ctypes.c_int(-1)
+        if self._lib.glint_cache_alloc_slot(self._h, ctypes.byref(slot)) != core.OK:
             raise SlotsExhausted(f"all {self.num_slots} request slots are in use")
-        slot = self._free_slots.pop()
-        self._slot_live[slot] = True
-        self.lengths[slot] = 0
         for st in list(self.states) + list(self.named_states.values()):
             if st is not None:
-                st[slot].zero_()
-        return slot
+                st[slot.value].zero_()
+        return slot.value
 
     def free_slot(self, slot):
-        if not (0 <= slot < self.num_slots) or not self._slot_live[slot]:
+        bad = ctypes.c_int(-1)
+        rc = self._lib.glint_cache_free_slot(self._h, int(slot), ctypes.byref(bad))
+        if rc == core.SLOT_NOT_LIVE:
             raise GlintError(f"slot {slot} freed but not in use")
-        for g in self.groups:
-            g.release_all(slot)
-        self._slot_live[slot] = False
-        self.lengths[slot] = 0
-        self._free_slots.append(slot)
+        if rc != core.OK:
+            raise GlintError(f"page {bad.value} of slot {slot} given back but not owned")
 
     def length(self, slot):
         return int(self.lengths[slot])
 
     # ---- pages ----------------------------------------------------------------------------------
 
+    @staticmethod
+    def _rows(rows):
+        slots, n = core.int_array([int(s) for s, _ in rows])
+        counts, _ = core.int_array([int(k) for _, k in rows])
+        return slots, counts, n
+
     def pages_short(self, rows):
         """For ``rows`` = [(slot, n_new_tokens)], the first group that cannot serve them all as
         (group name, needed, available), or ``None``.  Counts pages a window frees first."""
-        for g in self.groups:
-            need = 0
-            freed = 0
-            for slot, n in rows:
-                start = int(self.lengths[slot])
-                first = min(g._first_needed_page(start), int(g.end_live[slot]))
-                freed += max(0, first - int(g.first_live[slot]))
-                need += g.pages_needed(slot, start, n)
-            if need > g.pool.available + freed:
-                return (g.name, need, g.pool.available + freed)
+        slots, counts, n = self._rows(rows)
+        group, need, have = ctypes.c_int(0), ctypes.c_longlong(0), ctypes.c_longlong(0)
+        if self._lib.glint_cache_pages_short(self._h, slots, counts, n, ctypes.byref(group), ctypes.byref(need),
+                                             ctypes.byref(have)):
+            return (self.groups[group.value].name, need.value, have.value)
         return None
 
     def reserve(self, rows):
@@ -355,27 +357,29 @@ class CacheManager:
         either every group serves every row, or ``PagePoolExhausted`` is raised and no page
         was taken.  Also raises when a row would pass the model's context length.
         """
-        for slot, n in rows:
-            if not self._slot_live[slot]:
-                raise GlintError(f"slot {slot} is not in use")
-            if int(self.lengths[slot]) + n > self.max_positions:
-                raise GlintError(f"slot {slot}: {int(self.lengths[slot]) + n} positions exceed the "
-                                 f"context length {self.max_positions}")
-        for g in self.groups:
-            for slot, n in rows:
-                g.release_behind(slot, int(self.lengths[slot]))
-        for g in self.groups:
-            need = sum(g.pages_needed(slot, int(self.lengths[slot]), n) for slot, n in rows)
-            if need > g.pool.available:
-                raise PagePoolExhausted(g.name, need, g.pool.available, g.pool.capacity)
-        for g in self.groups:
-            for slot, n in rows:
-                g.extend(slot, int(self.lengths[slot]), n)
+        slots, counts, n = self._rows(rows)
+        slot, group, need, have = ctypes.c_int(-1), ctypes.c_int(0), ctypes.c_longlong(0), ctypes.c_longlong(0)
+        rc = self._lib.glint_cache_reserve(self._h, slots, counts, n, ctypes.byref(slot), ctypes.byref(group),
+                                           ctypes.byref(need), ctypes.byref(have))
+        if rc == core.OK:
+            return
+        if rc == core.EXHAUSTED:
+            g = self.groups[group.value]
+            raise PagePoolExhausted(g.name, need.value, have.value, g.pool.capacity)
+        if rc == core.SLOT_NOT_LIVE:
+            raise GlintError(f"slot {slot.value} is not in use")
+        if rc == core.CONTEXT:
+            asked = dict((int(s), int(k)) for s, k in rows)[slot.value]
+            raise GlintError(f"slot {slot.value}: {self.length(slot.value) + asked} positions exceed the "
+                             f"context length {self.max_positions}")
+        if rc == core.TABLE_FULL:
+            raise GlintError(f"slot {slot.value}: positions exceed the block table of {self.groups[0].max_pages} pages")
+        raise GlintError(f"the cache core failed with code {rc}")
 
     def advance(self, rows):
         """After the step ran: the slots now hold ``n`` more tokens each."""
-        for slot, n in rows:
-            self.lengths[slot] += n
+        slots, counts, n = self._rows(rows)
+        self._lib.glint_cache_advance(self._h, slots, counts, n)
 
     def block_tables(self, slots):
         """Per group, the block-table rows of ``slots`` as one int32 array [len(slots), max_pages]."""
@@ -400,7 +404,7 @@ class CacheManager:
                     if p in seen:
                         raise AssertionError(f"page {p} of {g.name} held by slots {seen[p]} and {slot}")
                     seen[p] = slot
-                    if not self._slot_live[slot]:
+                    if not self.slot_live(slot):
                         raise AssertionError(f"page {p} of {g.name} held by free slot {slot}")
             free = set(g.pool._free)
             if len(free) != len(g.pool._free):

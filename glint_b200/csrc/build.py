@@ -1,8 +1,10 @@
-"""Builds the CUDA kernels for sm_100a with nvcc and loads them through ctypes.
+"""Builds the CUDA kernels for sm_100a with nvcc, and the host-side C++ with the C++ compiler, and
+loads them through ctypes.
 
 Sources are grouped into libraries so that a process compiles only what its model and
-dtype need: ``core`` (plain kernels, both dtypes) and ``tensor`` (tcgen05/TMA kernels,
-bfloat16 only).  A library is rebuilt when the hash of its sources and flags changes.  It is
+dtype need: ``core`` (plain kernels and the step runtime, both dtypes), ``tensor`` (tcgen05/TMA
+kernels, bfloat16 only) and ``host`` (the cache manager's bookkeeping: no CUDA, so it builds and
+runs where there is no GPU and no nvcc).  A library is rebuilt when the hash of its sources and flags changes.  It is
 built inside the package (``csrc/_build``) when that folder can be written, else under the
 system's temporary folder; nothing depends on HOME.  While nvcc runs, a line is printed to
 stderr every few seconds.
@@ -31,8 +33,12 @@ NVCC_FLAGS += os.environ.get("GLINT_NVCC_EXTRA", "").split()
 LIBRARIES = {
     "core": ["elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu", "sample_noalloc.cu", "runtime.cu"],
     "tensor": ["gemm_tcgen05.cu", "gemm_skinny.cu", "attention_decode.cu", "attention_prefill.cu", "attention_tcgen05.cu"],
+    "host": ["host/cache_core.cpp"],
 }
 HEADERS = ["common.cuh", "tcgen05.cuh", "noalloc.h", "runtime.h"]
+HOST_LIBRARIES = {"host"}                 # plain C++: compiled without nvcc
+HOST_HEADERS = ["host/cache_core.h"]
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall"]
 
 _loaded = {}
 _lock = threading.Lock()
@@ -50,14 +56,23 @@ def find_nvcc():
                       "the CUDA kernels cannot be built and there is no fallback")
 
 
+def find_cxx():
+    for cand in (os.environ.get("GLINT_CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
+            return cand
+    raise KernelError("no C++ compiler found (looked at $GLINT_CXX, g++, c++, clang++): the host-side library "
+                      "cannot be built")
+
+
 def _sources(name):
     return [os.path.join(CSRC, s) for s in LIBRARIES[name] if os.path.isfile(os.path.join(CSRC, s))]
 
 
 def _digest(name):
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS).encode())
-    for path in _sources(name) + [os.path.join(CSRC, x) for x in HEADERS]:
+    host = name in HOST_LIBRARIES
+    h.update(" ".join(HOST_FLAGS if host else NVCC_FLAGS).encode())
+    for path in _sources(name) + [os.path.join(CSRC, x) for x in (HOST_HEADERS if host else HEADERS)]:
         if os.path.isfile(path):
             h.update(os.path.basename(path).encode())
             with open(path, "rb") as f:
@@ -98,6 +113,7 @@ def library_path(name):
 
 def _run_with_heartbeat(cmds, what):
     """Run the commands in parallel, printing a line every few seconds until all are done."""
+    compiler = os.path.basename(cmds[0][0]) if cmds else "compiler"
     t0 = time.time()
     procs = [(c, subprocess.Popen(c, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)) for c in cmds]
     outputs = [None] * len(procs)
@@ -120,7 +136,7 @@ def _run_with_heartbeat(cmds, what):
         t.join()
     for (cmd, p), out in zip(procs, outputs):
         if p.returncode != 0:
-            raise KernelError(f"nvcc failed ({p.returncode}): {' '.join(cmd)}\n{out}")
+            raise KernelError(f"{compiler} failed ({p.returncode}): {' '.join(cmd)}\n{out}")
 
 
 def build_library(name, verbose=True):
@@ -134,24 +150,31 @@ def build_library(name, verbose=True):
         srcs = _sources(name)
         if not srcs:
             raise KernelError(f"kernel library '{name}' has no sources in {CSRC}")
-        nvcc = find_nvcc()
+        host = name in HOST_LIBRARIES
+        nvcc = None if host else find_nvcc()
         out_dir = _writable_dir()
         tag = _digest(name)
         final = os.path.join(out_dir, f"libglint_{name}_{tag}.so")
         work = tempfile.mkdtemp(prefix=f"{name}_{tag}_", dir=out_dir)
         try:
-            if verbose:
-                _say(f"compiling kernel library '{name}' for sm_100a ({len(srcs)} files) into {out_dir}")
             t0 = time.time()
-            objs, cmds = [], []
-            for s in srcs:
-                o = os.path.join(work, os.path.basename(s) + ".o")
-                objs.append(o)
-                cmds.append([nvcc] + NVCC_FLAGS + ["-I", CSRC, "-c", s, "-o", o])
-            _run_with_heartbeat(cmds, f"'{name}'")
             tmp_so = os.path.join(work, "lib.so")
-            _run_with_heartbeat([[nvcc] + ARCH_FLAGS + ["-shared", "-o", tmp_so] + objs],
-                                f"'{name}' (link)")
+            if host:
+                if verbose:
+                    _say(f"compiling host library '{name}' ({len(srcs)} files) into {out_dir}")
+                _run_with_heartbeat([[find_cxx()] + HOST_FLAGS + ["-I", CSRC, "-shared", "-o", tmp_so] + srcs],
+                                    f"'{name}'")
+            else:
+                if verbose:
+                    _say(f"compiling kernel library '{name}' for sm_100a ({len(srcs)} files) into {out_dir}")
+                objs, cmds = [], []
+                for s in srcs:
+                    o = os.path.join(work, os.path.basename(s) + ".o")
+                    objs.append(o)
+                    cmds.append([nvcc] + NVCC_FLAGS + ["-I", CSRC, "-c", s, "-o", o])
+                _run_with_heartbeat(cmds, f"'{name}'")
+                _run_with_heartbeat([[nvcc] + ARCH_FLAGS + ["-shared", "-o", tmp_so] + objs],
+                                    f"'{name}' (link)")
             os.replace(tmp_so, final)  # atomic: concurrent builders never see a partial file
             for old in os.listdir(out_dir):  # drop builds of earlier source versions
                 if old.startswith(f"libglint_{name}_") and old.endswith(".so") and old != os.path.basename(final):
