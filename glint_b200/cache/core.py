@@ -35,6 +35,7 @@ def lib():
             "glint_cache_reserve": (I, [P, IP, IP, I, IP, IP, LP, LP]),
             "glint_cache_advance": (None, [P, IP, IP, I]),
             "glint_cache_release_behind": (I, [P, I, I, LL]),
+            "glint_cache_plan": (I, [P, I, I, I, IP, IP, IP, I, IP, IP, IP]),
         }
         for name, (res, args) in sig.items():
             f = getattr(l, name)

@@ -350,6 +350,23 @@ class CacheManager:
             return (self.groups[group.value].name, need.value, have.value)
         return None
 
+    def plan(self, budget, max_active, running, waiting):
+        """One step's plan for a continuous-batching scheduler, decided by the C++ core: ``running`` holds
+        (slot, tokens still to compute, is it decoding) per running request in admission order, ``waiting``
+        the tokens to compute per queued request in queue order.  Decoding requests first with one token each,
+        then running prompts with what the budget leaves, then admissions while slots are free; a row joins
+        only if the cache can serve it together with the rows before it.  Returns (tokens per running request,
+        tokens per admitted request); takes no page and no slot."""
+        slots, n_run = core.int_array([int(r[0]) for r in running])
+        remaining, _ = core.int_array([int(r[1]) for r in running])
+        decoding, _ = core.int_array([1 if r[2] else 0 for r in running])
+        wait, n_wait = core.int_array([int(w) for w in waiting])
+        out_run = (ctypes.c_int * max(n_run, 1))()
+        out_wait = (ctypes.c_int * max(n_wait, 1))()
+        admitted = self._lib.glint_cache_plan(self._h, int(budget), int(max_active), n_run, slots, remaining, decoding,
+                                              n_wait, wait, out_run, out_wait)
+        return list(out_run[:n_run]), list(out_wait[:admitted])
+
     def reserve(self, rows):
         """Make room for ``n`` more tokens of each (slot, n) in ``rows``; all or nothing.
 

@@ -187,8 +187,10 @@ extern "C" int glint_cache_release_behind(GlintCache* c, int group, int slot, lo
   return 0;
 }
 
-extern "C" int glint_cache_pages_short(const GlintCache* c, const int* slots, const int* counts, int n, int* group,
-                                       long long* need, long long* available) {
+// Rows of live slots, and `fresh` rows of requests that would start in a slot of their own (nothing cached,
+// nothing held): the first group that cannot serve them all, or none.
+static int short_for(const GlintCache* c, const int* slots, const int* counts, int n, const int* fresh, int n_fresh,
+                     int* group, long long* need, long long* available) {
   for (int gi = 0; gi < (int)c->groups.size(); ++gi) {
     const Group& g = c->groups[gi];
     long long want = 0, freed = 0;
@@ -197,13 +199,97 @@ extern "C" int glint_cache_pages_short(const GlintCache* c, const int* slots, co
       freed += c->freed_behind(g, slots[i], start);
       want += c->pages_needed(g, slots[i], start, counts[i]);
     }
+    for (int i = 0; i < n_fresh; ++i) want += ((long long)fresh[i] + c->page_size - 1) / c->page_size;
     const long long have = (long long)g.pool->free_list.size() + freed;
     if (want > have) {
-      *group = gi; *need = want; *available = have;
+      if (group) *group = gi;
+      if (need) *need = want;
+      if (available) *available = have;
       return 1;
     }
   }
   return 0;
+}
+
+extern "C" int glint_cache_pages_short(const GlintCache* c, const int* slots, const int* counts, int n, int* group,
+                                       long long* need, long long* available) {
+  return short_for(c, slots, counts, n, nullptr, 0, group, need, available);
+}
+
+// One step's plan (the reference's engine loop admits first-come while fewer than max_active run and
+// decodes one token per live sequence per step, src/server/engine.rs:489-511, :650-669; the token budget and
+// the portions are this engine's).  Running requests come in admission order with their slot, the tokens
+// they still have to compute, and whether they are decoding (one token behind their newest); waiting ones
+// in queue order with their tokens.  Decoding requests go first with one token each, then running prompts
+// with as much as the budget leaves, then new admissions while a slot is free; a row joins only if the cache
+// can serve it together with the rows before it.  out_running[i] and out_waiting[i] get the tokens of that
+// request in this step (0: not in it); admissions stop at the first waiting request that does not fit.
+// Returns the number of admissions.  Takes no page and no slot.
+extern "C" int glint_cache_plan(const GlintCache* c, int budget, int max_active, int n_running, const int* slots,
+                                const int* remaining, const int* decoding, int n_waiting, const int* waiting,
+                                int* out_running, int* out_waiting) {
+  std::vector<int> row_slots, row_counts, fresh;
+  row_slots.reserve(n_running);
+  row_counts.reserve(n_running);
+  for (int i = 0; i < n_running; ++i) out_running[i] = 0;
+  for (int i = 0; i < n_waiting; ++i) out_waiting[i] = 0;
+  auto fits = [&](int slot, int n) {
+    row_slots.push_back(slot);
+    row_counts.push_back(n);
+    const bool ok = !short_for(c, row_slots.data(), row_counts.data(), (int)row_slots.size(), nullptr, 0, nullptr,
+                               nullptr, nullptr);
+    if (!ok) {
+      row_slots.pop_back();
+      row_counts.pop_back();
+    }
+    return ok;
+  };
+  // the usual case: every decoding request fits, one check
+  int n_decoding = 0;
+  for (int i = 0; i < n_running; ++i)
+    if (decoding[i]) {
+      row_slots.push_back(slots[i]);
+      row_counts.push_back(1);
+      ++n_decoding;
+    }
+  if (n_decoding > 0 && n_decoding <= budget &&
+      !short_for(c, row_slots.data(), row_counts.data(), n_decoding, nullptr, 0, nullptr, nullptr, nullptr)) {
+    for (int i = 0; i < n_running; ++i)
+      if (decoding[i]) out_running[i] = 1;
+    budget -= n_decoding;
+  } else {
+    row_slots.clear();
+    row_counts.clear();
+    for (int i = 0; i < n_running; ++i)
+      if (decoding[i] && budget >= 1 && fits(slots[i], 1)) {
+        out_running[i] = 1;
+        --budget;
+      }
+  }
+  for (int i = 0; i < n_running; ++i) {
+    if (decoding[i]) continue;
+    const int n = std::min(remaining[i], budget);
+    if (n > 0 && fits(slots[i], n)) {        // a portion that does not fit waits for pages
+      out_running[i] = n;
+      budget -= n;
+    }
+  }
+  int admitted = 0;
+  int free_slots = (int)c->free_slots.size();
+  while (admitted < n_waiting && budget > 0 && n_running + admitted < max_active && free_slots > 0) {
+    const int n = std::min(waiting[admitted], budget);
+    fresh.push_back(n);
+    if (short_for(c, row_slots.data(), row_counts.data(), (int)row_slots.size(), fresh.data(), (int)fresh.size(),
+                  nullptr, nullptr, nullptr)) {
+      fresh.pop_back();
+      break;
+    }
+    out_waiting[admitted] = n;
+    budget -= n;
+    --free_slots;
+    ++admitted;
+  }
+  return admitted;
 }
 
 extern "C" int glint_cache_reserve(GlintCache* c, const int* slots, const int* counts, int n, int* info_slot,

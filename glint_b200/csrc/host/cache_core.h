@@ -54,6 +54,11 @@ int glint_cache_slot_live(const GlintCache* c, int slot);
 // needs and has (pages that a window frees first are counted as available).
 int glint_cache_pages_short(const GlintCache* c, const int* slots, const int* counts, int n, int* group,
                             long long* need, long long* available);
+// One step's plan for a continuous-batching scheduler: which running requests run how many tokens and how many
+// waiting requests are admitted with how many tokens (see cache_core.cpp); takes no page and no slot.
+int glint_cache_plan(const GlintCache* c, int budget, int max_active, int n_running, const int* slots,
+                     const int* remaining, const int* decoding, int n_waiting, const int* waiting, int* out_running,
+                     int* out_waiting);
 // Room for counts[i] more tokens of slots[i]; all or nothing.  Pages behind a window are given back first.
 int glint_cache_reserve(GlintCache* c, const int* slots, const int* counts, int n, int* info_slot, int* group,
                         long long* need, long long* available);

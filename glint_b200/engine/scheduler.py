@@ -145,47 +145,26 @@ class Scheduler:
     # ---- planning ---------------------------------------------------------------------------------
 
     def plan(self):
-        """Decide the next step: a list of (request, number of tokens).  Admits waiting requests
-        (taking slots) but takes no pages; ``engine.step`` reserves them all-or-nothing, and the
-        plan only holds rows that the cache can serve together."""
+        """Decide the next step: a list of (request, number of tokens).  The decision itself (decoding
+        requests first, running prompts under the budget, admissions while slots and pages allow) is the
+        cache core's (``CacheManager.plan``, C++); this admits the requests it names (taking slots) but takes
+        no pages: ``engine.step`` reserves them all-or-nothing, and the plan only holds rows that the cache can
+        serve together."""
         cache = self.engine.cache
-        budget = self.max_step_tokens
-        rows = []
-
-        def fits(req, n):
-            return cache.pages_short([(r.slot, k) for r, k in rows] + [(req.slot, n)]) is None
-
-        decoding = [r for r in self.running if r.computed == r.num_tokens - 1 and r.generated]
-        prefilling = [r for r in self.running if not (r.computed == r.num_tokens - 1 and r.generated)]
-        if decoding and len(decoding) <= budget and \
-                cache.pages_short([(r.slot, 1) for r in decoding]) is None:
-            rows = [(r, 1) for r in decoding]        # the usual case: every decoder fits, one check
-            budget -= len(decoding)
-        else:
-            for r in decoding:
-                if budget >= 1 and fits(r, 1):
-                    rows.append((r, 1))
-                    budget -= 1
-        for r in prefilling:
-            n = min(r.num_tokens - r.computed, budget)
-            if n > 0 and fits(r, n):   # a portion that does not fit waits for pages
-                rows.append((r, n))
-                budget -= n
-        while (self.waiting and budget > 0 and len(self.running) < self.max_active
-               and cache.free_slots > 0):
-            r = self.waiting[0]
-            n = min(r.num_tokens - r.computed, budget)
+        running = [(r.slot, r.num_tokens - r.computed, r.computed == r.num_tokens - 1 and r.generated > 0)
+                   for r in self.running]
+        waiting = [r.num_tokens - r.computed for r in self.waiting]
+        run_counts, admit_counts = cache.plan(self.max_step_tokens, self.max_active, running, waiting)
+        decoders = [(r, n) for r, n, row in zip(self.running, run_counts, running) if n and row[2]]
+        portions = [(r, n) for r, n, row in zip(self.running, run_counts, running) if n and not row[2]]
+        rows = decoders + portions
+        for n in admit_counts:
+            r = self.waiting.popleft()
             r.slot = self.engine.open()
-            if not fits(r, n):
-                self.engine.close(r.slot)
-                r.slot = None
-                break
-            self.waiting.popleft()
             self.running.append(r)
             if hasattr(self.sampler, "admit"):       # options and generator state go into the slot, once
                 self.sampler.admit(r.slot, r.params, r.rng_state, r.computed, len(r.output))
             rows.append((r, n))
-            budget -= n
         return rows
 
     def _preempt_or_finish(self):
