@@ -699,7 +699,8 @@ def test_runtime_routes_products_by_size():
     """Which product kernel the native runtime takes: the weight-streaming one up to 8 tokens, and from 9 to
     16 for small matrices; the tiled one beyond; neither when K is no multiple of 8 (CUDA cores then)."""
     from glint_b200 import ops_tensor
-    assert ops_tensor.route_linear(1, 4096, 2304) == 1 and ops_tensor.route_linear(8, 36864, 4608) == 1
+    assert ops_tensor.route_linear(1, 4096, 2304) == 1 and ops_tensor.route_linear(8, 9216, 2304) == 1
+    assert ops_tensor.route_linear(8, 36864, 4608) == 2            # the widest matrices stream on the tiled kernel
     assert ops_tensor.route_linear(16, 2304, 2048) == 1            # 9 to 16 tokens, a small matrix
     assert ops_tensor.route_linear(16, 9216, 2304) == 2            # 9 to 16 tokens, a large one
     assert ops_tensor.route_linear(17, 2304, 2048) == 2 and ops_tensor.route_linear(2048, 4096, 2304) == 2
