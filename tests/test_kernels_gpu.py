@@ -709,3 +709,4 @@ def test_runtime_routes_products_by_size():
     assert ops_tensor.route_linear(4, 4096, 2300) == 0
     assert ops_tensor.decode_splits(1, 4, 8192, 148) == 16 and ops_tensor.decode_splits(8, 4, 2304, 148) == 8
     assert ops_tensor.decode_splits(64, 4, 2304, 148) == 1 and ops_tensor.decode_splits(8, 4, 200, 148) == 1
+    assert ops_tensor.decode_splits(9, 4, 2304, 148) == 4          # 36 clusters of 8 would not fit the SMs at once
