@@ -782,8 +782,8 @@ static int gemm_launch(const void* x, const void* w, void* out, int out_bf16, in
     for (int cand = 1; cand <= 32 && tiles * cand <= sms && cand <= p.total_kb; ++cand) {
       const int per = (p.total_kb + cand - 1) / cand;
       // spread over the tile's blocks, the reduction costs the wait for the slowest block and one tile's worth of reads
-      const float reduce = 4.0f + 0.04f * width;
-      const float kb_us = fmaxf(0.3f, 0.0015f * width);       // a K block: instruction-bound for narrow tiles, tensor-bound for wide ones
+      const float reduce = 6.0f + 0.04f * width;
+      const float kb_us = fmaxf(0.2f, 0.0015f * width);       // a K block: instruction-bound for narrow tiles, tensor-bound for wide ones
       const float est = kb_us * per + (cand > 1 ? reduce : 0.f);
       if (est < best) {
         best = est;
