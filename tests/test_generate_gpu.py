@@ -276,3 +276,39 @@ def test_slot_record_follows_the_plain_generator(folders):
     again = LLM(folders["A"], dtype="float32", cache_tokens=512, max_active=3, max_step_tokens=16, lookahead=False)
     want = again.generate(drawing.prompt, max_tokens=40, temperature=0.9, top_k=5, seed=11, stop_at_eos=False)
     assert drawing.output[:len(before)] == before and drawing.output == want
+
+
+@pytest.mark.parametrize("temperature", [0.0, 0.7])
+def test_eleven_requests_through_padded_graphs(folders, temperature):
+    """Eleven requests decode in steps that replay the graph of twelve rows (one row of the engine's spare slot),
+    with the next step launched ahead; output lengths differ, so the batch shrinks through 10, 9 (both padded to
+    12) and 8 rows.  Greedy: the plain implementation's tokens.  Sampled: the tokens each request gets alone (its
+    generator is its own)."""
+    from glint_b200 import LLM
+    from glint_b200.engine.scheduler import Request
+    from glint_b200.sampling import SamplingParams
+    vocab = TINY["A"][0]["vocab_size"]
+    prompts = [random_tokens(6 + 2 * i, vocab, 300 + i) for i in range(11)]
+    budgets = [14 - (i % 4) * 3 for i in range(11)]
+    llm = LLM(folders["A"], dtype="float32", cache_tokens=2048, max_active=16, max_step_tokens=64)
+    requests = [Request(("r", i), p, budgets[i], SamplingParams(temperature=temperature, seed=40 + i), None)
+                for i, p in enumerate(prompts)]
+    for r in requests:
+        llm.scheduler.add(r)
+    llm.scheduler.run()
+    llm.model.rt.check_status()
+    assert llm.engine.graph_counts["replayed"] > 0
+    assert [len(r.output) for r in requests] == budgets
+    alone = LLM(folders["A"], dtype="float32", cache_tokens=512, max_active=2, max_step_tokens=64)
+    for i, r in enumerate(requests):
+        if temperature == 0.0:
+            want, margins = _plain_greedy(folders["A"], prompts[i], budgets[i])
+            for k, (a, b) in enumerate(zip(r.output, want)):
+                if a != b:
+                    assert margins[k] < 1e-4, (i, k, r.output, want)
+                    break
+        elif i % 3 == 0:
+            want = alone.generate(prompts[i], max_tokens=budgets[i], temperature=temperature, seed=40 + i,
+                                  stop_at_eos=False)
+            assert r.output == want, (i, r.output, want)
+    assert all(s["live"] == 0 for s in llm.cache_stats().values())
