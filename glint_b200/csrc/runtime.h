@@ -22,6 +22,8 @@ struct GlintStep {
   long long id;                 // increases with every step: what is computed once per step is marked with it
   int num_tokens, num_seqs, max_seq_len, max_context;
   int leading_single, leading_single_context, num_logit_rows, num_groups;
+  int uneven;                   // how far the single tokens' contexts fall short of the longest: their sum is
+                                // about (requests x longest) >> uneven
   const int* token_ids;         // [tokens]
   const int* positions;         // [tokens]
   const int* token_seq;         // [tokens] the token's request within the step = its block-table row
@@ -99,7 +101,7 @@ int glint_route_linear(const GlintRuntime* rt, int M, int N, int K);
 long long glint_native_launches();
 // Operations that a tensor-core runtime ran on CUDA cores because no tensor-core kernel takes their sizes.
 long long glint_native_fallbacks();
-int glint_decode_splits(int tokens, int nkv, int max_context, int sms);
+int glint_decode_splits(int tokens, int nkv, int max_context, int uneven, int sms);
 
 // ---- programs ------------------------------------------------------------------------------------------
 struct GlintProgram;

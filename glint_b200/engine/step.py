@@ -45,6 +45,18 @@ def padded_size(n):
     return (n + 15) & ~15
 
 
+def _uneven(contexts):
+    """How far the contexts of a step's single tokens fall short of the longest of them: 0 when they add
+    up to more than 0.7 of (their number x the longest), 1 down to 0.35, 2 down to 0.175, else 3.  The
+    split attention kernel shares a long context among more blocks when most others are short."""
+    if not contexts:
+        return 0
+    share, level, bound = sum(contexts) / (len(contexts) * max(contexts)), 0, 0.7
+    while level < 3 and share <= bound:
+        level, bound = level + 1, bound / 2
+    return level
+
+
 class StepContext:
     """Everything about one step that parts may read.  Device tensors are int32.
 
@@ -54,7 +66,7 @@ class StepContext:
     one more than requests) are per request; ``logit_rows`` are the token rows whose logits are
     wanted and ``logit_slots`` the request slots of those rows.  ``leading_single`` counts the requests at the front of the step that bring a single
     token (a scheduler puts its decoding requests first), ``leading_single_context`` is the longest
-    context among them.  The ``h_`` fields are host copies for
+    context among them and ``uneven`` says how far the others fall short of it.  The ``h_`` fields are host copies for
     planning launches.  ``memo`` is empty at the start of
     a step: parts keep there what several layers of the step share (a table of rotation angles, say),
     under a key of their own parameters.
@@ -76,6 +88,7 @@ class StepContext:
         self.leading_single = next((i for i, l in enumerate(lens) if l != 1), n)   # requests in front that bring one token
         self.max_context = max(s + l for s, l in zip(self.h_seq_start, lens))
         self.leading_single_context = max([s + 1 for s in self.h_seq_start[:self.leading_single]] or [0])
+        self.uneven = _uneven([s + 1 for s in self.h_seq_start[:self.leading_single]])
         rows, row_slots = [], []
         for i, e in enumerate(entries):
             for w in e.want:
@@ -306,8 +319,8 @@ class Engine:
     def _graph_key(self, entries, ctx):
         """Steps of single tokens with logits wanted for each are launch-bound: they replay a
         captured graph.  The key holds everything a captured launch depends on beyond the
-        step's device metadata: the number of requests, and the context bucket that sizes the
-        split of the attention kernels."""
+        step's device metadata: the number of requests, the context bucket that sizes the
+        split of the attention kernels, and how uneven the contexts are (which changes that split)."""
         if not self.use_graphs or not ctx.is_decode:
             return None
         if any(list(e.want) != [0] for e in entries):
@@ -315,7 +328,7 @@ class Engine:
         bucket = 256
         while bucket < ctx.max_context:
             bucket *= 2
-        return (ctx.num_seqs, bucket)
+        return (ctx.num_seqs, bucket, ctx.uneven)
 
     def _run_graphed(self, key, ctx):
         ctx.max_context = key[1]          # launches are planned for the bucket, not the exact length

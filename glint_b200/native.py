@@ -27,7 +27,7 @@ class StepStruct(Structure):
     _fields_ = [("id", c_longlong),
                 ("num_tokens", c_int), ("num_seqs", c_int), ("max_seq_len", c_int), ("max_context", c_int),
                 ("leading_single", c_int), ("leading_single_context", c_int), ("num_logit_rows", c_int),
-                ("num_groups", c_int),
+                ("num_groups", c_int), ("uneven", c_int),
                 ("token_ids", c_void_p), ("positions", c_void_p), ("token_seq", c_void_p), ("seq_slot", c_void_p),
                 ("seq_start", c_void_p), ("cu_seqlens", c_void_p), ("logit_rows", c_void_p),
                 ("block_table", c_void_p * MAX_GROUPS), ("max_pages", c_int * MAX_GROUPS)]
@@ -75,7 +75,7 @@ def lib():
         core.glint_route_linear.restype = c_int
         core.glint_route_linear.argtypes = [c_void_p, c_int, c_int, c_int]
         core.glint_decode_splits.restype = c_int
-        core.glint_decode_splits.argtypes = [c_int, c_int, c_int, c_int]
+        core.glint_decode_splits.argtypes = [c_int, c_int, c_int, c_int, c_int]
         _bound = True
     return core
 
@@ -105,6 +105,7 @@ def fill_step(step, ctx, step_id):
     step.max_seq_len, step.max_context = ctx.max_seq_len, ctx.max_context
     step.leading_single, step.leading_single_context = ctx.leading_single, ctx.leading_single_context
     step.num_logit_rows = ctx.num_logit_rows
+    step.uneven = ctx.uneven
     tables = ctx.block_tables
     if len(tables) > MAX_GROUPS:
         raise KernelError(f"a step carries block tables of {len(tables)} cache groups; the runtime takes {MAX_GROUPS}")

@@ -188,10 +188,11 @@ def sm_count(device=None):
     return n
 
 
-def decode_splits(tokens, nkv, max_context, sms=None):
-    """How many blocks share the keys of one token in the split attention kernel (the runtime's choice)."""
+def decode_splits(tokens, nkv, max_context, sms=None, uneven=0):
+    """How many blocks share the keys of one token in the split attention kernel (the runtime's choice).
+    ``uneven``: the contexts add up to about (tokens x max_context) >> uneven."""
     from . import native
-    return native.lib().glint_decode_splits(tokens, nkv, max_context, sms or sm_count())
+    return native.lib().glint_decode_splits(tokens, nkv, max_context, uneven, sms or sm_count())
 
 
 def attention_decode(q, k_pool, v_pool, positions, token_seq, block_table, out, nh, nkv, hd, page_size, num_pages,

@@ -710,3 +710,8 @@ def test_runtime_routes_products_by_size():
     assert ops_tensor.decode_splits(1, 4, 8192, 148) == 16 and ops_tensor.decode_splits(8, 4, 2304, 148) == 8
     assert ops_tensor.decode_splits(64, 4, 2304, 148) == 1 and ops_tensor.decode_splits(8, 4, 200, 148) == 1
     assert ops_tensor.decode_splits(9, 4, 2304, 148) == 4          # 36 clusters of 8 would not fit the SMs at once
+    # contexts that add up to half of (requests x longest): the longest is shared among more blocks
+    assert ops_tensor.decode_splits(56, 4, 8192, 148) == 1 and ops_tensor.decode_splits(56, 4, 8192, 148, uneven=1) == 4
+    assert ops_tensor.decode_splits(56, 8, 8192, 148, uneven=1) == 2 and ops_tensor.decode_splits(12, 4, 8192, 148, uneven=1) == 8
+    assert ops_tensor.decode_splits(64, 4, 300, 148, uneven=1) == 2   # never fewer than 128 keys to a split
+    assert ops_tensor.decode_splits(8, 4, 2304, 148, uneven=2) == 8   # and never fewer splits than even contexts get
