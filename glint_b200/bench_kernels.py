@@ -10,6 +10,7 @@ import argparse
 import json
 import math
 
+import numpy as np
 import torch
 
 DEV = "cuda:0"
@@ -141,11 +142,11 @@ def prefill_step(tokens, layers, iters):
     return {"kernel": "prefill step", "tokens": tokens, "layers": layers, "ms": round(ms, 4)}
 
 
-def engine_step(shape, layers, batch, context, tokens, timeline=False):
+def engine_step(shape, layers, batch, context, tokens, timeline=False, spread=0.0):
     """One step of an engine of a named shape with ``layers`` layers: ``batch`` requests with ``context``
-    tokens cached bring one token each and, with ``tokens`` > 0, one more request brings a portion of that
-    many tokens.  The last step runs between cudaProfilerStart and cudaProfilerStop (for a profiler started
-    with ``--profile-from-start off``).  ``timeline``: a step of single tokens is replayed from its CUDA graph
+    tokens cached (with ``spread`` > 0: uniformly between (1 - spread) x context and context, seeded) bring one
+    token each and, with ``tokens`` > 0, one more request brings a portion of that many tokens.  The last step
+    runs between cudaProfilerStart and cudaProfilerStop (for a profiler started with ``--profile-from-start off``).  ``timeline``: a step of single tokens is replayed from its CUDA graph
     under the PyTorch profiler and every kernel's start, end and duration in microseconds are printed, which
     shows what runs under what (a launch list shows each kernel alone)."""
     from . import bench as B
@@ -156,7 +157,9 @@ def engine_step(shape, layers, batch, context, tokens, timeline=False):
     eng = llm.engine
     V = eng.vocab_size
     slots = [eng.open() for _ in range(batch)]
-    B.fill_cache(eng, slots, [B.random_prompt(context, V, 100 + i) for i in range(batch)])
+    rng = np.random.default_rng(11)
+    contexts = [max(1, int(round(context * (1.0 - spread * rng.random())))) for _ in range(batch)]
+    B.fill_cache(eng, slots, [B.random_prompt(c, V, 100 + i) for i, c in enumerate(contexts)])
     out = torch.ones(max(batch, 1), dtype=torch.int32, device=DEV)
 
     def step():
@@ -178,7 +181,7 @@ def engine_step(shape, layers, batch, context, tokens, timeline=False):
     b.record()
     torch.cuda.synchronize()
     res = [{"kernel": "engine step", "shape": shape, "layers": layers, "batch": batch, "context": context,
-            "portion": tokens, "ms": round(a.elapsed_time(b), 4), "graphs": dict(eng.graph_counts)}]
+            "spread": spread, "portion": tokens, "ms": round(a.elapsed_time(b), 4), "graphs": dict(eng.graph_counts)}]
     if timeline:
         from torch.profiler import ProfilerActivity, profile
         with profile(activities=[ProfilerActivity.CUDA]) as prof:
@@ -228,6 +231,8 @@ def main():
                                      "attention-prefill", "rows", "prefill-step", "sampling", "step"])
     ap.add_argument("--shape", default="2b", help="step: 2b, 9b, 27b or a model folder")
     ap.add_argument("--portion", type=int, default=0, help="step: tokens of a prompt portion beside the single tokens")
+    ap.add_argument("--spread", type=float, default=0.0,
+                    help="step: contexts uniform between (1 - spread) x context and context instead of all equal")
     ap.add_argument("--timeline", action="store_true", help="step: kernel starts and ends inside a graph replay")
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
@@ -267,7 +272,7 @@ def main():
     elif a.what == "sampling":
         out.extend(bench_sampling(a.batch, a.n if a.n != 4096 else 256000, a.iters))
     elif a.what == "step":
-        out.extend(engine_step(a.shape, a.layers, a.batch, a.context, a.portion, a.timeline))
+        out.extend(engine_step(a.shape, a.layers, a.batch, a.context, a.portion, a.timeline, a.spread))
     elif a.what == "prefill-step":
         out.append(prefill_step(a.tokens, a.layers, a.iters))
     for row in out:

@@ -70,6 +70,93 @@ struct DecodeShared {
   int abort_flag;
 };
 
+// One page of keys and values in a stage of the ring, for one warp: scores^T = K q^T per 16 keys, soft cap,
+// running maximum and sum, out^T += V^T p^T.  `page_key0` is the index of the page's first key in its
+// request; keys outside [first, pos] are masked.  m, l: this thread's heads 2 tq and 2 tq + 1 (l over this
+// thread's keys only).
+template <int HD>
+__device__ __forceinline__ void decode_page(float (&o)[HD / 16][4], float (&m)[2], float (&l)[2],
+                                            const uint32_t (&qb)[HD / 16][2], uint32_t kbase, uint32_t vbase,
+                                            uint8_t* vstage, int page_key0, int pos, int first, int page_size,
+                                            int hd16, int nsub, uint32_t sub_bytes, float cap, float score_scale,
+                                            int lane) {
+  const int g = lane >> 2;
+  for (int tile = 0; tile * 16 < page_size; ++tile) {
+    const int key0 = page_key0 + tile * 16;
+    if (key0 > pos || key0 + 15 < first) continue;            // the whole tile is masked
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      if (ks < hd16) {
+        uint32_t a[4];
+        const int row = tile * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        ldsm_x4(a, kbase + (ks >> 2) * sub_bytes + swz(row, (ks & 3) * 2 + (lane >> 4)));
+        mma16816(sc, a, qb[ks][0], qb[ks][1]);
+      }
+    }
+    // sc[0], sc[1]: key g, heads 2tq, 2tq+1;  sc[2], sc[3]: key g + 8, same heads
+    const bool va = key0 + g >= first && key0 + g <= pos;
+    const bool vb = key0 + g + 8 >= first && key0 + g + 8 <= pos;
+    float corr[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float xa = sc[h] * score_scale, xb = sc[2 + h] * score_scale;
+      if (cap > 0.f) {
+        xa = cap * tanhf(xa);
+        xb = cap * tanhf(xb);
+      }
+      xa = va ? xa : -INFINITY;
+      xb = vb ? xb : -INFINITY;
+      float mx = fmaxf(xa, xb);
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      const float m_new = fmaxf(m[h], mx);
+      const float base = m_new == -INFINITY ? 0.f : m_new;
+      corr[h] = __expf(m[h] - base);
+      const float pa = __expf(xa - base), pb = __expf(xb - base);
+      l[h] = l[h] * corr[h] + pa + pb;       // this thread's keys only; lanes are added at the end
+      m[h] = m_new;
+      sc[h] = pa;
+      sc[2 + h] = pb;
+    }
+    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
+#pragma unroll
+      for (int i = 0; i < HD / 16; ++i) {
+        o[i][0] *= corr[0];
+        o[i][1] *= corr[1];
+        o[i][2] *= corr[0];
+        o[i][3] *= corr[1];
+      }
+    }
+    // value rows of masked keys may hold anything (a page's unwritten tail): zero them, since
+    // 0 * NaN would poison the product.  Only the first and last tile of a range get here.
+    if (key0 < first || key0 + 15 > pos) {
+      for (int r = 0; r < 16; ++r) {
+        const int key = key0 + r;
+        if (key >= first && key <= pos) continue;
+        for (int c = lane; c < nsub * 8; c += 32)
+          *reinterpret_cast<uint4*>(vstage + (c >> 3) * sub_bytes +
+                                    (tile * 16 + r) * SUB_BYTES_PER_ROW + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+      }
+      __syncwarp();
+    }
+    // p^T as the B operand: keys (2tq, 2tq+1) and (+8) of head g, by an 8x8 transpose in the warp
+    const uint32_t b0 = movmatrix_trans(pack2(sc[0], sc[1]));
+    const uint32_t b1 = movmatrix_trans(pack2(sc[2], sc[3]));
+#pragma unroll
+    for (int blk = 0; blk < HD / 16; ++blk) {
+      if (blk < hd16) {
+        uint32_t a[4];
+        const int i = lane >> 3;
+        const int key = tile * 16 + (lane & 7) + (i >> 1) * 8;
+        ldsm_x4_trans(a, vbase + (blk >> 2) * sub_bytes + swz(key, (blk & 3) * 2 + (i & 1)));
+        mma16816(o[blk], a, b0, b1);
+      }
+    }
+  }
+}
+
 // HD: register capacity (head_dim <= HD; head_dim and page_size are multiples of 16).
 template <int HD>
 __global__ void __launch_bounds__(DEC_BLOCK, 2)
@@ -188,80 +275,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       const bool ok = tc::mbar_wait(&sh->full[s], (it / stages) & 1, abort_flag);
       const uint32_t kbase = ring_addr + (uint32_t)s * 2 * page_bytes;
       const uint32_t vbase = kbase + page_bytes;
-      for (int tile = 0; tile * 16 < page_size && ok; ++tile) {
-        const int key0 = (my_lo + pi) * page_size + tile * 16;
-        if (key0 > pos || key0 + 15 < first) continue;            // the whole tile is masked
-        float sc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          if (ks < hd16) {
-            uint32_t a[4];
-            const int row = tile * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-            ldsm_x4(a, kbase + (ks >> 2) * sub_bytes + swz(row, (ks & 3) * 2 + (lane >> 4)));
-            mma16816(sc, a, qb[ks][0], qb[ks][1]);
-          }
-        }
-        // sc[0], sc[1]: key g, heads 2tq, 2tq+1;  sc[2], sc[3]: key g + 8, same heads
-        const bool va = key0 + g >= first && key0 + g <= pos;
-        const bool vb = key0 + g + 8 >= first && key0 + g + 8 <= pos;
-        float corr[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          float xa = sc[h] * score_scale, xb = sc[2 + h] * score_scale;
-          if (cap > 0.f) {
-            xa = cap * tanhf(xa);
-            xb = cap * tanhf(xb);
-          }
-          xa = va ? xa : -INFINITY;
-          xb = vb ? xb : -INFINITY;
-          float mx = fmaxf(xa, xb);
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-          const float m_new = fmaxf(m[h], mx);
-          const float base = m_new == -INFINITY ? 0.f : m_new;
-          corr[h] = __expf(m[h] - base);
-          const float pa = __expf(xa - base), pb = __expf(xb - base);
-          l[h] = l[h] * corr[h] + pa + pb;       // this thread's keys only; lanes are added at the end
-          m[h] = m_new;
-          sc[h] = pa;
-          sc[2 + h] = pb;
-        }
-        if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
-#pragma unroll
-          for (int i = 0; i < HD / 16; ++i) {
-            o[i][0] *= corr[0];
-            o[i][1] *= corr[1];
-            o[i][2] *= corr[0];
-            o[i][3] *= corr[1];
-          }
-        }
-        // value rows of masked keys may hold anything (a page's unwritten tail): zero them, since
-        // 0 * NaN would poison the product.  Only the first and last tile of a range get here.
-        if (key0 < first || key0 + 15 > pos) {
-          for (int r = 0; r < 16; ++r) {
-            const int key = key0 + r;
-            if (key >= first && key <= pos) continue;
-            for (int c = lane; c < nsub * 8; c += 32)
-              *reinterpret_cast<uint4*>(ring + (size_t)s * 2 * page_bytes + page_bytes + (c >> 3) * sub_bytes +
-                                        (tile * 16 + r) * SUB_BYTES_PER_ROW + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
-          }
-          __syncwarp();
-        }
-        // p^T as the B operand: keys (2tq, 2tq+1) and (+8) of head g, by an 8x8 transpose in the warp
-        const uint32_t b0 = movmatrix_trans(pack2(sc[0], sc[1]));
-        const uint32_t b1 = movmatrix_trans(pack2(sc[2], sc[3]));
-#pragma unroll
-        for (int blk = 0; blk < HD / 16; ++blk) {
-          if (blk < hd16) {
-            uint32_t a[4];
-            const int i = lane >> 3;
-            const int key = tile * 16 + (lane & 7) + (i >> 1) * 8;
-            ldsm_x4_trans(a, vbase + (blk >> 2) * sub_bytes + swz(key, (blk & 3) * 2 + (i & 1)));
-            mma16816(o[blk], a, b0, b1);
-          }
-        }
-      }
+      if (ok)
+        decode_page<HD>(o, m, l, qb, kbase, vbase, ring + (size_t)s * 2 * page_bytes + page_bytes,
+                        (my_lo + pi) * page_size, pos, first, page_size, hd16, nsub, sub_bytes, cap, score_scale, lane);
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&sh->empty[s]);     // this warp is done with stage s
     }
@@ -363,6 +379,374 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     cluster_sync();                                  // nobody leaves while its shared memory is being read
   }
   if (threadIdx.x == 0 && sh->abort_flag) atomicExch(status, 4);
+}
+
+// ---- the same attention with the keys of the whole launch shared evenly among the blocks -----------------
+//
+// The pages of all (token, kv head) pairs of a launch, in order, are one sequence; block b takes units
+// [b W, (b + 1) W) of it, whatever pairs they belong to, and streams them through its ring without a break.
+// A unit is a page, and every pair is preceded by `pair_cost` empty units that stand for what a pair costs a
+// block beside its pages (the query, the merge of the warps, the result): without them a block whose share
+// is forty requests of one page each would take forty times that while the others wait.
+// A pair whose pages lie inside one block is finished there; a pair that several blocks share gets a
+// partial result from each in a workspace, and the block that leaves its part last adds them up, in block
+// order.  So a launch lasts as long as its bytes take and not as long as its longest context (56 requests of
+// 200 to 4,600 keys: a block per pair streams the longest alone at about 32 GB/s while the SMs of the short
+// ones stand idle), every SM streams from the first page to the last, and without clusters the launch may
+// start under its predecessor's tail.  One block (decode_stream_plan_kernel) finds W and where each
+// block begins, once per step for all layers with the same window.
+struct StreamPlan {
+  const int4* starts;     // [blocks][2]: (token, kv head, unit within the pair, units this block takes),
+                          //              (W, the token's position, its row of the block table, pair_cost)
+  float* partials;        // [blocks][2][G][head_dim + 4]: a block's first pair (begun by another block) and its
+                          // last (finished by another block)
+  int* arrive;            // [tokens][kv heads]: blocks that have left their part; back at 0 after the launch
+};
+
+struct StreamShared {
+  uint64_t full[DEC_MAX_STAGES];
+  uint64_t empty[DEC_MAX_STAGES];
+  int abort_flag;
+  int last_one;
+};
+
+// One pair's range within a block: computed alike by the producer and the consumers.
+struct StreamSegment {
+  int pos, first, page_lo, pages;   // of the pair's token: last key, first key, first page, pages
+};
+__device__ __forceinline__ StreamSegment stream_segment(int pos, int window, int page_size) {
+  StreamSegment s;
+  s.pos = pos;
+  s.first = (window > 0 && s.pos - window + 1 > 0) ? s.pos - window + 1 : 0;
+  s.page_lo = s.first / page_size;
+  s.pages = s.pos / page_size - s.page_lo + 1;
+  return s;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(DEC_BLOCK, 2)
+attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                               const __nv_bfloat16* __restrict__ q, const int* __restrict__ positions,
+                               const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_pages,
+                               __nv_bfloat16* __restrict__ out, int T, int nh, int nkv, int hd, int page_size,
+                               int num_pages, float multiplier, float cap, int window, int stages, int whole_page,
+                               const StreamPlan plan, int* __restrict__ status) {
+  extern __shared__ uint8_t dec_raw[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dec_raw) + 1023) & ~(uintptr_t)1023);
+  const int G = nh / nkv;                                  // at most DEC_HEADS (the host checks)
+  const int hd16 = hd >> 4;
+  const int nsub = (hd + 63) >> 6;
+  const uint32_t sub_bytes = (uint32_t)page_size * SUB_BYTES_PER_ROW;
+  const uint32_t page_bytes = nsub * sub_bytes;
+  const int stride_f = hd + 2;
+  const int pstride = hd + 4;                              // rows of the workspace: 16-byte aligned
+  float* merge = reinterpret_cast<float*>(ring + (size_t)stages * 2 * page_bytes);   // [warps][G][hd + 2]
+  StreamShared* sh = reinterpret_cast<StreamShared*>(merge + (size_t)DEC_WARPS * G * stride_f);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      tc::mbar_init(&sh->full[s], 1);
+      tc::mbar_init(&sh->empty[s], 1);
+    }
+    sh->abort_flag = 0;
+    sh->last_one = 0;
+    tc::fence_barrier_init();
+    tc::tma_prefetch_desc(&map_k);
+    tc::tma_prefetch_desc(&map_v);
+  }
+  __syncthreads();
+  pdl_wait_release();                           // the keys of this step, q and the plan come from earlier kernels
+  const int4 start = plan.starts[2 * blockIdx.x], start2 = plan.starts[2 * blockIdx.x + 1];
+  if (start.w <= 0) return;                     // fewer pages than blocks
+  const int W = start2.x;
+  volatile int* abort_flag = &sh->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // The first pair's position and table row come with the plan: two loads fewer between the wait and the
+  // first page on its way.
+  const int pair_cost = start2.w;
+  int t = start.x, kvh = start.y, voff = start.z, remaining = start.w, it0 = 0;   // voff, remaining: in units
+  int pos_t = start2.y, row_t = start2.z;
+  if (warp == DEC_WARPS) {
+    // ---- producer warp: pair after pair, 32 page lookups at a time, one lane starts the tile loads --------
+    while (remaining > 0 && t < T) {
+      const StreamSegment sg = stream_segment(pos_t, window, page_size);
+      const int units = min(remaining, pair_cost + sg.pages - voff);      // of this pair in this block
+      const int off = max(voff, pair_cost) - pair_cost;                   // first page
+      const int n = max(0, voff + units - pair_cost - off);               // pages
+      const int* table = block_table + (size_t)row_t * max_pages + sg.page_lo + off;
+      for (int base = 0; base < n; base += 32) {
+        int page = 0;
+        if (base + lane < n) {
+          page = table[base + lane];
+          if (page < 0 || page >= num_pages) {     // never read outside the pool; report it
+            atomicExch(status, 3);
+            page = 0;
+          }
+        }
+        for (int j = 0; j < 32 && base + j < n; ++j) {
+          const int it = it0 + base + j;
+          const int pg = __shfl_sync(0xffffffffu, page, j);
+          if (tc::elect_one()) {
+            const int s = it % stages;
+            bool ok = true;
+            if (it >= stages) ok = tc::mbar_wait(&sh->empty[s], ((it / stages) - 1) & 1, abort_flag);
+            if (ok) {
+              uint8_t* kdst = ring + (size_t)s * 2 * page_bytes;
+              const int row = (pg * nkv + kvh) * page_size;
+              tc::mbar_expect_tx(&sh->full[s], 2 * page_bytes);
+              if (whole_page) {
+                tc::tma_load_3d(kdst, &map_k, &sh->full[s], 0, row, 0);
+                tc::tma_load_3d(kdst + page_bytes, &map_v, &sh->full[s], 0, row, 0);
+              } else {
+                for (int sub = 0; sub < nsub; ++sub) {
+                  tc::tma_load_2d(kdst + sub * sub_bytes, &map_k, &sh->full[s], sub * 64, row);
+                  tc::tma_load_2d(kdst + page_bytes + sub * sub_bytes, &map_v, &sh->full[s], sub * 64, row);
+                }
+              }
+            }
+          }
+        }
+      }
+      remaining -= units;
+      it0 += n;
+      voff = 0;
+      if (++kvh == nkv) {
+        kvh = 0;
+        if (++t < T && remaining > 0) {
+          pos_t = positions[t];
+          row_t = token_seq[t];
+        }
+      }
+    }
+    return;
+  }
+
+  // ---- consumer warps ------------------------------------------------------------------------------------
+  const int g = lane >> 2, tq = lane & 3;
+  const float score_scale = cap > 0.f ? multiplier / cap : multiplier;
+  const uint32_t ring_addr = tc::smem_u32(ring);
+  long long cursor = (long long)blockIdx.x * W;                 // where this block stands in the launch's sequence
+  while (remaining > 0 && t < T) {
+    const StreamSegment sg = stream_segment(pos_t, window, page_size);
+    const int units = min(remaining, pair_cost + sg.pages - voff);
+    const int off = max(voff, pair_cost) - pair_cost;
+    const int n = max(0, voff + units - pair_cost - off);
+    const long long pair_begin = cursor - voff + pair_cost;     // the pair's first page in the launch's sequence
+    cursor += units;
+    remaining -= units;
+    voff = 0;
+    if (n == 0) {                                               // only the empty units before the pair's pages
+      if (++kvh == nkv) {
+        kvh = 0;
+        if (++t < T && remaining > 0) pos_t = positions[t];
+      }
+      continue;
+    }
+    const bool begins = off == 0, ends = off + n == sg.pages;   // does this block hold the pair's first / last page
+    // q^T as the B operand: this thread holds dims (16 ks + 2 tq, +1) and (+8, +9) of head g
+    uint32_t qb[HD / 16][2];
+    {
+      const __nv_bfloat16* qrow = q + ((size_t)t * nh + kvh * G + (g < G ? g : 0)) * hd;
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        const bool in = ks < hd16 && g < G;
+        qb[ks][0] = in ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + tq * 2) : 0u;
+        qb[ks][1] = in ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + tq * 2) : 0u;
+      }
+    }
+    float o[HD / 16][4];
+#pragma unroll
+    for (int i = 0; i < HD / 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    // Page `it` of the block belongs to warp it % 4 and stage it % stages (a multiple of 4: a stage is always
+    // read by the same warp, which therefore sees every phase of the stage's barrier).
+    for (int it = it0 + ((warp - it0) % DEC_WARPS + DEC_WARPS) % DEC_WARPS; it < it0 + n; it += DEC_WARPS) {
+      const int s = it % stages;
+      const bool ok = tc::mbar_wait(&sh->full[s], (it / stages) & 1, abort_flag);
+      const uint32_t kbase = ring_addr + (uint32_t)s * 2 * page_bytes;
+      if (ok)
+        decode_page<HD>(o, m, l, qb, kbase, kbase + page_bytes, ring + (size_t)s * 2 * page_bytes + page_bytes,
+                        (sg.page_lo + off + it - it0) * page_size, sg.pos, sg.first, page_size, hd16, nsub, sub_bytes,
+                        cap, score_scale, lane);
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&sh->empty[s]);
+    }
+    // ---- this warp's totals; the four warps are merged in shared memory, in warp order ---------------------
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 4);
+      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 8);
+      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 16);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int head = 2 * tq + h;
+      if (head < G) {
+        float* dst = merge + ((size_t)warp * G + head) * stride_f;
+#pragma unroll
+        for (int blk = 0; blk < HD / 16; ++blk) {
+          if (blk < hd16) {
+            dst[blk * 16 + g] = o[blk][h];
+            dst[blk * 16 + g + 8] = o[blk][2 + h];
+          }
+        }
+        if (g == 0) {
+          dst[hd] = m[h];
+          dst[hd + 1] = l[h];
+        }
+      }
+    }
+    consumer_sync();
+    const bool whole = begins && ends;
+    float* partial = plan.partials + (((size_t)blockIdx.x * 2 + (begins ? 1 : 0)) * G) * pstride;
+    for (int j = 0; j < G; ++j) {
+      float M = -INFINITY;
+#pragma unroll
+      for (int wv = 0; wv < DEC_WARPS; ++wv) M = fmaxf(M, merge[((size_t)wv * G + j) * stride_f + hd]);
+      float L = 0.f;
+      float w[DEC_WARPS];
+#pragma unroll
+      for (int wv = 0; wv < DEC_WARPS; ++wv) {
+        const float mg = merge[((size_t)wv * G + j) * stride_f + hd];
+        w[wv] = mg == -INFINITY ? 0.f : __expf(mg - M);
+        L += merge[((size_t)wv * G + j) * stride_f + hd + 1] * w[wv];
+      }
+      for (int d = threadIdx.x; d < hd; d += DEC_THREADS) {
+        float ov = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < DEC_WARPS; ++wv) ov += merge[((size_t)wv * G + j) * stride_f + d] * w[wv];
+        if (whole) out[((size_t)t * nh + kvh * G + j) * hd + d] = __float2bfloat16_rn(L > 0.f ? ov / L : 0.f);
+        else partial[(size_t)j * pstride + d] = ov;
+      }
+      if (!whole && threadIdx.x == 0) {
+        partial[(size_t)j * pstride + hd] = M;
+        partial[(size_t)j * pstride + hd + 1] = L;
+      }
+    }
+    if (!whole) {
+      // ---- the pair is shared: the block that leaves its part last adds the parts up, in block order --------
+      const int b_first = (int)(pair_begin / W), b_last = (int)((pair_begin + sg.pages - 1) / W);
+      consumer_sync();                               // every thread's share of the partial result is written
+      if (threadIdx.x == 0) {
+        __threadfence();                             // and visible to the other blocks before this block is counted
+        int* counter = plan.arrive + (size_t)t * nkv + kvh;
+        const int before = atomicAdd(counter, 1);
+        const int last = before == b_last - b_first;
+        if (last) *counter = 0;                      // for the next launch
+        __threadfence();
+        sh->last_one = last;
+      }
+      consumer_sync();
+      if (sh->last_one) {
+        // Four output elements per thread, and of up to eight parts at a time the maxima, the sums and the
+        // elements all in flight together: one trip to L2 for a pair that two to eight blocks share (a chain
+        // of dependent loads per element and part took a block that merges 17 parts 20 us).
+        const int parts = b_last - b_first + 1;
+        const int quads = hd >> 2;
+        for (int e = threadIdx.x; e < G * quads; e += DEC_THREADS) {
+          const int j = e / quads, d = (e - j * quads) * 4;
+          float M = -INFINITY, L = 0.f;
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int i0 = 0; i0 < parts; i0 += 8) {
+            float2 ml[8];
+            float4 v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const int bk = b_first + i0 + k;
+              ml[k] = make_float2(-INFINITY, 0.f);
+              v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (i0 + k < parts) {
+                const float* row = plan.partials + (((size_t)bk * 2 + (bk == b_first ? 1 : 0)) * G + j) * pstride;
+                ml[k] = __ldcg(reinterpret_cast<const float2*>(row + hd));
+                v[k] = __ldcg(reinterpret_cast<const float4*>(row + d));
+              }
+            }
+            float top = M;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) top = fmaxf(top, ml[k].x);
+            const float keep = M == -INFINITY ? 0.f : __expf(M - top);
+            L *= keep;
+            acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const float wk = ml[k].x == -INFINITY ? 0.f : __expf(ml[k].x - top);
+              L += ml[k].y * wk;
+              acc.x += v[k].x * wk; acc.y += v[k].y * wk; acc.z += v[k].z * wk; acc.w += v[k].w * wk;
+            }
+            M = top;
+          }
+          const float inv = L > 0.f ? 1.f / L : 0.f;
+          uint2 packed;
+          packed.x = pack2(acc.x * inv, acc.y * inv);
+          packed.y = pack2(acc.z * inv, acc.w * inv);
+          *reinterpret_cast<uint2*>(out + ((size_t)t * nh + kvh * G + j) * hd + d) = packed;
+        }
+      }
+    }
+    consumer_sync();                                 // the merge area and last_one are used again by the next pair
+    it0 += n;
+    if (++kvh == nkv) {
+      kvh = 0;
+      if (++t < T && remaining > 0) pos_t = positions[t];
+    }
+  }
+  if (threadIdx.x == 0 && sh->abort_flag) atomicExch(status, 4);
+}
+
+// One block plans a launch: W = units per block (at least `min_units`), and for every block the pair and
+// the unit where it begins (see StreamPlan).
+constexpr int PLAN_THREADS = 256;
+constexpr int PLAN_ROWS = 4;          // tokens per thread: launches of up to 1024 tokens
+
+__global__ void __launch_bounds__(PLAN_THREADS)
+decode_stream_plan_kernel(const int* __restrict__ positions, const int* __restrict__ token_seq, int T, int window,
+                          int page_size, int nkv, int blocks, int min_units, int pair_cost, int4* __restrict__ starts,
+                          int* __restrict__ header) {
+  __shared__ int warp_sum[PLAN_THREADS / 32];
+  pdl_wait_release();
+  const int r0 = threadIdx.x * PLAN_ROWS;
+  int units[PLAN_ROWS], pos[PLAN_ROWS], row[PLAN_ROWS], mine = 0;     // units of one pair of the token
+#pragma unroll
+  for (int i = 0; i < PLAN_ROWS; ++i) {
+    pos[i] = r0 + i < T ? positions[r0 + i] : 0;
+    row[i] = r0 + i < T ? token_seq[r0 + i] : 0;
+    units[i] = r0 + i < T ? pair_cost + stream_segment(pos[i], window, page_size).pages : 0;
+    mine += units[i] * nkv;
+  }
+  // inclusive scan of the threads' page counts
+  int incl = mine;
+  for (int o = 1; o < 32; o <<= 1) {
+    const int up = __shfl_up_sync(0xffffffffu, incl, o);
+    if ((int)(threadIdx.x & 31) >= o) incl += up;
+  }
+  if ((threadIdx.x & 31) == 31) warp_sum[threadIdx.x >> 5] = incl;
+  __syncthreads();
+  int before = incl - mine, total = 0;
+  for (int w = 0; w < PLAN_THREADS / 32; ++w) {
+    if (w < (int)(threadIdx.x >> 5)) before += warp_sum[w];
+    total += warp_sum[w];
+  }
+  const int W = max(min_units, (total + blocks - 1) / blocks);
+  // the blocks that begin inside this thread's tokens
+  int p = before;
+#pragma unroll
+  for (int i = 0; i < PLAN_ROWS; ++i) {
+    const int span = units[i] * nkv;
+    if (span > 0) {
+      for (int b = (p + W - 1) / W; b < blocks && (long long)b * W < p + span; ++b) {
+        const int inside = b * W - p;
+        starts[2 * b] = make_int4(r0 + i, inside / units[i], inside % units[i], min(W, total - b * W));
+        starts[2 * b + 1] = make_int4(W, pos[i], row[i], pair_cost);
+      }
+      p += span;
+    }
+  }
+  for (int b = (total + W - 1) / W + threadIdx.x; b < blocks; b += PLAN_THREADS) starts[2 * b] = make_int4(0, 0, 0, 0);
+  if (threadIdx.x == 0) {
+    header[0] = W;
+    header[1] = total;
+  }
 }
 
 // ---- host side ---------------------------------------------------------------------------------
@@ -469,6 +853,85 @@ GLINT_API int glint_attention_decode(const void* q, const void* k_pool, const vo
                               map_k, map_v, qq, positions, token_seq, block_table, max_pages, oo, nh, nkv, hd,    \
                               page_size, num_pages, multiplier, cap, window, splits, stages, whole_page, status); \
     if (e != cudaSuccess) return (int)e;                                                                        \
+  }
+  if (hd <= 64) LAUNCH(64)
+  else if (hd <= 128) LAUNCH(128)
+  else LAUNCH(256)
+#undef LAUNCH
+  return (int)cudaGetLastError();
+}
+
+// ---- the stream variant ----------------------------------------------------------------------------------
+GLINT_API int glint_attention_decode_stream_supported(int nh, int nkv, int hd, int page_size) {
+  return (glint_attention_decode_supported(nh, nkv, hd, page_size) && nh / nkv <= DEC_HEADS) ? 1 : 0;
+}
+
+// Floats of workspace a launch of `blocks` blocks needs.
+GLINT_API long long glint_attention_decode_stream_workspace(int blocks, int nh, int nkv, int hd) {
+  return (long long)blocks * 2 * (nh / nkv) * (hd + 4);
+}
+
+// Plans a launch of T single tokens (at most 1024) over `blocks` blocks: starts [blocks][2] int4, header [2]
+// (units per block, units in all; for tests and measurements).  `pair_cost` < 0: what a pair costs a block
+// beside its pages, in pages of this size (about 5 us of a block's stream).
+// One plan serves every layer of a step with the same window, page size and number of kv heads.
+GLINT_API int glint_attention_decode_stream_plan(const int* positions, const int* token_seq, int T, int window,
+                                                 int page_size, int hd, int nkv, int blocks, int min_pages,
+                                                 int pair_cost, void* starts, int* header, cudaStream_t stream) {
+  if (T <= 0) return GLINT_OK;
+  if (T > PLAN_THREADS * PLAN_ROWS || page_size <= 0 || nkv <= 0 || blocks < 1 || hd <= 0)
+    return GLINT_ERR_UNSUPPORTED_SIZE;
+  if (pair_cost < 0) {
+    const long long page_bytes = 2ll * ((hd + 63) / 64) * page_size * SUB_BYTES_PER_ROW;   // keys and values
+    pair_cost = (int)((160 * 1024 + page_bytes / 2) / page_bytes);
+    if (pair_cost < 1) pair_cost = 1;
+  }
+  cudaError_t e = launch_kernel(decode_stream_plan_kernel, dim3(1), dim3(PLAN_THREADS), 0, stream, positions, token_seq, T,
+                                window, page_size, nkv, blocks, min_pages < 1 ? 1 : min_pages, pair_cost, (int4*)starts,
+                                header);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
+// `partials`: glint_attention_decode_stream_workspace floats; `arrive`: [T][nkv] counters that are zero before
+// the first launch (every launch leaves them zero).  The plan must have been made for the same positions,
+// window, page size, kv heads and number of blocks.
+GLINT_API int glint_attention_decode_stream(const void* q, const void* k_pool, const void* v_pool,
+                                            const int* positions, const int* token_seq, const int* block_table,
+                                            int max_pages, void* out, int T, int nh, int nkv, int hd, int page_size,
+                                            int num_pages, float multiplier, float cap, int window, int blocks,
+                                            const void* starts, float* partials, int* arrive, int* status,
+                                            cudaStream_t stream) {
+  if (T <= 0) return GLINT_OK;
+  if (!starts || !partials || !arrive || blocks < 1 || ((uintptr_t)partials & 15)) return GLINT_ERR_BAD_ARG;
+  if (!glint_attention_decode_stream_supported(nh, nkv, hd, page_size)) return GLINT_ERR_UNSUPPORTED_SIZE;
+  if (((uintptr_t)k_pool | (uintptr_t)v_pool) & 15 || ((uintptr_t)q & 3)) return GLINT_ERR_UNSUPPORTED_SIZE;
+  CUtensorMap map_k, map_v;
+  const long long rows = (long long)num_pages * nkv * page_size;
+  const int whole_page = (hd % 64 == 0 && page_size <= 256) ? 1 : 0;
+  int rc = pool_map(&map_k, k_pool, rows, hd, page_size, whole_page);
+  if (rc != GLINT_OK) return rc;
+  rc = pool_map(&map_v, v_pool, rows, hd, page_size, whole_page);
+  if (rc != GLINT_OK) return rc;
+  const int G = nh / nkv;
+  const long long page_bytes = (long long)((hd + 63) / 64) * page_size * SUB_BYTES_PER_ROW;
+  const long long fixed = (long long)DEC_WARPS * G * (hd + 2) * 4 + sizeof(StreamShared) + 1024 + 64;
+  int stages = (int)((110 * 1024 - fixed) / (2 * page_bytes)) / DEC_WARPS * DEC_WARPS;
+  if (stages > DEC_MAX_STAGES) stages = DEC_MAX_STAGES;
+  if (stages < DEC_WARPS) stages = DEC_WARPS;
+  const long long smem = stages * 2 * page_bytes + fixed;
+  if (smem > 227 * 1024) return GLINT_ERR_UNSUPPORTED_SIZE;
+  StreamPlan plan = {(const int4*)starts, partials, arrive};
+  const __nv_bfloat16* qq = (const __nv_bfloat16*)q;
+  __nv_bfloat16* oo = (__nv_bfloat16*)out;
+#define LAUNCH(HD)                                                                                                    \
+  {                                                                                                                   \
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_stream_kernel<HD>,                                          \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                     \
+    if (e != cudaSuccess) return (int)e;                                                                              \
+    e = launch_kernel(attention_decode_stream_kernel<HD>, dim3(blocks), dim3(DEC_BLOCK), (size_t)smem, stream, map_k,  \
+                      map_v, qq, positions, token_seq, block_table, max_pages, oo, T, nh, nkv, hd, page_size,          \
+                      num_pages, multiplier, cap, window, stages, whole_page, plan, status);                          \
+    if (e != cudaSuccess) return (int)e;                                                                              \
   }
   if (hd <= 64) LAUNCH(64)
   else if (hd <= 128) LAUNCH(128)

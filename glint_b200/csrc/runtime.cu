@@ -84,9 +84,10 @@ extern "C" int glint_decode_splits(int tokens, int nkv, int max_context, int une
   if (splits < 1) splits = 1;
   while (splits & (splits - 1)) splits &= splits - 1;
   // All clusters of the launch should be on the SMs at once: a cluster stays within one of the 8 GPCs, two
-  // blocks fit an SM, so 148 SMs hold 32 clusters of 8 but not the 36 of 9 requests with 4 kv heads (35 us
-  // with 8 splits against 29 us with 4).
-  while (splits > 1 && tokens * nkv > 8 * ((2 * sms / 8) / splits)) splits >>= 1;
+  // blocks fit an SM, and not every GPC has its full share of the SMs (counted here as two fewer), so 148
+  // SMs hold 32 clusters of 8 but not the 36 of 9 requests with 4 kv heads (35 us with 8 splits against 29 us
+  // with 4), and 64 clusters of 4 but not the 72 of 9 requests with 8 kv heads (58 us against 34 us for 64).
+  while (splits > 1 && tokens * nkv > 8 * ((2 * (sms / 8 - 2)) / splits)) splits >>= 1;
   if (uneven > 0) {
     // Contexts of different lengths: a block streams about 32 GB/s whatever else runs (its ring of pages
     // against the memory's latency), so the launch lasts as long as its longest block, and the blocks of
@@ -101,6 +102,25 @@ extern "C" int glint_decode_splits(int tokens, int nkv, int max_context, int une
     if (more > splits) splits = more;
   }
   return splits;
+}
+
+// Which kernel single tokens take.  Every (token, kv head) with a cluster of its own is the faster way while
+// the contexts are even and the clusters fit the SMs with the splits they want (8 requests x 4 kv heads: 22.7
+// against 26.7 us).  The kernel that shares all pages of the launch evenly wins where a block per pair would
+// wait for the longest context (56 requests of 200 to 4,600 keys, 4 kv heads: 114 against 138 us; 24 requests,
+// 8 kv heads: 89 against 112), where the clusters had to give up splits to fit (9 requests x 4 kv heads: 24.0
+// against 30.7 us; 9 x 8: 36 against 51), and where single blocks make more than one wave (64 x 8: 187 against 196).
+extern "C" int glint_decode_streams(int tokens, int nh, int nkv, int max_context, int uneven, int sms) {
+  if (nkv <= 0 || nh / nkv > 8 || tokens > 1024) return 0;
+  const int pairs = tokens * nkv;
+  if (pairs > 2 * sms) return 1;
+  if (uneven > 0) return pairs >= 32 ? 1 : 0;
+  const int limit = pairs <= 8 ? 16 : 8;
+  const int most = max_context / 128 < limit ? max_context / 128 : limit;
+  int want = 2 * sms / (pairs > 1 ? pairs : 1);
+  if (want > most) want = most;
+  while (want & (want - 1)) want &= want - 1;
+  return want > 1 && glint_decode_splits(tokens, nkv, max_context, 0, sms) < want ? 1 : 0;
 }
 
 extern "C" int glint_route_linear(const GlintRuntime* rt, int M, int N, int K) {
@@ -175,6 +195,50 @@ extern "C" int glint_op_qkv_rope(const GlintRuntime* rt, const GlintStep* step, 
   return glint_op_rope_store(rt, step, qkv_tmp, q_out, view, nh, nkv, hd, inv_freq, factor, rotary_dim, stream);
 }
 
+// Attention of the first `T` tokens of the step, single tokens all: the stream kernel with this step's plan
+// for (window, page size, kv heads), made here if no earlier layer of the step has, or the cluster kernel.
+static int decode_attention(const GlintRuntime* rt, const GlintStep* step, const void* q, const GlintView* view,
+                            void* out, int T, int nh, int nkv, int hd, float multiplier, float cap, int window,
+                            cudaStream_t stream) {
+  const GlintTensorEntries& t = rt->tensor;
+  const int g = view->group;
+  const int* table = step->block_table[g];
+  const int max_pages = step->max_pages[g];
+  const int page = view->page_size;
+  GlintAttnScratch* a = rt->attn;
+  if (a && t.attention_decode_stream && glint_decode_streams(T, nh, nkv, step->max_context, step->uneven, rt->sms) &&
+      (long long)a->blocks * 2 * (nh / nkv) * (hd + 4) <= a->partial_floats && (long long)T * nkv <= a->arrive_ints) {
+    int slot = -1;
+    for (int i = 0; i < GLINT_ATTN_PLANS; ++i)
+      if (a->plan_step[i] == step->id && a->plan_tokens[i] == T && a->plan_window[i] == window &&
+          a->plan_page[i] == page && a->plan_nkv[i] == nkv && a->plan_hd[i] == hd)
+        slot = i;
+    void* starts = nullptr;
+    if (slot < 0) {
+      slot = a->next;
+      a->next = (a->next + 1) % GLINT_ATTN_PLANS;
+      starts = (char*)a->starts + (size_t)slot * a->blocks * 32;
+      const int rc = counted(t.attention_decode_stream_plan(step->positions, step->token_seq, T, window, page, hd, nkv,
+                                                            a->blocks, 8, -1, starts, a->headers + 2 * slot, stream));
+      if (rc != GLINT_OK) return rc;
+      a->plan_step[slot] = step->id;
+      a->plan_tokens[slot] = T;
+      a->plan_window[slot] = window;
+      a->plan_page[slot] = page;
+      a->plan_nkv[slot] = nkv;
+      a->plan_hd[slot] = hd;
+    }
+    starts = (char*)a->starts + (size_t)slot * a->blocks * 32;
+    return counted(t.attention_decode_stream(q, view->k, view->v, step->positions, step->token_seq, table, max_pages, out,
+                                             T, nh, nkv, hd, page, view->num_pages, multiplier, cap, window, a->blocks,
+                                             starts, a->partials, a->arrive, rt->status, stream));
+  }
+  return counted(t.attention_decode(q, view->k, view->v, step->positions, step->token_seq, table, max_pages, out, T, nh,
+                                    nkv, hd, page, view->num_pages, multiplier, cap, window,
+                                    glint_decode_splits(T, nkv, step->max_context, step->uneven, rt->sms), rt->status,
+                                    stream));
+}
+
 extern "C" int glint_op_attention(const GlintRuntime* rt, const GlintStep* step, const void* q, const GlintView* view,
                                   void* out, int nh, int nkv, int hd, float multiplier, float cap, int window,
                                   cudaStream_t stream) {
@@ -198,9 +262,7 @@ extern "C" int glint_op_attention(const GlintRuntime* rt, const GlintStep* step,
       // such a row (8192 keys: 150 us, and the step waits for it); the split kernel shares them among a
       // cluster.  Many requests with short contexts stay: their walks hide behind the portions' tiles.
       // The portions keep their absolute token offsets.
-      int rc = counted(t.attention_decode(q, view->k, view->v, step->positions, step->token_seq, table, max_pages, out, lead,
-                                  nh, nkv, hd, page, view->num_pages, multiplier, cap, window,
-                                  glint_decode_splits(lead, nkv, step->max_context, step->uneven, rt->sms), rt->status, stream));
+      int rc = decode_attention(rt, step, q, view, out, lead, nh, nkv, hd, multiplier, cap, window, stream);
       if (rc != GLINT_OK) return rc;
       return counted(t.attention_tcgen05(q, view->k, view->v, step->cu_seqlens + lead, step->seq_start + lead,
                                  table + (size_t)lead * max_pages, max_pages, out, T, step->num_seqs - lead,
@@ -215,9 +277,7 @@ extern "C" int glint_op_attention(const GlintRuntime* rt, const GlintStep* step,
     return counted(t.attention_prefill(q, view->k, view->v, step->cu_seqlens, step->seq_start, table, max_pages, out,
                                step->num_seqs, step->max_seq_len, nh, nkv, hd, page, view->num_pages, multiplier, cap,
                                window, rt->status, stream));
-  return counted(t.attention_decode(q, view->k, view->v, step->positions, step->token_seq, table, max_pages, out, T, nh, nkv,
-                            hd, page, view->num_pages, multiplier, cap, window,
-                            glint_decode_splits(T, nkv, step->max_context, step->uneven, rt->sms), rt->status, stream));
+  return decode_attention(rt, step, q, view, out, T, nh, nkv, hd, multiplier, cap, window, stream);
 }
 
 // ---- programs ---------------------------------------------------------------------------------------------

@@ -46,10 +46,33 @@ struct GlintTensorEntries {
                           float, void*, void*, void*, int, int, int, int, int, int*, cudaStream_t);
   int (*attention_decode)(const void*, const void*, const void*, const int*, const int*, const int*, int, void*, int,
                           int, int, int, int, int, float, float, int, int, int*, cudaStream_t);
+  int (*attention_decode_stream_plan)(const int*, const int*, int, int, int, int, int, int, int, int, void*, int*,
+                                      cudaStream_t);
+  int (*attention_decode_stream)(const void*, const void*, const void*, const int*, const int*, const int*, int, void*,
+                                 int, int, int, int, int, int, float, float, int, int, const void*, float*, int*, int*,
+                                 cudaStream_t);
   int (*attention_prefill)(const void*, const void*, const void*, const int*, const int*, const int*, int, void*, int,
                            int, int, int, int, int, int, float, float, int, int*, cudaStream_t);
   int (*attention_tcgen05)(const void*, const void*, const void*, const int*, const int*, const int*, int, void*, int,
                            int, int, int, int, int, int, int, float, float, int, int*, cudaStream_t);
+};
+
+// Scratch of the single-token attention that shares the pages of a launch evenly among its blocks: the
+// plans of a step (one for every window, page size and number of kv heads that its layers have; made by
+// the first layer that asks and kept until the next step), the partial results and the arrival counters.
+#define GLINT_ATTN_PLANS 8
+struct GlintAttnScratch {
+  int blocks;                   // blocks of a launch (two per SM)
+  void* starts;                 // [GLINT_ATTN_PLANS][blocks][2] int4
+  int* headers;                 // [GLINT_ATTN_PLANS][2]
+  float* partials;              // [partial_floats]
+  long long partial_floats;
+  int* arrive;                  // [arrive_ints], zero between launches
+  int arrive_ints;
+  int next;                     // the plan slot to fill next
+  long long plan_step[GLINT_ATTN_PLANS];
+  int plan_tokens[GLINT_ATTN_PLANS], plan_window[GLINT_ATTN_PLANS], plan_page[GLINT_ATTN_PLANS], plan_nkv[GLINT_ATTN_PLANS];
+  int plan_hd[GLINT_ATTN_PLANS];
 };
 
 // What all operations of one model share.
@@ -60,6 +83,7 @@ struct GlintRuntime {
   int* status;                  // device status word
   float* workspace;             // split-K scratch of the tiled product
   int* counters;
+  GlintAttnScratch* attn;       // null: single tokens always take the cluster kernel
   GlintTensorEntries tensor;
 };
 
@@ -102,6 +126,9 @@ long long glint_native_launches();
 // Operations that a tensor-core runtime ran on CUDA cores because no tensor-core kernel takes their sizes.
 long long glint_native_fallbacks();
 int glint_decode_splits(int tokens, int nkv, int max_context, int uneven, int sms);
+// 1 when single tokens of these counts take the kernel that shares all pages of the launch evenly among
+// its blocks, 0 when every (token, kv head) gets a cluster of glint_decode_splits blocks.
+int glint_decode_streams(int tokens, int nh, int nkv, int max_context, int uneven, int sms);
 
 // ---- programs ------------------------------------------------------------------------------------------
 struct GlintProgram;

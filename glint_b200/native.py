@@ -35,12 +35,26 @@ class StepStruct(Structure):
 
 class TensorEntries(Structure):
     _fields_ = [(name, c_void_p) for name in ("gemm_tcgen05", "gemm_skinny", "gemm_tcgen05_rope", "gemm_skinny_rope",
-                                              "attention_decode", "attention_prefill", "attention_tcgen05")]
+                                              "attention_decode", "attention_decode_stream_plan",
+                                              "attention_decode_stream", "attention_prefill", "attention_tcgen05")]
+
+
+ATTN_PLANS = 8
+
+
+class AttnScratchStruct(Structure):
+    """``GlintAttnScratch`` of csrc/runtime.h."""
+    _fields_ = [("blocks", c_int), ("starts", c_void_p), ("headers", c_void_p), ("partials", c_void_p),
+                ("partial_floats", c_longlong), ("arrive", c_void_p), ("arrive_ints", c_int), ("next", c_int),
+                ("plan_step", c_longlong * ATTN_PLANS), ("plan_tokens", c_int * ATTN_PLANS),
+                ("plan_window", c_int * ATTN_PLANS), ("plan_page", c_int * ATTN_PLANS), ("plan_nkv", c_int * ATTN_PLANS),
+                ("plan_hd", c_int * ATTN_PLANS)]
 
 
 class RuntimeStruct(Structure):
     _fields_ = [("tensor_cores", c_int), ("dtype", c_int), ("sms", c_int), ("status", c_void_p),
-                ("workspace", c_void_p), ("counters", c_void_p), ("tensor", TensorEntries)]
+                ("workspace", c_void_p), ("counters", c_void_p), ("attn", POINTER(AttnScratchStruct)),
+                ("tensor", TensorEntries)]
 
 
 class ViewStruct(Structure):
@@ -76,6 +90,8 @@ def lib():
         core.glint_route_linear.argtypes = [c_void_p, c_int, c_int, c_int]
         core.glint_decode_splits.restype = c_int
         core.glint_decode_splits.argtypes = [c_int, c_int, c_int, c_int, c_int]
+        core.glint_decode_streams.restype = c_int
+        core.glint_decode_streams.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int]
         _bound = True
     return core
 
@@ -95,6 +111,21 @@ def make_runtime_struct(rt):
         s.workspace, s.counters = ws.data_ptr(), counters.data_ptr()
         for name, _ in TensorEntries._fields_:
             setattr(s.tensor, name, ctypes.cast(getattr(tl, "glint_" + name), c_void_p).value)
+        # scratch of the single-token attention that shares a launch's pages evenly: two blocks per SM, partial
+        # results of up to 8 query heads of 256 per kv head, counters for 1024 tokens x 64 kv heads
+        a = AttnScratchStruct()
+        a.blocks = 2 * s.sms
+        a.partial_floats = a.blocks * 2 * 8 * (256 + 4)
+        a.arrive_ints = 65536
+        tensors = (torch.empty(ATTN_PLANS * a.blocks * 8, dtype=torch.int32, device=rt.device),
+                   torch.zeros(ATTN_PLANS * 2, dtype=torch.int32, device=rt.device),
+                   torch.empty(a.partial_floats, dtype=torch.float32, device=rt.device),
+                   torch.zeros(a.arrive_ints, dtype=torch.int32, device=rt.device))
+        a.starts, a.headers, a.partials, a.arrive = (t.data_ptr() for t in tensors)
+        for i in range(ATTN_PLANS):
+            a.plan_step[i] = -1
+        rt.attn_scratch = (a, tensors)             # owned by the runtime: the structure below only points at them
+        s.attn = ctypes.pointer(a)
     return s
 
 

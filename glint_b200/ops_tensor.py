@@ -20,6 +20,9 @@ _SIGNATURES = {
     "glint_gemm_tcgen05_rope": [_P, _P, _I, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "glint_gemm_skinny_rope": [_P, _P, _I, _I, _P, _P, _P, _I, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "glint_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P],
+    "glint_attention_decode_stream_plan": [_P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
+    "glint_attention_decode_stream": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P,
+                                      _P, _P, _P],
     "glint_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
     "glint_attention_tcgen05": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
 }
@@ -195,6 +198,13 @@ def decode_splits(tokens, nkv, max_context, sms=None, uneven=0):
     return native.lib().glint_decode_splits(tokens, nkv, max_context, uneven, sms or sm_count())
 
 
+def decode_streams(tokens, nh, nkv, max_context, sms=None, uneven=0):
+    """True when single tokens of these counts take the kernel that shares all pages of the launch evenly among
+    its blocks (the runtime's choice), False when every (token, kv head) gets a cluster of ``decode_splits`` blocks."""
+    from . import native
+    return bool(native.lib().glint_decode_streams(tokens, nh, nkv, max_context, uneven, sms or sm_count()))
+
+
 def attention_decode(q, k_pool, v_pool, positions, token_seq, block_table, out, nh, nkv, hd, page_size, num_pages,
                      multiplier, cap, window, status, splits, tokens=None):
     """Every token attends alone (split over its keys): right for any batch, meant for single tokens.
@@ -207,6 +217,39 @@ def attention_decode(q, k_pool, v_pool, positions, token_seq, block_table, out, 
                                            ops.ptr(out), T, nh, nkv, hd, page_size, num_pages, multiplier,
                                            cap or 0.0, window or 0, splits, ops.ptr(status), ops.stream()),
               "attention_decode")
+
+
+def attention_decode_stream_plan(positions, token_seq, tokens, window, page_size, hd, nkv, blocks, min_pages=8,
+                                 pair_cost=-1):
+    """Plans a launch of ``attention_decode_stream``: (starts [blocks, 2, 4] int32, header [2] int32 = units per
+    block and units in all, blocks).  A unit is a page; every (token, kv head) pair counts ``pair_cost`` more
+    (default: what the runtime takes for pages of this size)."""
+    starts = torch.empty(blocks, 2, 4, dtype=torch.int32, device=positions.device)
+    header = torch.zeros(2, dtype=torch.int32, device=positions.device)
+    ops.check(lib().glint_attention_decode_stream_plan(ops.ptr(positions), ops.ptr(token_seq), tokens, window or 0,
+                                                       page_size, hd, nkv, blocks, min_pages, pair_cost,
+                                                       ops.ptr(starts), ops.ptr(header), ops.stream()),
+              "attention_decode_stream_plan")
+    return starts, header, blocks
+
+
+def attention_decode_stream(q, k_pool, v_pool, positions, token_seq, block_table, out, nh, nkv, hd, page_size,
+                            num_pages, multiplier, cap, window, status, plan, partials, arrive, tokens=None):
+    """``attention_decode`` with the pages of the whole launch shared evenly among the blocks (``plan`` from
+    ``attention_decode_stream_plan`` with the same positions, window, page size and kv heads): ``partials``
+    float32 [blocks * 2 * (nh / nkv) * (hd + 4)], ``arrive`` int32 [tokens * nkv], zero before the first launch."""
+    T = q.shape[0] if tokens is None else tokens
+    starts, header, blocks = plan
+    ops.require(q, torch.bfloat16, "q"); ops.require(k_pool, torch.bfloat16, "k_pool")
+    ops.require(v_pool, torch.bfloat16, "v_pool"); ops.require(out, torch.bfloat16, "out")
+    if partials.numel() < blocks * 2 * (nh // nkv) * (hd + 4) or arrive.numel() < T * nkv:
+        raise KernelError("attention_decode_stream: the workspace is too small for this launch")
+    ops.check(lib().glint_attention_decode_stream(ops.ptr(q), ops.ptr(k_pool), ops.ptr(v_pool), ops.ptr(positions),
+                                                  ops.ptr(token_seq), ops.ptr(block_table), block_table.shape[1],
+                                                  ops.ptr(out), T, nh, nkv, hd, page_size, num_pages, multiplier,
+                                                  cap or 0.0, window or 0, blocks, ops.ptr(starts),
+                                                  ops.ptr(partials), ops.ptr(arrive), ops.ptr(status), ops.stream()),
+              "attention_decode_stream")
 
 
 def attention_prefill(q, k_pool, v_pool, cu_seqlens, seq_start, block_table, out, n_seqs, max_q_len, nh, nkv, hd,

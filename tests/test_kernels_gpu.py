@@ -344,6 +344,22 @@ def _attention_reference(q, dense, seq_of_token, positions, nh, nkv, multiplier,
     return out
 
 
+def _stream_attention(qd, k_pool, v_pool, positions, seq_of_token, table, out, nh, nkv, hd, page, mult, cap, window,
+                      status, blocks, arrive=None, pair_cost=-1):
+    """The single-token kernel that shares all pages of the launch evenly among ``blocks`` blocks."""
+    from glint_b200 import ops_tensor
+    T = positions.shape[0]
+    plan = ops_tensor.attention_decode_stream_plan(positions, seq_of_token, T, window, page, hd, nkv, blocks, min_pages=1,
+                                                   pair_cost=pair_cost)
+    partials = torch.full((blocks * 2 * (nh // nkv) * (hd + 4),), float("nan"), dtype=torch.float32, device=DEV)
+    arrive = torch.zeros(T * nkv, dtype=torch.int32, device=DEV) if arrive is None else arrive
+    ops_tensor.attention_decode_stream(qd, k_pool, v_pool, positions, seq_of_token, table, out, nh, nkv, hd, page,
+                                       k_pool.shape[0], mult, cap, window, status, plan, partials, arrive)
+    assert int(arrive.abs().sum().item()) == 0, "the arrival counters are not back at zero"
+    pages_per_block, pages = plan[1].cpu().tolist()
+    return pages_per_block, pages
+
+
 ATT_CASES = [
     # nh, nkv, hd, page, before,            new,             window, cap
     (8, 4, 256, 16, [300, 0, 1023, 77], [1, 1, 1, 1], None, 50.0),
@@ -357,11 +373,13 @@ ATT_CASES = [
 ]
 
 
-@pytest.mark.parametrize("kernel", ["plain32", "plain16", "decode", "prefill", "tcgen05"])
+@pytest.mark.parametrize("kernel", ["plain32", "plain16", "decode", "stream", "prefill", "tcgen05"])
 @pytest.mark.parametrize("case", range(len(ATT_CASES)))
 def test_attention_kernels_against_float32(case, kernel):
     from glint_b200 import ops, ops_tensor
     nh, nkv, hd, page, before, new, window, cap = ATT_CASES[case]
+    if kernel == "stream" and nh // nkv > 8:
+        pytest.skip("more than 8 query heads per kv head: the cluster kernel takes it")
     if kernel == "prefill" and not ops_tensor.prefill_supported(nh, nkv, hd):
         pytest.skip("size outside the tiled kernel's range (the split kernel takes it)")
     if kernel == "tcgen05" and not ops_tensor.tcgen05_attention_supported(nh, nkv, hd, page):
@@ -392,6 +410,16 @@ def test_attention_kernels_against_float32(case, kernel):
                                         hd, page, k_pool.shape[0], mult, cap, window, status, splits)
             got = out.float().cpu().reshape(T, nh, hd)
             assert (got - want).abs().max().item() < 0.03, splits
+    elif kernel == "stream":
+        # one block for everything; blocks that end inside pairs; more blocks than pages (a page per block)
+        arrive = torch.zeros(T * nkv, dtype=torch.int32, device=DEV)
+        for blocks, pair_cost in ((1, -1), (5, 0), (5, 3), (37, 1), (37, -1), (2000, 0), (2000, 2)):
+            out.fill_(float("nan"))
+            per_block, units = _stream_attention(qd, k_pool, v_pool, i32(positions), i32(seq_of_token), table, out, nh,
+                                                 nkv, hd, page, mult, cap, window, status, blocks, arrive, pair_cost)
+            assert per_block == max(1, -(-units // blocks))
+            got = out.float().cpu().reshape(T, nh, hd)
+            assert (got - want).abs().max().item() < 0.03, blocks
     else:
         cu = [0]
         for n in new:
@@ -405,7 +433,7 @@ def test_attention_kernels_against_float32(case, kernel):
     assert (got - want).abs().max().item() < tol, (got - want).abs().max().item()
 
 
-@pytest.mark.parametrize("kernel", ["plain16", "decode", "prefill", "tcgen05"])
+@pytest.mark.parametrize("kernel", ["plain16", "decode", "stream", "prefill", "tcgen05"])
 def test_attention_finds_one_far_key_among_hundreds(kernel):
     """One key far back is scaled so that its score stands out: the output must be its value row."""
     from glint_b200 import ops, ops_tensor
@@ -431,6 +459,9 @@ def test_attention_finds_one_far_key_among_hundreds(kernel):
     elif kernel == "decode":
         ops_tensor.attention_decode(qd, k_pool, v_pool, i32([900]), i32([0]), table, out, nh, nkv, hd, page,
                                     k_pool.shape[0], 1 / 16.0, None, None, status, 7)
+    elif kernel == "stream":
+        _stream_attention(qd, k_pool, v_pool, i32([900]), i32([0]), table, out, nh, nkv, hd, page, 1 / 16.0, None, None,
+                          status, 23)
     else:
         fn = ops_tensor.attention_prefill if kernel == "prefill" else ops_tensor.attention_tcgen05
         fn(qd, k_pool, v_pool, i32([0, 1]), i32([900]), table, out, 1, 1, nh, nkv, hd, page, k_pool.shape[0], 1 / 16.0,
@@ -439,7 +470,7 @@ def test_attention_finds_one_far_key_among_hundreds(kernel):
     assert (got - want).abs().max().item() < 0.03
 
 
-@pytest.mark.parametrize("kernel", ["plain16", "decode", "prefill", "tcgen05"])
+@pytest.mark.parametrize("kernel", ["plain16", "decode", "stream", "prefill", "tcgen05"])
 @pytest.mark.parametrize("pos", [63, 64, 79, 80, 200])
 def test_attention_window_edge(kernel, pos):
     """A hot key just outside the window must not be seen; the same key just inside must win.
@@ -468,6 +499,9 @@ def test_attention_window_edge(kernel, pos):
         elif kernel == "decode":
             ops_tensor.attention_decode(qd, k_pool, v_pool, i32([pos]), i32([0]), table, out, nh, nkv, hd, page,
                                         k_pool.shape[0], 0.125, None, window, status, 2)
+        elif kernel == "stream":
+            _stream_attention(qd, k_pool, v_pool, i32([pos]), i32([0]), table, out, nh, nkv, hd, page, 0.125, None,
+                              window, status, 3)
         else:
             fn = ops_tensor.attention_prefill if kernel == "prefill" else ops_tensor.attention_tcgen05
             fn(qd, k_pool, v_pool, i32([0, 1]), i32([pos]), table, out, 1, 1, nh, nkv, hd, page, k_pool.shape[0],
@@ -715,3 +749,10 @@ def test_runtime_routes_products_by_size():
     assert ops_tensor.decode_splits(56, 8, 8192, 148, uneven=1) == 2 and ops_tensor.decode_splits(12, 4, 8192, 148, uneven=1) == 8
     assert ops_tensor.decode_splits(64, 4, 300, 148, uneven=1) == 2   # never fewer than 128 keys to a split
     assert ops_tensor.decode_splits(8, 4, 2304, 148, uneven=2) == 8   # and never fewer splits than even contexts get
+    assert ops_tensor.decode_splits(9, 8, 2304, 148) == 2          # 72 clusters of 4 do not fit either
+    # the kernel that shares all pages of a launch evenly: uneven contexts from 32 (token, kv head) pairs, even ones
+    # where the clusters gave up splits to fit or single blocks make more than a wave
+    streams = lambda t, nkv, uneven=0, nh=None: ops_tensor.decode_streams(t, nh or 2 * nkv, nkv, 4096, 148, uneven)
+    assert not streams(8, 4) and streams(9, 4) and not streams(16, 4) and not streams(64, 4) and streams(64, 8)
+    assert streams(56, 4, 1) and streams(8, 4, 1) and not streams(7, 4, 1) and streams(9, 8) and not streams(8, 8)
+    assert not streams(64, 4, 1, nh=64)                            # 16 query heads per kv head: the cluster kernel
