@@ -104,23 +104,20 @@ extern "C" int glint_decode_splits(int tokens, int nkv, int max_context, int une
   return splits;
 }
 
-// Which kernel single tokens take.  Every (token, kv head) with a cluster of its own is the faster way while
-// the contexts are even and the clusters fit the SMs with the splits they want (8 requests x 4 kv heads: 22.7
-// against 26.7 us).  The kernel that shares all pages of the launch evenly wins where a block per pair would
-// wait for the longest context (56 requests of 200 to 4,600 keys, 4 kv heads: 114 against 138 us; 24 requests,
-// 8 kv heads: 89 against 112), where the clusters had to give up splits to fit (9 requests x 4 kv heads: 24.0
-// against 30.7 us; 9 x 8: 36 against 51), and where single blocks make more than one wave (64 x 8: 187 against 196).
+// Which kernel single tokens take.  A cluster per (token, kv head) is the faster way while the contexts are
+// even and the clusters fill the SMs (8 requests x 4 kv heads x 8 splits, whole decode steps of the 2B shape:
+// 1.806 against 1.833 ms; 16 x 4 x 4: 2.304 against 2.347; one request: 1.512 against 1.547).  The kernel that
+// shares all pages of the launch evenly wins where the clusters' power of two leaves SMs idle (12 requests:
+// 2.175 against 2.235 ms; 24: 2.81 against 3.02; 48: 3.78 against 4.155), where single blocks make more than
+// one wave (64 requests x 8 kv heads, 9B shape: 12.19 against 12.39 ms), and where contexts are uneven, since a
+// block per pair waits for the longest (serving 64 requests of 128 to 4,600 tokens, 9B shape: decode steps
+// of 57 to 64 requests 11.8 against 13.6 ms, of 9 to 16 requests 6.0 against 7.1 ms).
 extern "C" int glint_decode_streams(int tokens, int nh, int nkv, int max_context, int uneven, int sms) {
   if (nkv <= 0 || nh / nkv > 8 || tokens > 1024) return 0;
   const int pairs = tokens * nkv;
   if (pairs > 2 * sms) return 1;
   if (uneven > 0) return pairs >= 32 ? 1 : 0;
-  const int limit = pairs <= 8 ? 16 : 8;
-  const int most = max_context / 128 < limit ? max_context / 128 : limit;
-  int want = 2 * sms / (pairs > 1 ? pairs : 1);
-  if (want > most) want = most;
-  while (want & (want - 1)) want &= want - 1;
-  return want > 1 && glint_decode_splits(tokens, nkv, max_context, 0, sms) < want ? 1 : 0;
+  return pairs >= 16 && pairs * glint_decode_splits(tokens, nkv, max_context, 0, sms) * 10 <= 7 * 2 * sms ? 1 : 0;
 }
 
 extern "C" int glint_route_linear(const GlintRuntime* rt, int M, int N, int K) {
@@ -206,7 +203,10 @@ static int decode_attention(const GlintRuntime* rt, const GlintStep* step, const
   const int max_pages = step->max_pages[g];
   const int page = view->page_size;
   GlintAttnScratch* a = rt->attn;
-  if (a && t.attention_decode_stream && glint_decode_streams(T, nh, nkv, step->max_context, step->uneven, rt->sms) &&
+  const bool wanted = a && (a->mode == 1 ? (nkv > 0 && nh / nkv <= 8 && T <= 1024)
+                                         : a->mode == 0 && glint_decode_streams(T, nh, nkv, step->max_context,
+                                                                                 step->uneven, rt->sms));
+  if (wanted && t.attention_decode_stream &&
       (long long)a->blocks * 2 * (nh / nkv) * (hd + 4) <= a->partial_floats && (long long)T * nkv <= a->arrive_ints) {
     int slot = -1;
     for (int i = 0; i < GLINT_ATTN_PLANS; ++i)

@@ -62,6 +62,8 @@ struct GlintTensorEntries {
 // the first layer that asks and kept until the next step), the partial results and the arrival counters.
 #define GLINT_ATTN_PLANS 8
 struct GlintAttnScratch {
+  int mode;                     // 0: the runtime chooses between the two single-token kernels; 1: this one wherever
+                                // it takes the sizes; 2: never (tests and measurements)
   int blocks;                   // blocks of a launch (two per SM)
   void* starts;                 // [GLINT_ATTN_PLANS][blocks][2] int4
   int* headers;                 // [GLINT_ATTN_PLANS][2]

@@ -53,6 +53,18 @@ class Runtime:
     def tensor_cores(self):
         return self.dtype == torch.bfloat16 and self.kernels == "auto"
 
+    def single_token_attention(self, which):
+        """Which of the two single-token attention kernels steps take from now on: "routed" (the runtime's
+        choice, the default), "stream" (the kernel that shares all pages of a launch evenly among its blocks,
+        wherever it takes the sizes) or "cluster" (a cluster of blocks per token and kv head, always).  For
+        tests and measurements; graphs captured before the call keep what they captured."""
+        modes = {"routed": 0, "stream": 1, "cluster": 2}
+        if which not in modes:
+            raise KernelError(f"single_token_attention: {which!r} is none of {sorted(modes)}")
+        scratch = getattr(self, "attn_scratch", None)
+        if scratch is not None:
+            scratch[0].mode = modes[which]
+
     def empty(self, shape, dtype=None):
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
 

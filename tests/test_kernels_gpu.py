@@ -751,8 +751,9 @@ def test_runtime_routes_products_by_size():
     assert ops_tensor.decode_splits(8, 4, 2304, 148, uneven=2) == 8   # and never fewer splits than even contexts get
     assert ops_tensor.decode_splits(9, 8, 2304, 148) == 2          # 72 clusters of 4 do not fit either
     # the kernel that shares all pages of a launch evenly: uneven contexts from 32 (token, kv head) pairs, even ones
-    # where the clusters gave up splits to fit or single blocks make more than a wave
+    # where the clusters would leave SMs idle or single blocks make more than a wave
     streams = lambda t, nkv, uneven=0, nh=None: ops_tensor.decode_streams(t, nh or 2 * nkv, nkv, 4096, 148, uneven)
     assert not streams(8, 4) and streams(9, 4) and not streams(16, 4) and not streams(64, 4) and streams(64, 8)
+    assert streams(12, 4) and streams(24, 4) and streams(48, 4) and streams(4, 4) and not streams(1, 4)
     assert streams(56, 4, 1) and streams(8, 4, 1) and not streams(7, 4, 1) and streams(9, 8) and not streams(8, 8)
     assert not streams(64, 4, 1, nh=64)                            # 16 query heads per kv head: the cluster kernel

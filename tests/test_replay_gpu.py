@@ -28,9 +28,11 @@ def expected(folders):
     return out
 
 
-def _engine(folder, dtype, max_tokens, kernels="auto"):
+def _engine(folder, dtype, max_tokens, kernels="auto", attention="routed"):
     from glint_b200.engine.loading import build_engine, load_model
-    return build_engine(load_model(folder, dtype, kernels=kernels), max_tokens, num_slots=4)
+    engine = build_engine(load_model(folder, dtype, kernels=kernels), max_tokens, num_slots=4)
+    engine.rt.single_token_attention(attention)
+    return engine
 
 
 def _check(name, dtype, steps, outputs, expected_logits):
@@ -66,6 +68,21 @@ def test_replay_in_process(folders, expected, name, mode, dtype):
     if mode == "mixed":
         assert any(s["reuses"] > 0 for s in engine.cache.stats().values()), "no page was used again"
     assert all(s["live"] == 0 for s in engine.cache.stats().values())
+
+
+@pytest.mark.parametrize("mode", ["tail", "mixed"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_replay_with_the_page_sharing_attention_kernel(folders, expected, name, mode):
+    """Single tokens through the kernel that shares all pages of a launch evenly among its blocks (the runtime
+    takes it only for larger launches than these): the last 32 tokens one by one, and mixed steps with pages
+    that are used again."""
+    reqs, want = expected[name]
+    steps = MODES[mode](reqs)
+    engine = _engine(folders[name], "bfloat16", tracing.max_live_tokens(steps), attention="stream")
+    outputs = tracing.run_in_process(engine, steps)
+    _check(name, "bfloat16", steps, outputs, want)
+    assert all(s["live"] == 0 for s in engine.cache.stats().values())
+    engine.rt.check_status()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -113,8 +130,9 @@ def test_single_tokens_in_front_of_portions(folders, expected, name, dtype):
         engine.rt.check_status()
 
 
+@pytest.mark.parametrize("attention", ["routed", "stream"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_decode_steps_padded_to_a_graph_size(folders, dtype):
+def test_decode_steps_padded_to_a_graph_size(folders, dtype, attention):
     """Steps of 11 and then 9 single tokens replay the graph captured for 12 (the rows that fill the step
     up belong to the engine's spare slot): the logits are the plain ones at every step, a request that ends
     changes nothing for the others, and the spare slot's page is not counted among the caller's."""
@@ -126,6 +144,7 @@ def test_decode_steps_padded_to_a_graph_size(folders, dtype):
     reqs = [random_tokens(14 + 3 * i, vocab, 700 + i) for i in range(11)]
     want = [plain_logits(folders[name], r) for r in reqs]
     engine = build_engine(load_model(folders[name], dtype), 11 * 64, num_slots=11)
+    engine.rt.single_token_attention(attention)
     slots = [engine.open() for _ in reqs]
     tail = 6
     for s, r in zip(slots, reqs):
