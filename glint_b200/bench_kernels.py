@@ -65,28 +65,53 @@ def bench_gemm(M, N, K, gated=False, splits=0, iters=20, path=None):
             "GB/s": round(nbytes / us / 1e3, 1), "TFLOP/s": round(flops / us / 1e6, 1)}
 
 
-def bench_attention_decode(batch, context, nh=8, nkv=4, hd=256, page=16, window=None, cap=50.0, splits=None, iters=20):
+def bench_attention_decode(batch, context, nh=8, nkv=4, hd=256, page=16, window=None, cap=50.0, splits=None, iters=20,
+                           kernel=None, spread=0.0):
+    """Single tokens of ``batch`` requests with ``context`` tokens cached (``spread`` > 0: uniformly between
+    (1 - spread) x context and context, seeded).  ``kernel``: "cluster", "stream", or None for the runtime's choice."""
     from . import ops_tensor
-    pages_per_seq = (context + page - 1) // page
-    n_pages = batch * pages_per_seq
-    bytes_kv = 2 * batch * context * nkv * hd * 2
-    n = min(_copies(bytes_kv), 16)
+    rng = np.random.default_rng(11)
+    contexts = [max(1, int(round(context * (1.0 - spread * rng.random())))) for _ in range(batch)]
+    pages = [(c + page - 1) // page for c in contexts]
+    n_pages = sum(pages)
+    keys = [min(c, window) if window else c for c in contexts]
+    nbytes = 2 * sum(keys) * nkv * hd * 2
+    n = min(_copies(nbytes), 16)
     pools = [(torch.randn(n_pages, nkv, page, hd, device=DEV).to(torch.bfloat16),
               torch.randn(n_pages, nkv, page, hd, device=DEV).to(torch.bfloat16)) for _ in range(n)]
-    table = torch.arange(n_pages, dtype=torch.int32, device=DEV).view(batch, pages_per_seq)
+    table = torch.full((batch, max(pages)), -1, dtype=torch.int32)
+    at = 0
+    for i, p in enumerate(pages):
+        table[i, :p] = torch.arange(at, at + p, dtype=torch.int32)
+        at += p
+    table = table.to(DEV)
     q = torch.randn(batch, nh * hd, device=DEV).to(torch.bfloat16)
     out = torch.empty_like(q)
-    pos = torch.full((batch,), context - 1, dtype=torch.int32, device=DEV)
+    pos = torch.tensor([c - 1 for c in contexts], dtype=torch.int32, device=DEV)
     seq = torch.arange(batch, dtype=torch.int32, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    sp = splits or ops_tensor.decode_splits(batch, nkv, context)
-    fn = lambda i: ops_tensor.attention_decode(q, pools[i][0], pools[i][1], pos, seq, table, out, nh, nkv, hd, page,
-                                               n_pages, 1 / 16.0, cap, window, status, sp)
+    share = sum(contexts) / (batch * max(contexts))
+    uneven = 0 if share > 0.7 else 1 if share > 0.35 else 2 if share > 0.175 else 3
+    if kernel is None:
+        kernel = "stream" if ops_tensor.decode_streams(batch, nh, nkv, max(contexts), uneven=uneven) else "cluster"
+    res = {"kernel": "attention_decode", "batch": batch, "context": context, "spread": spread}
+    if kernel == "stream":
+        blocks = 2 * ops_tensor.sm_count()
+        plan = ops_tensor.attention_decode_stream_plan(pos, seq, batch, window, page, hd, nkv, blocks)
+        partials = torch.empty(blocks * 2 * (nh // nkv) * (hd + 4), dtype=torch.float32, device=DEV)
+        arrive = torch.zeros(batch * nkv, dtype=torch.int32, device=DEV)
+        fn = lambda i: ops_tensor.attention_decode_stream(q, pools[i][0], pools[i][1], pos, seq, table, out, nh, nkv,
+                                                          hd, page, n_pages, 1 / 16.0, cap, window, status, plan,
+                                                          partials, arrive)
+        res["blocks"] = blocks
+    else:
+        sp = splits or ops_tensor.decode_splits(batch, nkv, max(contexts), uneven=uneven)
+        fn = lambda i: ops_tensor.attention_decode(q, pools[i][0], pools[i][1], pos, seq, table, out, nh, nkv, hd, page,
+                                                   n_pages, 1 / 16.0, cap, window, status, sp)
+        res["splits"] = sp
     us = _time(fn, n, iters)
-    keys = min(context, window) if window else context
-    nbytes = 2 * batch * keys * nkv * hd * 2
-    return {"kernel": "attention_decode", "batch": batch, "context": context, "splits": sp, "us": round(us, 2),
-            "GB/s": round(nbytes / us / 1e3, 1)}
+    res.update({"variant": kernel, "us": round(us, 2), "GB/s": round(nbytes / us / 1e3, 1)})
+    return res
 
 
 def bench_attention_prefill(tokens, before=0, nh=8, nkv=4, hd=256, page=16, window=None, cap=50.0, iters=10,
@@ -232,7 +257,13 @@ def main():
     ap.add_argument("--shape", default="2b", help="step: 2b, 9b, 27b or a model folder")
     ap.add_argument("--portion", type=int, default=0, help="step: tokens of a prompt portion beside the single tokens")
     ap.add_argument("--spread", type=float, default=0.0,
-                    help="step: contexts uniform between (1 - spread) x context and context instead of all equal")
+                    help="step, attention-decode: contexts uniform between (1 - spread) x context and context "
+                         "instead of all equal")
+    ap.add_argument("--kernel", default=None, choices=["cluster", "stream"],
+                    help="attention-decode: the kernel (default: the runtime's choice)")
+    ap.add_argument("--heads", type=int, default=8, help="attention-decode: query heads")
+    ap.add_argument("--kv-heads", type=int, default=4, help="attention-decode: kv heads")
+    ap.add_argument("--head-dim", type=int, default=256, help="attention-decode: head size")
     ap.add_argument("--timeline", action="store_true", help="step: kernel starts and ends inside a graph replay")
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
@@ -263,8 +294,9 @@ def main():
         out.append(bench_attention_prefill(a.tokens, iters=a.iters, kernel="mma"))
         out.extend(bench_rows(a.tokens))
     elif a.what == "attention-decode":
-        out.append(bench_attention_decode(a.batch, a.context, page=a.page, window=a.window or None,
-                                          splits=a.splits or None, iters=a.iters))
+        out.append(bench_attention_decode(a.batch, a.context, nh=a.heads, nkv=a.kv_heads, hd=a.head_dim, page=a.page,
+                                          window=a.window or None, splits=a.splits or None, iters=a.iters,
+                                          kernel=a.kernel, spread=a.spread))
     elif a.what == "attention-prefill":
         out.append(bench_attention_prefill(a.tokens, page=a.page, window=a.window or None, iters=a.iters))
     elif a.what == "rows":
