@@ -257,10 +257,21 @@ extern "C" int glint_op_attention(const GlintRuntime* rt, const GlintStep* step,
   const GlintTensorEntries& t = rt->tensor;
   if (step->max_seq_len > 1 && tiled_attention_supported(nh, nkv, hd, page)) {
     const int lead = step->leading_single;
-    if (lead > 0 && (lead <= SPLIT_SINGLES_UP_TO || step->leading_single_context >= SPLIT_SINGLES_FROM) && dec) {
+    // What the single tokens in front would cost in the tiled kernel.  Walks: a block of 128 rows for each token
+    // and kv head, two to eight rows of it in use, takes about 3 us of an SM per tile of 128 keys.  Slots: the
+    // grid has a block for every (query tile of the longest portion, request, kv head), and a block that finds
+    // its request shorter than that leaves after one load, about 1.8 us of an SM each.
+    const int G = nh / nkv;
+    const long long walks = (((long long)lead * ((step->leading_single_context + 127) / 128)) >> step->uneven) * nkv;
+    const long long slots = (long long)lead * ((step->max_seq_len * G + 127) / 128) * nkv;
+    if (lead > 0 && dec && (lead <= SPLIT_SINGLES_UP_TO || step->leading_single_context >= SPLIT_SINGLES_FROM ||
+                            walks >= 4ll * rt->sms || slots >= 8ll * rt->sms)) {
       // Decoding requests in front of the prompt portions: in the tiled kernel one block walks all keys of
-      // such a row (8192 keys: 150 us, and the step waits for it); the split kernel shares them among a
-      // cluster.  Many requests with short contexts stay: their walks hide behind the portions' tiles.
+      // such a row (8192 keys: 150 us, and the step waits for it), and many rows take the SMs from the
+      // portions' tiles (48 requests of 2400 keys beside a portion of 4048 tokens, 8 kv heads: 494 us, of which
+      // the portion needs 176; 16 requests beside 4080 tokens: 290 us, of which 100 go to blocks that only find
+      // out that they have nothing to do); the single-token kernels stream them at the memory's speed instead.
+      // A few requests with short contexts beside short portions stay: their walks hide behind the portions' tiles.
       // The portions keep their absolute token offsets.
       int rc = decode_attention(rt, step, q, view, out, lead, nh, nkv, hd, multiplier, cap, window, stream);
       if (rc != GLINT_OK) return rc;
