@@ -3,12 +3,12 @@
 // Memory-bound work: every key and value row of the request is read once per kv head and shared
 // by all query heads of its group.  grid = (tokens, kv heads, splits).  A producer warp streams
 // the request's pages into a ring of shared-memory stages with TMA tile loads (128-byte swizzle,
-// completion on an mbarrier); four consumer warps take the pages in turn.  A consumer computes,
+// completion on an mbarrier); three consumer warps take the pages in turn.  A consumer computes,
 // per 16 keys, scores^T = K q^T and out^T += V^T p^T with mma.sync tiles in which the N
 // dimension (8) holds the query heads of the group, so that keys and values are the large
 // operands read straight from shared memory and nothing is padded to a 128-row tile.  Scores,
 // soft cap, running max/sum and the output accumulator are 32-bit (src/tensor/flash.rs:65-123);
-// probabilities are rounded to bfloat16 for the second product.  The four warps are merged in
+// probabilities are rounded to bfloat16 for the second product.  The three warps are merged in
 // shared memory in warp order.  With more than one split, the splits of a (token, kv head) are
 // the blocks of one thread-block cluster: every block leaves its partial result in its own shared
 // memory, and after a cluster barrier each block adds up, in split order, its share of the output
@@ -21,7 +21,12 @@
 
 namespace glint {
 
-constexpr int DEC_WARPS = 4;                      // consumer warps
+// Consumer warps.  Three and not four: the ring holds a multiple of this many stages (see the kernels), and two
+// blocks of an SM have room for six stages of a page of head size 256 each but not for eight, so three warps
+// keep 96 KB in flight per block where four keep 64 KB.  The products are a tenth of a block's time either
+// way.  64 requests x 4 kv heads at 2176 keys: 99.9 -> 89.6 us (0.97 of the measured HBM bandwidth); 8
+// requests: 22.9 -> 21.0 us; 56 requests of uneven length in the page-sharing kernel: 105.8 -> 101.0 us.
+constexpr int DEC_WARPS = 3;
 constexpr int DEC_THREADS = DEC_WARPS * 32;
 constexpr int DEC_BLOCK = DEC_THREADS + 32;       // plus the producer warp
 constexpr int DEC_MAX_STAGES = 12;
@@ -29,7 +34,7 @@ constexpr int DEC_MAX_SPLITS = 16;                // blocks of a cluster
 constexpr int DEC_HEADS = 8;                      // query heads per pass (the MMA's N)
 constexpr int SUB_BYTES_PER_ROW = 128;            // one swizzle row: 64 bf16
 
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(DEC_WARPS * 32) : "memory"); }
 
 __device__ __forceinline__ void ldsm_x4(uint32_t* r, uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -265,8 +270,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     for (int i = 0; i < HD / 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-    // Iteration `it` (over all passes) belongs to warp it % 4 and stage it % stages; the stage count
-    // is a multiple of 4, so a stage is always read by the same warp and that warp sees every
+    // Iteration `it` (over all passes) belongs to warp it % 3 and stage it % stages; the stage count
+    // is a multiple of 3, so a stage is always read by the same warp and that warp sees every
     // phase of the stage's barrier (a waiter that skipped a phase would match the wrong parity).
     const int it_lo = pass * n_pages, it_hi = it_lo + n_pages;
     for (int it = it_lo + ((warp - it_lo) % DEC_WARPS + DEC_WARPS) % DEC_WARPS; it < it_hi; it += DEC_WARPS) {
@@ -281,7 +286,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&sh->empty[s]);     // this warp is done with stage s
     }
-    // ---- this warp's totals, then the four warps are merged in shared memory, in warp order ----------
+    // ---- this warp's totals, then the three warps are merged in shared memory, in warp order ---------
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       l[h] += __shfl_xor_sync(0xffffffffu, l[h], 4);
@@ -559,7 +564,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
 #pragma unroll
     for (int i = 0; i < HD / 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    // Page `it` of the block belongs to warp it % 4 and stage it % stages (a multiple of 4: a stage is always
+    // Page `it` of the block belongs to warp it % 3 and stage it % stages (a multiple of 3: a stage is always
     // read by the same warp, which therefore sees every phase of the stage's barrier).
     for (int it = it0 + ((warp - it0) % DEC_WARPS + DEC_WARPS) % DEC_WARPS; it < it0 + n; it += DEC_WARPS) {
       const int s = it % stages;
@@ -572,7 +577,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&sh->empty[s]);
     }
-    // ---- this warp's totals; the four warps are merged in shared memory, in warp order ---------------------
+    // ---- this warp's totals; the three warps are merged in shared memory, in warp order --------------------
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       l[h] += __shfl_xor_sync(0xffffffffu, l[h], 4);
