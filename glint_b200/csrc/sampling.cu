@@ -97,7 +97,9 @@ __device__ __forceinline__ unsigned ordered_key(float v);
 // equal values the later index wins as in `better`), and the block that arrives last at the row's
 // counter writes the index and leaves key and counter zero for the next launch.  `keys` and
 // `counters` hold one zeroed entry per row.
-__global__ void __launch_bounds__(SAMPLE_THREADS)
+constexpr int ARGMAX_WIDE_THREADS = 256;   // eight blocks to an SM: the launch of 64 rows is one wave
+
+__global__ void __launch_bounds__(ARGMAX_WIDE_THREADS)
 argmax_wide_kernel(const float* __restrict__ logits, long long row_stride, int V, int chunk,
                    unsigned long long* __restrict__ keys, int* __restrict__ counters, int* __restrict__ out) {
   __shared__ ArgBest scratch[33];
@@ -848,18 +850,30 @@ GLINT_API int glint_argmax(const float* logits, long long row_stride, int rows, 
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
-// Rows of 64 K entries and more are shared by several blocks; `keys` (64-bit) and `counters` hold one
+// Rows of 32 K entries and more are shared by several blocks; `keys` (64-bit) and `counters` hold one
 // zeroed entry per row and are left zeroed.  Without them, or for narrow rows, one block per row.
 GLINT_API int glint_argmax_wide(const float* logits, long long row_stride, int rows, int V, int* out,
                                 unsigned long long* keys, int* counters, cudaStream_t stream) {
   if (rows <= 0) return GLINT_OK;
   if (V <= 0) return GLINT_ERR_BAD_ARG;
-  int chunks = V / 16384;
-  if (chunks > 32) chunks = 32;
-  if (!keys || !counters || chunks < 2 || rows > 65535) return glint_argmax(logits, row_stride, rows, V, out, stream);
+  if (!keys || !counters || V < 32768 || rows > 65535) return glint_argmax(logits, row_stride, rows, V, out, stream);
+  // About four blocks of 256 threads for every SM, a chunk of at least 4096 entries each (one round of four
+  // 16-byte loads per thread): blocks of 1024 threads with 17,000 entries each, three waves of them for 64 rows,
+  // spent their time on their own start, reduction and atomics (64 rows of 256,000: 33 us for 65 MB).
+  static int sms = 0;
+  if (sms <= 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 128;
+  }
+  int chunks = (4 * sms + rows - 1) / rows;
+  if (chunks > V / 4096) chunks = V / 4096;
+  if (chunks > 64) chunks = 64;
+  if (chunks < 2) chunks = 2;
   const int chunk = (((V + chunks - 1) / chunks) + 3) & ~3;
   chunks = (V + chunk - 1) / chunk;
-  const cudaError_t e = launch_kernel(argmax_wide_kernel, dim3(rows, chunks), dim3(SAMPLE_THREADS), 0, stream, logits,
+  const cudaError_t e = launch_kernel(argmax_wide_kernel, dim3(rows, chunks), dim3(ARGMAX_WIDE_THREADS), 0, stream, logits,
                                       row_stride, V, chunk, keys, counters, out);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
