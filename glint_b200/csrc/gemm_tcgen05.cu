@@ -742,8 +742,7 @@ static int gemm_launch(const void* x, const void* w, void* out, int out_bf16, in
   const int m_tiles_256 = (M + bn_max - 1) / bn_max;
   int bn = ((M + m_tiles_256 - 1) / m_tiles_256 + 15) / 16 * 16;
   if (dual && bn > 256) bn = 256;
-  p.BN = bn;
-  const int m_tiles = (M + bn - 1) / bn;
+  int m_tiles = (M + bn - 1) / bn;
   int n_tiles = rope ? N / (2 * GEMM_BM) : (N + GEMM_BM - 1) / GEMM_BM;
   // A plain product whose 128-feature tiles would need more than one wave, and whose 256-feature
   // tiles still fill three quarters of the SMs, runs as the dual kernel with two plain tiles.
@@ -763,6 +762,26 @@ static int gemm_launch(const void* x, const void* w, void* out, int out_bf16, in
     dual_offset = GEMM_BM;
     n_tiles = n_tiles_wide;
   }
+  // More tiles than SMs: the launch lasts as many waves as the tiles need, the last one mostly empty when
+  // the count falls just behind a multiple of the SMs (4096 tokens x 3584 features in tiles of 256 x 256:
+  // 224 tiles, two waves for the work of one and a half).  A tile's time goes with its tokens, so token
+  // tiles a little narrower that fill the last wave cost less: waves x (tokens per tile + what a tile costs
+  // beside its K loop, about 24 tokens' worth) is what is made smallest, down to tiles of 128 tokens.
+  if (force_splits == 0 && (long long)n_tiles * m_tiles > sms) {
+    long long best = (((long long)n_tiles * m_tiles + sms - 1) / sms) * (bn + 24);
+    for (int mt = m_tiles + 1; mt <= (M + 127) / 128; ++mt) {
+      const int bn_c = ((M + mt - 1) / mt + 15) / 16 * 16;
+      if (bn_c < 128) break;
+      const int mt_c = (M + bn_c - 1) / bn_c;
+      const long long cost = (((long long)n_tiles * mt_c + sms - 1) / sms) * (bn_c + 24);
+      if (cost < best) {
+        best = cost;
+        bn = bn_c;
+        m_tiles = mt_c;
+      }
+    }
+  }
+  p.BN = bn;
   const int stage_bytes = A_STAGE_BYTES * (dual ? 2 : 1) + bn * GEMM_BK * 2;
   int stages = (227 * 1024 - 1024 - (int)sizeof(GemmShared) - 256) / stage_bytes;
   if (stages > GEMM_MAX_STAGES) stages = GEMM_MAX_STAGES;
