@@ -764,17 +764,26 @@ static int gemm_launch(const void* x, const void* w, void* out, int out_bf16, in
   }
   // More tiles than SMs: the launch lasts as many waves as the tiles need, the last one mostly empty when
   // the count falls just behind a multiple of the SMs (4096 tokens x 3584 features in tiles of 256 x 256:
-  // 224 tiles, two waves for the work of one and a half).  A tile's time goes with its tokens, so token
-  // tiles a little narrower that fill the last wave cost less: waves x (tokens per tile + what a tile costs
-  // beside its K loop, about 24 tokens' worth) is what is made smallest, down to tiles of 128 tokens.
-  if (force_splits == 0 && (long long)n_tiles * m_tiles > sms) {
-    long long best = (((long long)n_tiles * m_tiles + sms - 1) / sms) * (bn + 24);
+  // 224 tiles, two waves for the work of one and a half).  Token tiles a little narrower that fill the last
+  // wave cost less.  A K block of a tile takes the longer of its tensor time (0.75 us for 256 features x 256
+  // tokens) and its operands' way into shared memory (0.54 us for 256 + 256 rows of 128 bytes), as measured in
+  // the prefill products, and a tile costs about 3 us and 8 ns per token beside its K loop (its start and its
+  // epilogue, which do not overlap the next tile's loop); waves x that is made smallest, down to tiles of 128
+  // tokens.
+  if ((force_splits == 0 || rope) && (long long)n_tiles * m_tiles > sms) {
+    const int features = dual ? 2 * GEMM_BM : GEMM_BM;
+    const int k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
+    auto waves_cost = [&](int tokens, int mt) {
+      const float tensor = 0.75f * features * tokens / 65536.f, intake = 0.54f * (features + tokens) / 512.f;
+      return (float)(((long long)n_tiles * mt + sms - 1) / sms) * (fmaxf(tensor, intake) * k_blocks + 3.0f + 0.008f * tokens);
+    };
+    float best = waves_cost(bn, m_tiles);
     for (int mt = m_tiles + 1; mt <= (M + 127) / 128; ++mt) {
       const int bn_c = ((M + mt - 1) / mt + 15) / 16 * 16;
       if (bn_c < 128) break;
       const int mt_c = (M + bn_c - 1) / bn_c;
-      const long long cost = (((long long)n_tiles * mt_c + sms - 1) / sms) * (bn_c + 24);
-      if (cost < best) {
+      const float cost = waves_cost(bn_c, mt_c);
+      if (cost < 0.97f * best) {          // a clear gain only: the tiles of 256 tokens are the ones measured most
         best = cost;
         bn = bn_c;
         m_tiles = mt_c;

@@ -17,7 +17,9 @@ def _bf16(t):
 
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 4096, 2304), (5, 200, 72), (16, 2304, 2048), (33, 1000, 328),
                                    (64, 512, 9216), (100, 130, 8), (256, 256, 256), (300, 384, 520),
-                                   (777, 2304, 576)])
+                                   (777, 2304, 576),
+                                   (2500, 2304, 72),      # 18 x 10 tiles on 148 SMs: token tiles of 240 fill two waves
+                                   (3000, 3584, 136)])    # tiles of 256 features, 14 x 14 of them with 224 tokens each
 def test_gemm_tcgen05_against_float32(M, N, K):
     from glint_b200 import ops_tensor
     torch.manual_seed(M * 7 + N)
@@ -150,7 +152,8 @@ def test_gemm_soft_cap_and_bf16_output():
     assert (out16.float() - want).abs().max().item() < 0.15
 
 
-@pytest.mark.parametrize("M,I,K,act", [(7, 320, 96, "gelu_tanh"), (130, 9216, 2304, "gelu_tanh"), (40, 200, 136, "silu")])
+@pytest.mark.parametrize("M,I,K,act", [(7, 320, 96, "gelu_tanh"), (130, 9216, 2304, "gelu_tanh"), (40, 200, 136, "silu"),
+                                       (1300, 3840, 72, "gelu_tanh")])     # 30 x 6 tiles: token tiles of 192 instead of 224
 def test_gemm_gated_against_float32(M, I, K, act):
     from glint_b200 import ops_tensor
     torch.manual_seed(3)
@@ -242,6 +245,7 @@ def test_qkv_product_with_rotation_and_cache_write_in_one_kernel(M, K, nh, nkv, 
     ([300, 41, 2], [0, 77, 1000], 136, 3, 1, 256, 16, True, 12),   # tiles of 128 tokens to have 12 blocks
     ([5], [3], 64, 2, 2, 512, 32, True, 0),                         # two groups of 128 pairs per head
     ([600], [4090], 2304, 8, 4, 256, 16, True, 0),
+    ([2400, 100], [0, 7], 72, 8, 4, 256, 16, True, 0),             # 16 x 10 tiles on 148 SMs: token tiles of 240
     ([70, 9], [0, 5], 200, 1, 1, 256, 16, False, 0)])
 def test_tiled_qkv_product_with_rotation_and_cache_write(lens, starts, K, nh, nkv, hd, page, writes, min_blocks):
     """The same on the tiled kernel for portions of prompts: the angles come from a table made by
