@@ -762,15 +762,16 @@ static int gemm_launch(const void* x, const void* w, void* out, int out_bf16, in
     dual_offset = GEMM_BM;
     n_tiles = n_tiles_wide;
   }
-  // More tiles than SMs: the launch lasts as many waves as the tiles need, the last one mostly empty when
-  // the count falls just behind a multiple of the SMs (4096 tokens x 3584 features in tiles of 256 x 256:
+  // More tiles than half the SMs (fewer get a split of K below): the launch lasts as many waves as the tiles
+  // need, the last one mostly empty when the count falls just behind a multiple of the SMs (4096 tokens x 3584 features in tiles of 256 x 256:
   // 224 tiles, two waves for the work of one and a half).  Token tiles a little narrower that fill the last
-  // wave cost less.  A K block of a tile takes the longer of its tensor time (0.75 us for 256 features x 256
+  // wave cost less, and so do narrower tiles that still fit one wave (2048 tokens x 16 pairs of q/k/v tiles: 128
+  // tiles of 256 tokens, or 144 of 240).  A K block of a tile takes the longer of its tensor time (0.75 us for 256 features x 256
   // tokens) and its operands' way into shared memory (0.54 us for 256 + 256 rows of 128 bytes), as measured in
   // the prefill products, and a tile costs about 3 us and 8 ns per token beside its K loop (its start and its
   // epilogue, which do not overlap the next tile's loop); waves x that is made smallest, down to tiles of 128
   // tokens.
-  if ((force_splits == 0 || rope) && (long long)n_tiles * m_tiles > sms) {
+  if ((force_splits == 0 || rope) && 2ll * n_tiles * m_tiles > sms) {
     const int features = dual ? 2 * GEMM_BM : GEMM_BM;
     const int k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
     auto waves_cost = [&](int tokens, int mt) {
