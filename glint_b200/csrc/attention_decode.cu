@@ -435,7 +435,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
                                const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_pages,
                                __nv_bfloat16* __restrict__ out, int T, int nh, int nkv, int hd, int page_size,
                                int num_pages, float multiplier, float cap, int window, int stages, int whole_page,
-                               const StreamPlan plan, int* __restrict__ status) {
+                               int early, const StreamPlan plan, int* __restrict__ status) {
   extern __shared__ uint8_t dec_raw[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dec_raw) + 1023) & ~(uintptr_t)1023);
   const int G = nh / nkv;                                  // at most DEC_HEADS (the host checks)
@@ -460,12 +460,18 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
     tc::tma_prefetch_desc(&map_v);
   }
   __syncthreads();
-  pdl_wait_release();                           // the keys of this step, q and the plan come from earlier kernels
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // q and the newest key and value of every token come from the kernel before this one.  With `early` the
+  // caller promises that nothing else does: the tokens belong to different requests, so that only the last
+  // page of a token's range is being written, and the plan was made by a kernel further back.  The producer
+  // warp then starts the block's first pages on their way before it waits for that kernel, as many as the ring
+  // holds, and they arrive while that kernel finishes.
+  bool waited = !(early && warp == DEC_WARPS);
+  if (waited) pdl_wait_release();
   const int4 start = plan.starts[2 * blockIdx.x], start2 = plan.starts[2 * blockIdx.x + 1];
   if (start.w <= 0) return;                     // fewer pages than blocks
   const int W = start2.x;
   volatile int* abort_flag = &sh->abort_flag;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   // The first pair's position and table row come with the plan: two loads fewer between the wait and the
   // first page on its way.
@@ -492,6 +498,11 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
         for (int j = 0; j < 32 && base + j < n; ++j) {
           const int it = it0 + base + j;
           const int pg = __shfl_sync(0xffffffffu, page, j);
+          // the ring is full, or this is the page that the kernel before is writing: time to wait for it
+          if (!waited && (it >= stages || off + base + j == sg.pages - 1)) {
+            pdl_wait_release();
+            waited = true;
+          }
           if (tc::elect_one()) {
             const int s = it % stages;
             bool ok = true;
@@ -524,6 +535,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
         }
       }
     }
+    if (!waited) pdl_wait_release();
     return;
   }
 
@@ -898,14 +910,14 @@ GLINT_API int glint_attention_decode_stream_plan(const int* positions, const int
 }
 
 // `partials`: glint_attention_decode_stream_workspace floats; `arrive`: [T][nkv] counters that are zero before
-// the first launch (every launch leaves them zero).  The plan must have been made for the same positions,
+// the first launch (every launch leaves them zero).  `early`: see the kernel; 0 is always right.  The plan must have been made for the same positions,
 // window, page size, kv heads and number of blocks.
 GLINT_API int glint_attention_decode_stream(const void* q, const void* k_pool, const void* v_pool,
                                             const int* positions, const int* token_seq, const int* block_table,
                                             int max_pages, void* out, int T, int nh, int nkv, int hd, int page_size,
                                             int num_pages, float multiplier, float cap, int window, int blocks,
-                                            const void* starts, float* partials, int* arrive, int* status,
-                                            cudaStream_t stream) {
+                                            const void* starts, float* partials, int* arrive, int early,
+                                            int* status, cudaStream_t stream) {
   if (T <= 0) return GLINT_OK;
   if (!starts || !partials || !arrive || blocks < 1 || ((uintptr_t)partials & 15)) return GLINT_ERR_BAD_ARG;
   if (!glint_attention_decode_stream_supported(nh, nkv, hd, page_size)) return GLINT_ERR_UNSUPPORTED_SIZE;
@@ -935,7 +947,7 @@ GLINT_API int glint_attention_decode_stream(const void* q, const void* k_pool, c
     if (e != cudaSuccess) return (int)e;                                                                              \
     e = launch_kernel(attention_decode_stream_kernel<HD>, dim3(blocks), dim3(DEC_BLOCK), (size_t)smem, stream, map_k,  \
                       map_v, qq, positions, token_seq, block_table, max_pages, oo, T, nh, nkv, hd, page_size,          \
-                      num_pages, multiplier, cap, window, stages, whole_page, plan, status);                          \
+                      num_pages, multiplier, cap, window, stages, whole_page, early ? 1 : 0, plan, status);           \
     if (e != cudaSuccess) return (int)e;                                                                              \
   }
   if (hd <= 64) LAUNCH(64)

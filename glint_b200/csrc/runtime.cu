@@ -214,6 +214,10 @@ static int decode_attention(const GlintRuntime* rt, const GlintStep* step, const
           a->plan_page[i] == page && a->plan_nkv[i] == nkv && a->plan_hd[i] == hd)
         slot = i;
     void* starts = nullptr;
+    // A plan that an earlier layer of the step made lies several kernels back: the producer warps may read it
+    // and start their first pages before they wait for the kernel in front (which writes only the tokens'
+    // newest keys and values: the tokens here are single tokens of different requests).
+    const int early = slot >= 0 ? 1 : 0;
     if (slot < 0) {
       slot = a->next;
       a->next = (a->next + 1) % GLINT_ATTN_PLANS;
@@ -231,7 +235,8 @@ static int decode_attention(const GlintRuntime* rt, const GlintStep* step, const
     starts = (char*)a->starts + (size_t)slot * a->blocks * 32;
     return counted(t.attention_decode_stream(q, view->k, view->v, step->positions, step->token_seq, table, max_pages, out,
                                              T, nh, nkv, hd, page, view->num_pages, multiplier, cap, window, a->blocks,
-                                             starts, a->partials, a->arrive, rt->status, stream));
+                                             starts, a->partials, a->arrive, a->early_off ? 0 : early, rt->status,
+                                             stream));
   }
   return counted(t.attention_decode(q, view->k, view->v, step->positions, step->token_seq, table, max_pages, out, T, nh,
                                     nkv, hd, page, view->num_pages, multiplier, cap, window,

@@ -49,8 +49,8 @@ struct GlintTensorEntries {
   int (*attention_decode_stream_plan)(const int*, const int*, int, int, int, int, int, int, int, int, void*, int*,
                                       cudaStream_t);
   int (*attention_decode_stream)(const void*, const void*, const void*, const int*, const int*, const int*, int, void*,
-                                 int, int, int, int, int, int, float, float, int, int, const void*, float*, int*, int*,
-                                 cudaStream_t);
+                                 int, int, int, int, int, int, float, float, int, int, const void*, float*, int*, int,
+                                 int*, cudaStream_t);
   int (*attention_prefill)(const void*, const void*, const void*, const int*, const int*, const int*, int, void*, int,
                            int, int, int, int, int, int, float, float, int, int*, cudaStream_t);
   int (*attention_tcgen05)(const void*, const void*, const void*, const int*, const int*, const int*, int, void*, int,
@@ -64,6 +64,7 @@ struct GlintTensorEntries {
 struct GlintAttnScratch {
   int mode;                     // 0: the runtime chooses between the two single-token kernels; 1: this one wherever
                                 // it takes the sizes; 2: never (tests and measurements)
+  int early_off;                // 1: no page is started before the wait for the kernel in front (measurements)
   int blocks;                   // blocks of a launch (two per SM)
   void* starts;                 // [GLINT_ATTN_PLANS][blocks][2] int4
   int* headers;                 // [GLINT_ATTN_PLANS][2]

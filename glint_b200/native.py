@@ -44,7 +44,7 @@ ATTN_PLANS = 8
 
 class AttnScratchStruct(Structure):
     """``GlintAttnScratch`` of csrc/runtime.h."""
-    _fields_ = [("mode", c_int), ("blocks", c_int), ("starts", c_void_p), ("headers", c_void_p), ("partials", c_void_p),
+    _fields_ = [("mode", c_int), ("early_off", c_int), ("blocks", c_int), ("starts", c_void_p), ("headers", c_void_p), ("partials", c_void_p),
                 ("partial_floats", c_longlong), ("arrive", c_void_p), ("arrive_ints", c_int), ("next", c_int),
                 ("plan_step", c_longlong * ATTN_PLANS), ("plan_tokens", c_int * ATTN_PLANS),
                 ("plan_window", c_int * ATTN_PLANS), ("plan_page", c_int * ATTN_PLANS), ("plan_nkv", c_int * ATTN_PLANS),

@@ -22,7 +22,7 @@ _SIGNATURES = {
     "glint_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P],
     "glint_attention_decode_stream_plan": [_P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
     "glint_attention_decode_stream": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P,
-                                      _P, _P, _P],
+                                      _P, _I, _P, _P],
     "glint_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
     "glint_attention_tcgen05": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
 }
@@ -248,7 +248,7 @@ def attention_decode_stream(q, k_pool, v_pool, positions, token_seq, block_table
                                                   ops.ptr(token_seq), ops.ptr(block_table), block_table.shape[1],
                                                   ops.ptr(out), T, nh, nkv, hd, page_size, num_pages, multiplier,
                                                   cap or 0.0, window or 0, blocks, ops.ptr(starts),
-                                                  ops.ptr(partials), ops.ptr(arrive), ops.ptr(status), ops.stream()),
+                                                  ops.ptr(partials), ops.ptr(arrive), 0, ops.ptr(status), ops.stream()),
               "attention_decode_stream")
 
 
