@@ -3,12 +3,12 @@
 // Memory-bound work: every key and value row of the request is read once per kv head and shared
 // by all query heads of its group.  grid = (tokens, kv heads, splits).  A producer warp streams
 // the request's pages into a ring of shared-memory stages with TMA tile loads (128-byte swizzle,
-// completion on an mbarrier); three consumer warps take the pages in turn.  A consumer computes,
+// completion on an mbarrier); three or four consumer warps take the pages in turn.  A consumer computes,
 // per 16 keys, scores^T = K q^T and out^T += V^T p^T with mma.sync tiles in which the N
 // dimension (8) holds the query heads of the group, so that keys and values are the large
 // operands read straight from shared memory and nothing is padded to a 128-row tile.  Scores,
 // soft cap, running max/sum and the output accumulator are 32-bit (src/tensor/flash.rs:65-123);
-// probabilities are rounded to bfloat16 for the second product.  The three warps are merged in
+// probabilities are rounded to bfloat16 for the second product.  The warps are merged in
 // shared memory in warp order.  With more than one split, the splits of a (token, kv head) are
 // the blocks of one thread-block cluster: every block leaves its partial result in its own shared
 // memory, and after a cluster barrier each block adds up, in split order, its share of the output
@@ -21,20 +21,23 @@
 
 namespace glint {
 
-// Consumer warps.  Three and not four: the ring holds a multiple of this many stages (see the kernels), and two
-// blocks of an SM have room for six stages of a page of head size 256 each but not for eight, so three warps
-// keep 96 KB in flight per block where four keep 64 KB.  The products are a tenth of a block's time either
-// way.  64 requests x 4 kv heads at 2176 keys: 99.9 -> 89.6 us (0.97 of the measured HBM bandwidth); 8
-// requests: 22.9 -> 21.0 us; 56 requests of uneven length in the page-sharing kernel: 105.8 -> 101.0 us.
-constexpr int DEC_WARPS = 3;
-constexpr int DEC_THREADS = DEC_WARPS * 32;
-constexpr int DEC_BLOCK = DEC_THREADS + 32;       // plus the producer warp
+// Consumer warps: a template parameter of both kernels, chosen by the host.  The ring holds a multiple of this
+// many stages (see the kernels), and two blocks of an SM have room for six stages of a page of head size 256 each
+// but not for eight, so three warps keep 96 KB in flight per block where four keep 64 KB; the products are a
+// tenth of a block's time either way.  64 requests x 4 kv heads at 2176 keys: 99.9 -> 89.6 us with three (0.97
+// of the measured HBM bandwidth); 56 requests of uneven length in the page-sharing kernel: 105.8 -> 101.0 us.
+// Launches of a few tokens keep four: their blocks hold 75 KB of shared memory instead of 107, and whole decode
+// steps of the 9B shape at 1 to 8 requests are 4 to 7 % faster with them (4.16 against 4.40 ms at one request:
+// the products on either side of the attention kernel lose their overlap with it), while from 16 requests on
+// three are faster (6.08 against 6.27 ms; 2B shape at 64: 4.03 against 4.29 ms).
+static inline int decode_consumer_warps(int tokens) { return tokens <= 8 ? 4 : 3; }
 constexpr int DEC_MAX_STAGES = 12;
 constexpr int DEC_MAX_SPLITS = 16;                // blocks of a cluster
 constexpr int DEC_HEADS = 8;                      // query heads per pass (the MMA's N)
 constexpr int SUB_BYTES_PER_ROW = 128;            // one swizzle row: 64 bf16
 
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(DEC_WARPS * 32) : "memory"); }
+template <int W>
+__device__ __forceinline__ void consumer_sync_w() { asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory"); }
 
 __device__ __forceinline__ void ldsm_x4(uint32_t* r, uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -163,13 +166,14 @@ __device__ __forceinline__ void decode_page(float (&o)[HD / 16][4], float (&m)[2
 }
 
 // HD: register capacity (head_dim <= HD; head_dim and page_size are multiples of 16).
-template <int HD>
-__global__ void __launch_bounds__(DEC_BLOCK, 2)
+template <int HD, int CW>
+__global__ void __launch_bounds__(CW * 32 + 32, 2)
 attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                         const __nv_bfloat16* __restrict__ q, const int* __restrict__ positions,
                         const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_pages,
                         __nv_bfloat16* __restrict__ out, int nh, int nkv, int hd, int page_size, int num_pages, float multiplier, float cap,
                         int window, int splits, int stages, int whole_page, int* __restrict__ status) {
+  constexpr int DEC_WARPS = CW, DEC_THREADS = CW * 32;          // consumer warps; one more warp is the producer
   extern __shared__ uint8_t dec_raw[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dec_raw) + 1023) & ~(uintptr_t)1023);
   const int t = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -270,8 +274,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     for (int i = 0; i < HD / 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-    // Iteration `it` (over all passes) belongs to warp it % 3 and stage it % stages; the stage count
-    // is a multiple of 3, so a stage is always read by the same warp and that warp sees every
+    // Iteration `it` (over all passes) belongs to warp it % warps and stage it % stages; the stage count
+    // is a multiple of the warps, so a stage is always read by the same warp and that warp sees every
     // phase of the stage's barrier (a waiter that skipped a phase would match the wrong parity).
     const int it_lo = pass * n_pages, it_hi = it_lo + n_pages;
     for (int it = it_lo + ((warp - it_lo) % DEC_WARPS + DEC_WARPS) % DEC_WARPS; it < it_hi; it += DEC_WARPS) {
@@ -286,7 +290,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&sh->empty[s]);     // this warp is done with stage s
     }
-    // ---- this warp's totals, then the three warps are merged in shared memory, in warp order ---------
+    // ---- this warp's totals, then the warps are merged in shared memory, in warp order ---------------
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       l[h] += __shfl_xor_sync(0xffffffffu, l[h], 4);
@@ -311,7 +315,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
       }
     }
-    consumer_sync();
+    consumer_sync_w<DEC_WARPS>();
     for (int j = 0; j < HP; ++j) {
       const int hg = pass * DEC_HEADS + j;
       if (hg >= G) break;
@@ -342,7 +346,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         xchg[(size_t)hg * stride_f + hd + 1] = L;
       }
     }
-    consumer_sync();   // the merge area is reused by the next pass
+    consumer_sync_w<DEC_WARPS>();   // the merge area is reused by the next pass
   }
 
   }  // consumer warps
@@ -428,14 +432,15 @@ __device__ __forceinline__ StreamSegment stream_segment(int pos, int window, int
   return s;
 }
 
-template <int HD>
-__global__ void __launch_bounds__(DEC_BLOCK, 2)
+template <int HD, int CW>
+__global__ void __launch_bounds__(CW * 32 + 32, 2)
 attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                                const __nv_bfloat16* __restrict__ q, const int* __restrict__ positions,
                                const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_pages,
                                __nv_bfloat16* __restrict__ out, int T, int nh, int nkv, int hd, int page_size,
                                int num_pages, float multiplier, float cap, int window, int stages, int whole_page,
                                int early, const StreamPlan plan, int* __restrict__ status) {
+  constexpr int DEC_WARPS = CW, DEC_THREADS = CW * 32;          // consumer warps; one more warp is the producer
   extern __shared__ uint8_t dec_raw[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dec_raw) + 1023) & ~(uintptr_t)1023);
   const int G = nh / nkv;                                  // at most DEC_HEADS (the host checks)
@@ -576,7 +581,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
 #pragma unroll
     for (int i = 0; i < HD / 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    // Page `it` of the block belongs to warp it % 3 and stage it % stages (a multiple of 3: a stage is always
+    // Page `it` of the block belongs to warp it % warps and stage it % stages (a multiple of them: a stage is always
     // read by the same warp, which therefore sees every phase of the stage's barrier).
     for (int it = it0 + ((warp - it0) % DEC_WARPS + DEC_WARPS) % DEC_WARPS; it < it0 + n; it += DEC_WARPS) {
       const int s = it % stages;
@@ -589,7 +594,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&sh->empty[s]);
     }
-    // ---- this warp's totals; the three warps are merged in shared memory, in warp order --------------------
+    // ---- this warp's totals; the warps are merged in shared memory, in warp order --------------------------
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       l[h] += __shfl_xor_sync(0xffffffffu, l[h], 4);
@@ -614,7 +619,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
         }
       }
     }
-    consumer_sync();
+    consumer_sync_w<DEC_WARPS>();
     const bool whole = begins && ends;
     float* partial = plan.partials + (((size_t)blockIdx.x * 2 + (begins ? 1 : 0)) * G) * pstride;
     for (int j = 0; j < G; ++j) {
@@ -644,7 +649,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
     if (!whole) {
       // ---- the pair is shared: the block that leaves its part last adds the parts up, in block order --------
       const int b_first = (int)(pair_begin / W), b_last = (int)((pair_begin + sg.pages - 1) / W);
-      consumer_sync();                               // every thread's share of the partial result is written
+      consumer_sync_w<DEC_WARPS>();                               // every thread's share of the partial result is written
       if (threadIdx.x == 0) {
         __threadfence();                             // and visible to the other blocks before this block is counted
         int* counter = plan.arrive + (size_t)t * nkv + kvh;
@@ -654,7 +659,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
         __threadfence();
         sh->last_one = last;
       }
-      consumer_sync();
+      consumer_sync_w<DEC_WARPS>();
       if (sh->last_one) {
         // Four output elements per thread, and of up to eight parts at a time the maxima, the sums and the
         // elements all in flight together: one trip to L2 for a pair that two to eight blocks share (a chain
@@ -701,7 +706,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
         }
       }
     }
-    consumer_sync();                                 // the merge area and last_one are used again by the next pair
+    consumer_sync_w<DEC_WARPS>();                                 // the merge area and last_one are used again by the next pair
     it0 += n;
     if (++kvh == nkv) {
       kvh = 0;
@@ -846,35 +851,42 @@ GLINT_API int glint_attention_decode(const void* q, const void* k_pool, const vo
   const int G = nh / nkv;
   const int HP = G < DEC_HEADS ? G : DEC_HEADS;
   const long long page_bytes = (long long)((hd + 63) / 64) * page_size * SUB_BYTES_PER_ROW;
-  const long long fixed = (long long)DEC_WARPS * HP * (hd + 2) * 4 + (splits > 1 ? (long long)G * (hd + 2) * 4 : 0) +
+  const int warps = decode_consumer_warps(T);
+  const long long fixed = (long long)warps * HP * (hd + 2) * 4 + (splits > 1 ? (long long)G * (hd + 2) * 4 : 0) +
                           sizeof(DecodeShared) + 1024 + 64;
   // a multiple of the consumer warps (see the kernel), as many as let two blocks share an SM
-  int stages = (int)((110 * 1024 - fixed) / (2 * page_bytes)) / DEC_WARPS * DEC_WARPS;
+  int stages = (int)((110 * 1024 - fixed) / (2 * page_bytes)) / warps * warps;
   if (stages > DEC_MAX_STAGES) stages = DEC_MAX_STAGES;
-  if (stages < DEC_WARPS) stages = DEC_WARPS;
+  if (stages < warps) stages = warps;
   const long long smem = stages * 2 * page_bytes + fixed;
   if (smem > 227 * 1024) return GLINT_ERR_UNSUPPORTED_SIZE;
   dim3 grid(T, nkv, splits);
   const __nv_bfloat16* qq = (const __nv_bfloat16*)q;
   __nv_bfloat16* oo = (__nv_bfloat16*)out;
-#define LAUNCH(HD)                                                                                              \
-  {                                                                                                             \
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                         (int)smem);                                                            \
-    if (e != cudaSuccess) return (int)e;                                                                        \
-    if (splits > 8) {                                                                                           \
-      e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);   \
-      if (e != cudaSuccess) return (int)e;                                                                      \
-    }                                                                                                           \
-    e = launch_kernel_cluster(attention_decode_kernel<HD>, grid, dim3(DEC_BLOCK), (size_t)smem, stream, splits,  \
-                              map_k, map_v, qq, positions, token_seq, block_table, max_pages, oo, nh, nkv, hd,    \
-                              page_size, num_pages, multiplier, cap, window, splits, stages, whole_page, status); \
-    if (e != cudaSuccess) return (int)e;                                                                        \
+#define LAUNCH_W(HD, W)                                                                                           \
+  {                                                                                                               \
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         (int)smem);                                                              \
+    if (e != cudaSuccess) return (int)e;                                                                          \
+    if (splits > 8) {                                                                                             \
+      e = cudaFuncSetAttribute(attention_decode_kernel<HD, W>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);  \
+      if (e != cudaSuccess) return (int)e;                                                                        \
+    }                                                                                                             \
+    e = launch_kernel_cluster(attention_decode_kernel<HD, W>, grid, dim3(W * 32 + 32), (size_t)smem, stream, splits, \
+                              map_k, map_v, qq, positions, token_seq, block_table, max_pages, oo, nh, nkv, hd,      \
+                              page_size, num_pages, multiplier, cap, window, splits, stages, whole_page, status);   \
+    if (e != cudaSuccess) return (int)e;                                                                          \
+  }
+#define LAUNCH(HD)                 \
+  {                                \
+    if (warps == 4) LAUNCH_W(HD, 4) \
+    else LAUNCH_W(HD, 3)           \
   }
   if (hd <= 64) LAUNCH(64)
   else if (hd <= 128) LAUNCH(128)
   else LAUNCH(256)
 #undef LAUNCH
+#undef LAUNCH_W
   return (int)cudaGetLastError();
 }
 
@@ -931,28 +943,35 @@ GLINT_API int glint_attention_decode_stream(const void* q, const void* k_pool, c
   if (rc != GLINT_OK) return rc;
   const int G = nh / nkv;
   const long long page_bytes = (long long)((hd + 63) / 64) * page_size * SUB_BYTES_PER_ROW;
-  const long long fixed = (long long)DEC_WARPS * G * (hd + 2) * 4 + sizeof(StreamShared) + 1024 + 64;
-  int stages = (int)((110 * 1024 - fixed) / (2 * page_bytes)) / DEC_WARPS * DEC_WARPS;
+  const int warps = decode_consumer_warps(T);
+  const long long fixed = (long long)warps * G * (hd + 2) * 4 + sizeof(StreamShared) + 1024 + 64;
+  int stages = (int)((110 * 1024 - fixed) / (2 * page_bytes)) / warps * warps;
   if (stages > DEC_MAX_STAGES) stages = DEC_MAX_STAGES;
-  if (stages < DEC_WARPS) stages = DEC_WARPS;
+  if (stages < warps) stages = warps;
   const long long smem = stages * 2 * page_bytes + fixed;
   if (smem > 227 * 1024) return GLINT_ERR_UNSUPPORTED_SIZE;
   StreamPlan plan = {(const int4*)starts, partials, arrive};
   const __nv_bfloat16* qq = (const __nv_bfloat16*)q;
   __nv_bfloat16* oo = (__nv_bfloat16*)out;
-#define LAUNCH(HD)                                                                                                    \
-  {                                                                                                                   \
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_stream_kernel<HD>,                                          \
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                     \
-    if (e != cudaSuccess) return (int)e;                                                                              \
-    e = launch_kernel(attention_decode_stream_kernel<HD>, dim3(blocks), dim3(DEC_BLOCK), (size_t)smem, stream, map_k,  \
-                      map_v, qq, positions, token_seq, block_table, max_pages, oo, T, nh, nkv, hd, page_size,          \
-                      num_pages, multiplier, cap, window, stages, whole_page, early ? 1 : 0, plan, status);           \
-    if (e != cudaSuccess) return (int)e;                                                                              \
+#define LAUNCH_W(HD, W)                                                                                                 \
+  {                                                                                                                     \
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_stream_kernel<HD, W>,                                         \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                       \
+    if (e != cudaSuccess) return (int)e;                                                                                \
+    e = launch_kernel(attention_decode_stream_kernel<HD, W>, dim3(blocks), dim3(W * 32 + 32), (size_t)smem, stream,      \
+                      map_k, map_v, qq, positions, token_seq, block_table, max_pages, oo, T, nh, nkv, hd, page_size,     \
+                      num_pages, multiplier, cap, window, stages, whole_page, early ? 1 : 0, plan, status);             \
+    if (e != cudaSuccess) return (int)e;                                                                                \
+  }
+#define LAUNCH(HD)                 \
+  {                                \
+    if (warps == 4) LAUNCH_W(HD, 4) \
+    else LAUNCH_W(HD, 3)           \
   }
   if (hd <= 64) LAUNCH(64)
   else if (hd <= 128) LAUNCH(128)
   else LAUNCH(256)
 #undef LAUNCH
+#undef LAUNCH_W
   return (int)cudaGetLastError();
 }
