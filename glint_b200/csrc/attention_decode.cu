@@ -14,6 +14,9 @@
 // memory, and after a cluster barrier each block adds up, in split order, its share of the output
 // elements from the shared memory of all of them (distributed shared memory): no workspace in
 // global memory, no counter, no second launch, a fixed order of addition.
+// A second kernel (attention_decode_stream_kernel, further down) cuts the pages of ALL (token, kv head)
+// pairs of a launch into equal shares for two blocks per SM instead, for launches whose contexts are of
+// uneven length or whose clusters would not fill the SMs; the runtime chooses between the two.
 // Score = (q.k) * multiplier, then cap * tanh(score / cap) (src/tensor/flash.rs:76-87); keys from
 // max(0, pos - window + 1) to pos (src/transformer/forward.rs:574-582).
 #include "common.cuh"
