@@ -729,17 +729,17 @@ decode_stream_plan_kernel(const int* __restrict__ positions, const int* __restri
                           int page_size, int nkv, int blocks, int min_units, int pair_cost, int4* __restrict__ starts,
                           int* __restrict__ header) {
   __shared__ int warp_sum[PLAN_THREADS / 32];
+  __shared__ int first_unit[PLAN_THREADS * PLAN_ROWS + 1];     // of every token's first pair; [T] = units in all
+  __shared__ int pair_units[PLAN_THREADS * PLAN_ROWS];         // of one pair of the token
   pdl_wait_release();
   const int r0 = threadIdx.x * PLAN_ROWS;
-  int units[PLAN_ROWS], pos[PLAN_ROWS], row[PLAN_ROWS], mine = 0;     // units of one pair of the token
+  int units[PLAN_ROWS], mine = 0;
 #pragma unroll
   for (int i = 0; i < PLAN_ROWS; ++i) {
-    pos[i] = r0 + i < T ? positions[r0 + i] : 0;
-    row[i] = r0 + i < T ? token_seq[r0 + i] : 0;
-    units[i] = r0 + i < T ? pair_cost + stream_segment(pos[i], window, page_size).pages : 0;
+    units[i] = r0 + i < T ? pair_cost + stream_segment(positions[r0 + i], window, page_size).pages : 0;
     mine += units[i] * nkv;
   }
-  // inclusive scan of the threads' page counts
+  // inclusive scan of the threads' unit counts
   int incl = mine;
   for (int o = 1; o < 32; o <<= 1) {
     const int up = __shfl_up_sync(0xffffffffu, incl, o);
@@ -752,22 +752,35 @@ decode_stream_plan_kernel(const int* __restrict__ positions, const int* __restri
     if (w < (int)(threadIdx.x >> 5)) before += warp_sum[w];
     total += warp_sum[w];
   }
-  const int W = max(min_units, (total + blocks - 1) / blocks);
-  // the blocks that begin inside this thread's tokens
-  int p = before;
 #pragma unroll
   for (int i = 0; i < PLAN_ROWS; ++i) {
-    const int span = units[i] * nkv;
-    if (span > 0) {
-      for (int b = (p + W - 1) / W; b < blocks && (long long)b * W < p + span; ++b) {
-        const int inside = b * W - p;
-        starts[2 * b] = make_int4(r0 + i, inside / units[i], inside % units[i], min(W, total - b * W));
-        starts[2 * b + 1] = make_int4(W, pos[i], row[i], pair_cost);
-      }
-      p += span;
+    if (r0 + i < T) {
+      first_unit[r0 + i] = before;
+      pair_units[r0 + i] = units[i];
+      before += units[i] * nkv;
     }
   }
-  for (int b = (total + W - 1) / W + threadIdx.x; b < blocks; b += PLAN_THREADS) starts[2 * b] = make_int4(0, 0, 0, 0);
+  if (threadIdx.x == 0) first_unit[T] = total;
+  __syncthreads();
+  const int W = max(min_units, (total + blocks - 1) / blocks);
+  // A thread per block: the token in whose units the block begins, by bisection.  (A thread per token, writing
+  // the starts of all blocks that begin inside it, left a launch of 12 tokens to three threads: 9.5 us.)
+  for (int b = threadIdx.x; b < blocks; b += PLAN_THREADS) {
+    const long long at = (long long)b * W;
+    if (at >= total) {
+      starts[2 * b] = make_int4(0, 0, 0, 0);
+      continue;
+    }
+    int lo = 0, hi = T - 1;                 // the last token with first_unit <= at
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (first_unit[mid] <= at) lo = mid;
+      else hi = mid - 1;
+    }
+    const int inside = (int)at - first_unit[lo], u = pair_units[lo];
+    starts[2 * b] = make_int4(lo, inside / u, inside % u, min(W, total - (int)at));
+    starts[2 * b + 1] = make_int4(W, positions[lo], token_seq[lo], pair_cost);
+  }
   if (threadIdx.x == 0) {
     header[0] = W;
     header[1] = total;
@@ -827,9 +840,16 @@ using namespace glint;
 // driver schedules clusters of that size for this kernel's launch shape.
 GLINT_API int glint_attention_decode_max_splits() { return DEC_MAX_SPLITS; }
 
+// Three stages of a page of keys and values (one for each of three consumer warps) have to fit a block's
+// shared memory: pages of up to 64 tokens at head size 256, 128 at 128, 256 at 64.
 GLINT_API int glint_attention_decode_supported(int nh, int nkv, int hd, int page_size) {
-  return (nkv > 0 && nh % nkv == 0 && hd % 16 == 0 && hd >= 16 && hd <= 256 && page_size % 16 == 0 &&
-          page_size >= 16 && page_size <= 256) ? 1 : 0;
+  if (!(nkv > 0 && nh % nkv == 0 && hd % 16 == 0 && hd >= 16 && hd <= 256 && page_size % 16 == 0 &&
+        page_size >= 16 && page_size <= 256))
+    return 0;
+  const long long page_bytes = (long long)((hd + 63) / 64) * page_size * SUB_BYTES_PER_ROW;
+  const int G = nh / nkv, HP = G < DEC_HEADS ? G : DEC_HEADS;
+  const long long fixed = 3ll * HP * (hd + 2) * 4 + (long long)G * (hd + 2) * 4 + 2048;
+  return 3 * 2 * page_bytes + fixed <= 227 * 1024 ? 1 : 0;
 }
 
 // head_dim a multiple of 16 up to 256, page_size a multiple of 16 up to 256, splits up to 16 (more
@@ -854,7 +874,10 @@ GLINT_API int glint_attention_decode(const void* q, const void* k_pool, const vo
   const int G = nh / nkv;
   const int HP = G < DEC_HEADS ? G : DEC_HEADS;
   const long long page_bytes = (long long)((hd + 63) / 64) * page_size * SUB_BYTES_PER_ROW;
-  const int warps = decode_consumer_warps(T);
+  int warps = decode_consumer_warps(T);
+  if (warps > 3 && warps * 2 * page_bytes + (long long)warps * HP * (hd + 2) * 4 + (long long)G * (hd + 2) * 4 + 2048 >
+                       227 * 1024)
+    warps = 3;                      // large pages: a stage for each of four warps does not fit
   const long long fixed = (long long)warps * HP * (hd + 2) * 4 + (splits > 1 ? (long long)G * (hd + 2) * 4 : 0) +
                           sizeof(DecodeShared) + 1024 + 64;
   // a multiple of the consumer warps (see the kernel), as many as let two blocks share an SM
@@ -946,7 +969,8 @@ GLINT_API int glint_attention_decode_stream(const void* q, const void* k_pool, c
   if (rc != GLINT_OK) return rc;
   const int G = nh / nkv;
   const long long page_bytes = (long long)((hd + 63) / 64) * page_size * SUB_BYTES_PER_ROW;
-  const int warps = decode_consumer_warps(T);
+  int warps = decode_consumer_warps(T);
+  if (warps > 3 && warps * 2 * page_bytes + (long long)warps * G * (hd + 2) * 4 + 2048 > 227 * 1024) warps = 3;
   const long long fixed = (long long)warps * G * (hd + 2) * 4 + sizeof(StreamShared) + 1024 + 64;
   int stages = (int)((110 * 1024 - fixed) / (2 * page_bytes)) / warps * warps;
   if (stages > DEC_MAX_STAGES) stages = DEC_MAX_STAGES;

@@ -56,8 +56,14 @@ bool takes_skinny(int M, long long N, int K) {
 }
 
 // ---- which attention kernel -----------------------------------------------------------------------------
+// as glint_attention_decode_supported (the tensor-core library is not linked here): three stages of a page of
+// keys and values have to fit a block's shared memory
 bool decode_supported(int nh, int nkv, int hd, int page) {
-  return nkv > 0 && nh % nkv == 0 && hd % 16 == 0 && hd >= 16 && hd <= 256 && page % 16 == 0 && page >= 16 && page <= 256;
+  if (!(nkv > 0 && nh % nkv == 0 && hd % 16 == 0 && hd >= 16 && hd <= 256 && page % 16 == 0 && page >= 16 && page <= 256))
+    return false;
+  const long long page_bytes = (long long)((hd + 63) / 64) * page * 128;
+  const int G = nh / nkv, HP = G < 8 ? G : 8;
+  return 3 * 2 * page_bytes + 3ll * HP * (hd + 2) * 4 + (long long)G * (hd + 2) * 4 + 2048 <= 227 * 1024;
 }
 bool prefill_supported(int nh, int nkv, int hd) {
   return nkv > 0 && nh % nkv == 0 && nh / nkv <= 64 && hd % 16 == 0 && hd >= 16 && hd <= 256;

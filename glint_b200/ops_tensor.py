@@ -20,6 +20,7 @@ _SIGNATURES = {
     "glint_gemm_tcgen05_rope": [_P, _P, _I, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "glint_gemm_skinny_rope": [_P, _P, _I, _I, _P, _P, _P, _I, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "glint_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P],
+    "glint_attention_decode_supported": [_I, _I, _I, _I],
     "glint_attention_decode_stream_plan": [_P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
     "glint_attention_decode_stream": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P,
                                       _P, _I, _P, _P],
@@ -171,8 +172,11 @@ def gemm_gated(a, w_gate_up, out, activation, status=None, force_splits=0, path=
 
 
 def decode_supported(nh, nkv, hd, page_size):
-    return (nkv > 0 and nh % nkv == 0 and hd % 16 == 0 and 16 <= hd <= 256 and page_size % 16 == 0
-            and 16 <= page_size <= 256)
+    """Sizes the single-token attention kernels take (three stages of a page of keys and values have to fit a
+    block's shared memory: pages of up to 64 tokens at head size 256)."""
+    if nkv <= 0:
+        return False
+    return bool(lib().glint_attention_decode_supported(nh, nkv, hd, page_size))
 
 
 def prefill_supported(nh, nkv, hd):

@@ -374,6 +374,7 @@ ATT_CASES = [
     (32, 16, 128, 16, [500, 0], [1, 130], 100, 30.0),
     (3, 3, 80, 32, [90], [45], None, 10.0),
     (16, 1, 64, 16, [31], [20], None, None),
+    (4, 2, 256, 64, [100, 3], [1, 1], None, 50.0),          # pages of 64 at head size 256: three stages, not four
 ]
 
 
@@ -435,6 +436,14 @@ def test_attention_kernels_against_float32(case, kernel):
     assert int(status.item()) == 0
     tol = 2e-5 if kernel == "plain32" else 0.03
     assert (got - want).abs().max().item() < tol, (got - want).abs().max().item()
+
+
+def test_single_token_attention_says_which_pages_it_takes():
+    from glint_b200 import ops_tensor
+    assert ops_tensor.decode_supported(8, 4, 256, 16) and ops_tensor.decode_supported(8, 4, 256, 64)
+    assert not ops_tensor.decode_supported(8, 4, 256, 128)       # three stages of such pages do not fit an SM
+    assert ops_tensor.decode_supported(32, 16, 128, 128) and ops_tensor.decode_supported(4, 1, 64, 256)
+    assert not ops_tensor.decode_supported(8, 3, 256, 16) and not ops_tensor.decode_supported(8, 4, 24, 16)
 
 
 @pytest.mark.parametrize("kernel", ["plain16", "decode", "stream", "prefill", "tcgen05"])
