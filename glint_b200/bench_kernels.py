@@ -98,7 +98,7 @@ def bench_attention_decode(batch, context, nh=8, nkv=4, hd=256, page=16, window=
     if kernel == "stream":
         blocks = 2 * ops_tensor.sm_count()
         plan = ops_tensor.attention_decode_stream_plan(pos, seq, batch, window, page, hd, nkv, blocks)
-        partials = torch.empty(blocks * 2 * (nh // nkv) * (hd + 4), dtype=torch.float32, device=DEV)
+        partials = torch.empty(ops_tensor.stream_workspace_floats(blocks, nh, nkv, hd), dtype=torch.float32, device=DEV)
         arrive = torch.zeros(batch * nkv, dtype=torch.int32, device=DEV)
         fn = lambda i: ops_tensor.attention_decode_stream(q, pools[i][0], pools[i][1], pos, seq, table, out, nh, nkv,
                                                           hd, page, n_pages, 1 / 16.0, cap, window, status, plan,

@@ -44,8 +44,8 @@ ATTN_PLANS = 8
 
 class AttnScratchStruct(Structure):
     """``GlintAttnScratch`` of csrc/runtime.h."""
-    _fields_ = [("mode", c_int), ("early_off", c_int), ("blocks", c_int), ("starts", c_void_p), ("headers", c_void_p), ("partials", c_void_p),
-                ("partial_floats", c_longlong), ("arrive", c_void_p), ("arrive_ints", c_int), ("next", c_int),
+    _fields_ = [("mode", c_int), ("early_off", c_int), ("blocks", c_int), ("starts", c_void_p),
+                ("headers", c_void_p), ("partials", c_void_p), ("partial_floats", c_longlong), ("arrive", c_void_p), ("arrive_ints", c_int), ("next", c_int),
                 ("plan_step", c_longlong * ATTN_PLANS), ("plan_tokens", c_int * ATTN_PLANS),
                 ("plan_window", c_int * ATTN_PLANS), ("plan_page", c_int * ATTN_PLANS), ("plan_nkv", c_int * ATTN_PLANS),
                 ("plan_hd", c_int * ATTN_PLANS)]
@@ -115,7 +115,7 @@ def make_runtime_struct(rt):
         # results of up to 8 query heads of 256 per kv head, counters for 1024 tokens x 64 kv heads
         a = AttnScratchStruct()
         a.blocks = 2 * s.sms
-        a.partial_floats = a.blocks * 2 * 8 * (256 + 4)
+        a.partial_floats = ops_tensor.stream_workspace_floats(a.blocks, 8, 1, 256)
         a.arrive_ints = 65536
         tensors = (torch.empty(ATTN_PLANS * a.blocks * 8, dtype=torch.int32, device=rt.device),
                    torch.zeros(ATTN_PLANS * 2, dtype=torch.int32, device=rt.device),

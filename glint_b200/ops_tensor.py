@@ -21,6 +21,7 @@ _SIGNATURES = {
     "glint_gemm_skinny_rope": [_P, _P, _I, _I, _P, _P, _P, _I, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "glint_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P],
     "glint_attention_decode_supported": [_I, _I, _I, _I],
+    "glint_attention_decode_stream_workspace": [_I, _I, _I, _I],
     "glint_attention_decode_stream_plan": [_P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
     "glint_attention_decode_stream": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P, _P,
                                       _P, _I, _P, _P],
@@ -223,6 +224,13 @@ def attention_decode(q, k_pool, v_pool, positions, token_seq, block_table, out, 
               "attention_decode")
 
 
+def stream_workspace_floats(blocks, nh, nkv, hd):
+    """Floats of workspace a launch of ``attention_decode_stream`` over ``blocks`` blocks needs."""
+    fn = lib().lib.glint_attention_decode_stream_workspace
+    fn.restype = c_longlong
+    return int(fn(blocks, nh, nkv, hd))
+
+
 def attention_decode_stream_plan(positions, token_seq, tokens, window, page_size, hd, nkv, blocks, min_pages=8,
                                  pair_cost=-1):
     """Plans a launch of ``attention_decode_stream``: (starts [blocks, 2, 4] int32, header [2] int32 = units per
@@ -241,12 +249,12 @@ def attention_decode_stream(q, k_pool, v_pool, positions, token_seq, block_table
                             num_pages, multiplier, cap, window, status, plan, partials, arrive, tokens=None):
     """``attention_decode`` with the pages of the whole launch shared evenly among the blocks (``plan`` from
     ``attention_decode_stream_plan`` with the same positions, window, page size and kv heads): ``partials``
-    float32 [blocks * 2 * (nh / nkv) * (hd + 4)], ``arrive`` int32 [tokens * nkv], zero before the first launch."""
+    float32 [``stream_workspace_floats``], ``arrive`` int32 [tokens * nkv], zero before the first launch."""
     T = q.shape[0] if tokens is None else tokens
     starts, header, blocks = plan
     ops.require(q, torch.bfloat16, "q"); ops.require(k_pool, torch.bfloat16, "k_pool")
     ops.require(v_pool, torch.bfloat16, "v_pool"); ops.require(out, torch.bfloat16, "out")
-    if partials.numel() < blocks * 2 * (nh // nkv) * (hd + 4) or arrive.numel() < T * nkv:
+    if partials.numel() < stream_workspace_floats(blocks, nh, nkv, hd) or arrive.numel() < T * nkv:
         raise KernelError("attention_decode_stream: the workspace is too small for this launch")
     ops.check(lib().glint_attention_decode_stream(ops.ptr(q), ops.ptr(k_pool), ops.ptr(v_pool), ops.ptr(positions),
                                                   ops.ptr(token_seq), ops.ptr(block_table), block_table.shape[1],

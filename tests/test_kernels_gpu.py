@@ -355,7 +355,8 @@ def _stream_attention(qd, k_pool, v_pool, positions, seq_of_token, table, out, n
     T = positions.shape[0]
     plan = ops_tensor.attention_decode_stream_plan(positions, seq_of_token, T, window, page, hd, nkv, blocks, min_pages=1,
                                                    pair_cost=pair_cost)
-    partials = torch.full((blocks * 2 * (nh // nkv) * (hd + 4),), float("nan"), dtype=torch.float32, device=DEV)
+    partials = torch.full((ops_tensor.stream_workspace_floats(blocks, nh, nkv, hd),), float("nan"), dtype=torch.float32,
+                          device=DEV)
     arrive = torch.zeros(T * nkv, dtype=torch.int32, device=DEV) if arrive is None else arrive
     ops_tensor.attention_decode_stream(qd, k_pool, v_pool, positions, seq_of_token, table, out, nh, nkv, hd, page,
                                        k_pool.shape[0], mult, cap, window, status, plan, partials, arrive)
